@@ -1,0 +1,171 @@
+"""Filter vocabularies as flat CSR arrays.
+
+The reference keeps three pickled ``defaultdict(list)`` objects keyed by int tuples
+(``er_vocab``: (h, r) → tails, ``re_vocab``: (r, t) → heads, ``ee_vocab``: (h, t) → relations;
+reference ``dicee/static_funcs.py:75-126``).  Here the same information lives in three
+sorted integer arrays (pair keys, offsets, values) that can be moved to the GPU as they
+are and consumed by the label-construction and filtered-ranking kernels.  ``to_dict``
+exports the reference's dictionary form so that the pickles on disk keep their layout.
+"""
+from __future__ import annotations
+
+from collections import defaultdict
+from typing import Dict, List, Tuple
+
+import numpy as np
+import torch
+
+
+class PairCSR:
+    """Mapping ``(a, b) -> sorted unique values`` stored as CSR over sorted pair keys.
+
+    ``key = a * num_b + b``.  ``keys`` is strictly increasing, ``offsets`` has
+    ``len(keys) + 1`` entries and ``values[offsets[i]:offsets[i+1]]`` are the values of
+    pair ``i`` in ascending order.
+    """
+
+    def __init__(self, keys: np.ndarray, offsets: np.ndarray, values: np.ndarray, num_b: int):
+        self.keys = keys.astype(np.int64, copy=False)
+        self.offsets = offsets.astype(np.int64, copy=False)
+        self.values = values.astype(np.int64, copy=False)
+        self.num_b = int(num_b)
+        self._torch_cache: Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def build(a: np.ndarray, b: np.ndarray, v: np.ndarray, num_b: int) -> "PairCSR":
+        a = np.asarray(a, dtype=np.int64)
+        b = np.asarray(b, dtype=np.int64)
+        v = np.asarray(v, dtype=np.int64)
+        if a.size == 0:
+            return PairCSR(np.zeros(0, np.int64), np.zeros(1, np.int64), np.zeros(0, np.int64), num_b)
+        key = a * int(num_b) + b
+        order = np.lexsort((v, key))
+        key, v = key[order], v[order]
+        # drop duplicate (key, value) rows
+        keep = np.ones(key.shape[0], dtype=bool)
+        keep[1:] = (key[1:] != key[:-1]) | (v[1:] != v[:-1])
+        key, v = key[keep], v[keep]
+        uniq, start = np.unique(key, return_index=True)
+        offsets = np.concatenate([start, [key.shape[0]]])
+        return PairCSR(uniq, offsets, v, num_b)
+
+    # ------------------------------------------------------------------ queries
+    def __len__(self) -> int:
+        return int(self.keys.shape[0])
+
+    @property
+    def pairs(self) -> np.ndarray:
+        """``[num_pairs, 2]`` array of (a, b) in key order (lexicographic)."""
+        return np.stack([self.keys // self.num_b, self.keys % self.num_b], axis=1)
+
+    def counts(self) -> np.ndarray:
+        return np.diff(self.offsets)
+
+    def lookup(self, a: int, b: int) -> np.ndarray:
+        k = int(a) * self.num_b + int(b)
+        i = int(np.searchsorted(self.keys, k))
+        if i >= len(self) or self.keys[i] != k:
+            return self.values[:0]
+        return self.values[self.offsets[i]:self.offsets[i + 1]]
+
+    def to_dict(self) -> Dict[Tuple[int, int], List[int]]:
+        out: Dict[Tuple[int, int], List[int]] = defaultdict(list)
+        pairs = self.pairs
+        off = self.offsets
+        vals = self.values.tolist()
+        for i, (x, y) in enumerate(pairs.tolist()):
+            out[(x, y)] = vals[off[i]:off[i + 1]]
+        return out
+
+    def tensors(self, device="cpu") -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(keys, offsets, values) as int64 tensors on ``device`` (cached per device)."""
+        dev = str(device)
+        if dev not in self._torch_cache:
+            self._torch_cache[dev] = (torch.from_numpy(self.keys).to(device),
+                                      torch.from_numpy(self.offsets).to(device),
+                                      torch.from_numpy(self.values).to(device))
+        return self._torch_cache[dev]
+
+    def batch_slices(self, a: torch.Tensor, b: torch.Tensor):
+        """For query tensors ``a, b`` return ``(start, count)`` of each pair's value slice
+        (count 0 for unseen pairs).  Runs on the device the queries live on."""
+        keys, offsets, _ = self.tensors(a.device)
+        k = a.long() * self.num_b + b.long()
+        if keys.numel() == 0:
+            z = torch.zeros_like(k)
+            return z, z
+        pos = torch.searchsorted(keys, k).clamp_(max=keys.numel() - 1)
+        hit = keys[pos] == k
+        start = offsets[pos]
+        count = torch.where(hit, offsets[pos + 1] - start, torch.zeros_like(start))
+        return start, count
+
+    def batch_rows_cols(self, a: torch.Tensor, b: torch.Tensor):
+        """Flattened (row, value) coordinates of all known values of the given pairs."""
+        _, _, values = self.tensors(a.device)
+        start, count = self.batch_slices(a, b)
+        total = int(count.sum())
+        rows = torch.repeat_interleave(torch.arange(a.shape[0], device=a.device), count)
+        if total == 0:
+            return rows, values[:0]
+        first = torch.cumsum(count, 0) - count
+        within = torch.arange(total, device=a.device) - torch.repeat_interleave(first, count)
+        cols = values[torch.repeat_interleave(start, count) + within]
+        return rows, cols
+
+
+def er_csr(triples: np.ndarray, num_relations: int) -> PairCSR:
+    return PairCSR.build(triples[:, 0], triples[:, 1], triples[:, 2], num_relations)
+
+
+def re_csr(triples: np.ndarray, num_entities: int) -> PairCSR:
+    return PairCSR.build(triples[:, 1], triples[:, 2], triples[:, 0], num_entities)
+
+
+def ee_csr(triples: np.ndarray, num_entities: int) -> PairCSR:
+    return PairCSR.build(triples[:, 0], triples[:, 2], triples[:, 1], num_entities)
+
+
+def _dict_vocab(a, b, v) -> Dict[Tuple[int, int], List[int]]:
+    out: Dict[Tuple[int, int], List[int]] = defaultdict(list)
+    for x, y, z in zip(a.tolist(), b.tolist(), v.tolist()):
+        out[(x, y)].append(z)
+    return out
+
+
+def get_er_vocab(data: np.ndarray) -> Dict[Tuple[int, int], List[int]]:
+    """(head, relation) → list of tails in input order (reference ``static_funcs.py:75-90``)."""
+    data = np.asarray(data)
+    return _dict_vocab(data[:, 0], data[:, 1], data[:, 2])
+
+
+def get_re_vocab(data: np.ndarray) -> Dict[Tuple[int, int], List[int]]:
+    """(relation, tail) → list of heads (reference ``static_funcs.py:93-108``)."""
+    data = np.asarray(data)
+    return _dict_vocab(data[:, 1], data[:, 2], data[:, 0])
+
+
+def get_ee_vocab(data: np.ndarray) -> Dict[Tuple[int, int], List[int]]:
+    """(head, tail) → list of relations (reference ``static_funcs.py:111-126``)."""
+    data = np.asarray(data)
+    return _dict_vocab(data[:, 0], data[:, 2], data[:, 1])
+
+
+def create_constraints(triples: np.ndarray):
+    """Domain / range of every relation and their complements.
+
+    Returns ``(domain_constraints, range_constraints, domain, range)`` as dicts
+    relation → list of entity ids, where the *constraints* are the entities that never
+    occur in that slot (reference ``dicee/static_preprocess_funcs.py:76-108``).
+    """
+    triples = np.asarray(triples)
+    ents = np.unique(np.concatenate([triples[:, 0], triples[:, 2]]))
+    dom, rng = {}, {}
+    for r in np.unique(triples[:, 1]).tolist():
+        sel = triples[triples[:, 1] == r]
+        dom[r] = np.unique(sel[:, 0])
+        rng[r] = np.unique(sel[:, 2])
+    dom_c = {r: np.setdiff1d(ents, d).tolist() for r, d in dom.items()}
+    rng_c = {r: np.setdiff1d(ents, d).tolist() for r, d in rng.items()}
+    return dom_c, rng_c, {r: d.tolist() for r, d in dom.items()}, {r: d.tolist() for r, d in rng.items()}
