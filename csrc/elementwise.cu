@@ -1,0 +1,526 @@
+// Bandwidth-bound kernels around the fused scoring GEMM:
+//   * lookup + query composition (+ broadcast of the bf16 query rows to every rank's buffer),
+//   * sparse positive-label correction of loss / dQ / dE driven by the CSR of known tails,
+//   * backward of the composition with scatter-add of row gradients to the owning shard,
+//   * dense Adam / ADOPT / SGD sweeps that also refresh the bf16 shadow table and clear the gradient,
+//   * small helpers (casts, prefix sums, loss finalisation).
+// Entity rows are distributed cyclically: global row e lives on rank e % W at local row e / W.  All kernels take
+// arrays of per-rank base pointers, so with W == 1 they act on one table and with W > 1 they read / write peer
+// memory directly (plain ld/st/red over NVLink; no multicast loads).
+#include "ptx_sm100.cuh"
+
+namespace dice {
+
+// ------------------------------------------------------------------------------------ algebra tables
+// q_k = sum_a SGN[k][a] * h_a * r_{IDX[k][a]}   for K blocks of width D / K (block layout).
+template <int K> struct Alg;
+template <> struct Alg<1> {
+  static __device__ __forceinline__ int idx(int k, int a) { return 0; }
+  static __device__ __forceinline__ float sgn(int k, int a) { return 1.f; }
+};
+template <> struct Alg<2> {  // complex product
+  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
+  static __device__ __forceinline__ float sgn(int k, int a) { return (k == 0 && a == 1) ? -1.f : 1.f; }
+};
+template <> struct Alg<4> {  // Hamilton product
+  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
+  static __device__ __forceinline__ float sgn(int k, int a) {
+    // rows k, columns a; entries are the sign of h_a * r_{k^a} in component k
+    constexpr int S[4][4] = {{1, -1, -1, -1}, {1, 1, 1, -1}, {1, -1, 1, 1}, {1, 1, -1, 1}};
+    return static_cast<float>(S[k][a]);
+  }
+};
+template <> struct Alg<8> {  // octonion product
+  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
+  static __device__ __forceinline__ float sgn(int k, int a) {
+    constexpr int S[8][8] = {{1, -1, -1, -1, -1, -1, -1, -1}, {1, 1, 1, -1, 1, -1, -1, 1},
+                             {1, -1, 1, 1, 1, 1, -1, -1},     {1, 1, -1, 1, 1, -1, 1, -1},
+                             {1, -1, -1, -1, 1, 1, 1, 1},     {1, 1, -1, 1, -1, 1, -1, 1},
+                             {1, 1, 1, -1, -1, 1, 1, -1},     {1, -1, 1, 1, -1, -1, 1, 1}};
+    return static_cast<float>(S[k][a]);
+  }
+};
+
+enum NormMode : int { NORM_NONE = 0, NORM_ACROSS_BLOCKS = 1, NORM_CONSECUTIVE4 = 2 };
+
+// Loads the K x VEC elements of row `row` that one thread owns (positions j0..j0+VEC-1 of every block).
+template <int K, int VEC>
+__device__ __forceinline__ void load_blocks(const float* __restrict__ row, int w, int j0, float (&v)[K][VEC]) {
+#pragma unroll
+  for (int a = 0; a < K; ++a)
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) v[a][u] = row[a * w + j0 + u];
+}
+
+template <int K, int VEC>
+__device__ __forceinline__ void normalize_rel(int mode, const float (&r)[K][VEC], float (&rh)[K][VEC],
+                                              float (&nrm)[K][VEC]) {
+#pragma unroll
+  for (int a = 0; a < K; ++a)
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) { rh[a][u] = r[a][u]; nrm[a][u] = 1.f; }
+  if (mode == NORM_ACROSS_BLOCKS) {
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      float s = 0.f;
+#pragma unroll
+      for (int a = 0; a < K; ++a) s += r[a][u] * r[a][u];
+      const float n = sqrtf(s);
+#pragma unroll
+      for (int a = 0; a < K; ++a) { rh[a][u] = r[a][u] / n; nrm[a][u] = n; }
+    }
+  } else if (mode == NORM_CONSECUTIVE4) {
+#pragma unroll
+    for (int a = 0; a < K; ++a) {
+      float s = 0.f;
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) s += r[a][u] * r[a][u];
+      const float n = fmaxf(sqrtf(s), 1e-12f);
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) { rh[a][u] = r[a][u] / n; nrm[a][u] = n; }
+    }
+  }
+}
+
+struct LookupParams {
+  const long long* idx_h;        // [B] global entity ids
+  const long long* idx_r;        // [B] relation ids
+  const float* const* ent;       // [W] fp32 shard bases (peer pointers allowed)
+  const float* rel;              // [R, D] replicated
+  const float* coeff;            // Keci q-coefficient (single float) or null
+  __nv_bfloat16* const* q_dst;   // [n_dst] destination query buffers (all ranks, or just this one)
+  float* q_f32;                  // optional local fp32 copy [B, D]
+  int n_dst;
+  long long q_row_offset;        // first destination row of this rank's batch
+  int B, D, W, norm_mode;
+  int* status;
+  long long num_entities;
+};
+
+template <int K, int VEC>
+__global__ void lookup_compose_kernel(const LookupParams p) {
+  const int w = p.D / K;
+  const int per_row = w / VEC;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (tid >= static_cast<long long>(p.B) * per_row) return;
+  const int i = static_cast<int>(tid / per_row);
+  const int j0 = static_cast<int>(tid % per_row) * VEC;
+  const long long h = p.idx_h[i];
+  const long long r_id = p.idx_r[i];
+  if (h < 0 || h >= p.num_entities) { atomicCAS(p.status, 0, ST_BAD_INDEX); return; }
+  const float* hrow = p.ent[h % p.W] + (h / p.W) * p.D;
+  const float* rrow = p.rel + r_id * p.D;
+  float hv[K][VEC], rv[K][VEC], rh[K][VEC], nrm[K][VEC];
+  load_blocks<K, VEC>(hrow, w, j0, hv);
+  load_blocks<K, VEC>(rrow, w, j0, rv);
+  normalize_rel<K, VEC>(p.norm_mode, rv, rh, nrm);
+  if (p.coeff != nullptr) {  // Keci Cl(0,1): the vector part of head and relation is scaled by the coefficient
+    const float c = *p.coeff;
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) { hv[K - 1][u] *= c; rh[K - 1][u] *= c; }
+  }
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+      float q = 0.f;
+#pragma unroll
+      for (int a = 0; a < K; ++a) q = fmaf(Alg<K>::sgn(k, a) * hv[a][u], rh[Alg<K>::idx(k, a)][u], q);
+      const long long col = k * w + j0 + u;
+      const __nv_bfloat16 qb = __float2bfloat16_rn(q);
+      for (int d = 0; d < p.n_dst; ++d) p.q_dst[d][(p.q_row_offset + i) * p.D + col] = qb;
+      if (p.q_f32 != nullptr) p.q_f32[static_cast<long long>(i) * p.D + col] = q;
+    }
+  }
+}
+
+struct ComposeBwdParams {
+  const long long* idx_h;
+  const long long* idx_r;
+  const float* const* ent;     // fp32 shards (forward values are recomputed from them)
+  const float* rel;
+  const float* coeff;
+  const float* dq;             // [B, D] fp32 gradient w.r.t. the query vectors
+  float* const* g_ent;         // [W] fp32 gradient shards (red.add; peer pointers allowed)
+  float* g_rel;                // [R, D]
+  float* g_coeff;              // single float or null
+  int B, D, W, norm_mode;
+};
+
+template <int K, int VEC>
+__global__ void compose_backward_kernel(const ComposeBwdParams p) {
+  const int w = p.D / K;
+  const int per_row = w / VEC;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  float dc = 0.f;
+  if (tid < static_cast<long long>(p.B) * per_row) {
+    const int i = static_cast<int>(tid / per_row);
+    const int j0 = static_cast<int>(tid % per_row) * VEC;
+    const long long h = p.idx_h[i];
+    const long long r_id = p.idx_r[i];
+    const float* hrow = p.ent[h % p.W] + (h / p.W) * p.D;
+    const float* rrow = p.rel + r_id * p.D;
+    float hv[K][VEC], rv[K][VEC], rh[K][VEC], nrm[K][VEC], dq[K][VEC], dh[K][VEC], drh[K][VEC];
+    load_blocks<K, VEC>(hrow, w, j0, hv);
+    load_blocks<K, VEC>(rrow, w, j0, rv);
+    load_blocks<K, VEC>(p.dq + static_cast<long long>(i) * p.D, w, j0, dq);
+    normalize_rel<K, VEC>(p.norm_mode, rv, rh, nrm);
+    float c = 1.f;
+    if (p.coeff != nullptr) {
+      c = *p.coeff;
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) { hv[K - 1][u] *= c; rh[K - 1][u] *= c; }
+    }
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) { dh[a][u] = 0.f; drh[a][u] = 0.f; }
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) {
+          const float g = Alg<K>::sgn(k, a) * dq[k][u];
+          dh[a][u] = fmaf(g, rh[Alg<K>::idx(k, a)][u], dh[a][u]);
+          drh[Alg<K>::idx(k, a)][u] = fmaf(g, hv[a][u], drh[Alg<K>::idx(k, a)][u]);
+        }
+    if (p.coeff != nullptr) {
+      // hv[K-1] = c * h_raw, rh[K-1] = c * r_raw  =>  d/dc collects both, raw grads pick up a factor c
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) {
+        const float h_raw = (c != 0.f) ? hv[K - 1][u] / c : hrow[(K - 1) * w + j0 + u];
+        const float r_raw = (c != 0.f) ? rh[K - 1][u] / c : rrow[(K - 1) * w + j0 + u];
+        dc += dh[K - 1][u] * h_raw + drh[K - 1][u] * r_raw;
+        dh[K - 1][u] *= c;
+        drh[K - 1][u] *= c;
+      }
+    }
+    // back through the relation normalisation: dr = (drh - rh * <drh, rh>_group) / norm
+    if (p.norm_mode == NORM_ACROSS_BLOCKS) {
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) {
+        float dot = 0.f;
+#pragma unroll
+        for (int a = 0; a < K; ++a) dot += drh[a][u] * rh[a][u];
+#pragma unroll
+        for (int a = 0; a < K; ++a) drh[a][u] = (drh[a][u] - rh[a][u] * dot) / nrm[a][u];
+      }
+    } else if (p.norm_mode == NORM_CONSECUTIVE4) {
+#pragma unroll
+      for (int a = 0; a < K; ++a) {
+        float dot = 0.f;
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) dot += drh[a][u] * rh[a][u];
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) drh[a][u] = (drh[a][u] - rh[a][u] * dot) / nrm[a][u];
+      }
+    }
+    float* ge = p.g_ent[h % p.W] + (h / p.W) * p.D;
+    float* gr = p.g_rel + r_id * p.D;
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) {
+        atomicAdd(ge + a * w + j0 + u, dh[a][u]);
+        atomicAdd(gr + a * w + j0 + u, drh[a][u]);
+      }
+  }
+  if (p.g_coeff != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dc += __shfl_xor_sync(0xffffffffu, dc, o);
+    if ((threadIdx.x & 31) == 0 && dc != 0.f) atomicAdd(p.g_coeff, dc);
+  }
+}
+
+// ------------------------------------------------------------------------------------ positives
+// first[i] = number of positive labels of batch items 0..i-1; first[n] = total.
+__global__ void positive_scan_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
+                                     int n, int* __restrict__ first) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    int c = 0;
+    if (i < n) {
+      const long long d = dp_idx[i];
+      c = static_cast<int>(offsets[d + 1] - offsets[d]);
+    }
+    int v = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, v, o);
+      if ((threadIdx.x & 31) >= o) v += t;
+    }
+    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int s = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, s, o);
+        if (threadIdx.x >= o) s += t;
+      }
+      warp_sums[threadIdx.x] = s;
+    }
+    __syncthreads();
+    const int prefix = carry + ((threadIdx.x >> 5) > 0 ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - c;
+    if (i < n) first[i] = prefix;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = prefix + c;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) first[n] = carry;
+}
+
+struct PositiveParams {
+  const long long* dp_idx;     // [n] data-point ids of the (gathered) batch
+  const long long* offsets;    // CSR over data points
+  const long long* values;     // global tail ids
+  const int* first;            // [n + 1] prefix sums of positives per batch item
+  const __nv_bfloat16* q;      // [n, D]
+  const __nv_bfloat16* e;      // local entity shard [rows_local, D], bf16 shadow
+  float* dq;                   // [n, D] fp32, red.add
+  float* de;                   // [rows_local, D] fp32, red.add
+  double* loss;
+  float weight;                // label(positive) - label(elsewhere)
+  float scale;                 // 1 / (B * |E|)
+  int n, W, rank;
+};
+
+template <int D, int CHUNK>
+__global__ void positive_correction_kernel(const PositiveParams p) {
+  constexpr int PER = D / 32;  // dims per lane
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const long long warp_global = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5);
+  const long long num_warps = static_cast<long long>(gridDim.x) * warps_per_block;
+  const int total = p.first[p.n];
+  float loss_local = 0.f;
+  for (long long c0 = warp_global * CHUNK; c0 < total; c0 += num_warps * CHUNK) {
+    const int pend = static_cast<int>(min(static_cast<long long>(total), c0 + CHUNK));
+    // batch item owning positive c0: last i with first[i] <= c0
+    int lo = 0, hi = p.n;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.first[mid] <= c0) lo = mid; else hi = mid;
+    }
+    int i = lo;
+    float qv[PER], acc[PER];
+    int loaded = -1;
+#pragma unroll
+    for (int u = 0; u < PER; ++u) acc[u] = 0.f;
+    for (int pp = static_cast<int>(c0); pp < pend; ++pp) {
+      while (p.first[i + 1] <= pp) {
+        if (loaded == i) {
+#pragma unroll
+          for (int u = 0; u < PER; ++u) { atomicAdd(p.dq + static_cast<long long>(i) * D + lane * PER + u, acc[u]); acc[u] = 0.f; }
+        }
+        ++i;
+      }
+      const long long d = p.dp_idx[i];
+      const long long j = p.values[p.offsets[d] + (pp - p.first[i])];
+      if (j % p.W != p.rank) continue;
+      if (loaded != i) {
+        const __nv_bfloat16* qrow = p.q + static_cast<long long>(i) * D + lane * PER;
+#pragma unroll
+        for (int u = 0; u < PER; ++u) qv[u] = __bfloat162float(qrow[u]);
+        loaded = i;
+      }
+      const long long jl = j / p.W;
+      const __nv_bfloat16* erow = p.e + jl * D + lane * PER;
+      float ev[PER];
+      float dot = 0.f;
+#pragma unroll
+      for (int u = 0; u < PER; ++u) { ev[u] = __bfloat162float(erow[u]); dot = fmaf(qv[u], ev[u], dot); }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      loss_local -= p.weight * dot;
+      const float g = -p.weight * p.scale;
+      float* derow = p.de + jl * D + lane * PER;
+#pragma unroll
+      for (int u = 0; u < PER; ++u) { atomicAdd(derow + u, g * qv[u]); acc[u] = fmaf(g, ev[u], acc[u]); }
+    }
+    if (loaded == i) {
+#pragma unroll
+      for (int u = 0; u < PER; ++u) atomicAdd(p.dq + static_cast<long long>(i) * D + lane * PER + u, acc[u]);
+    }
+  }
+  if (lane == 0 && loss_local != 0.f) atomicAdd(p.loss, static_cast<double>(loss_local));
+}
+
+// ------------------------------------------------------------------------------------ optimisers
+struct OptParams {
+  float* param;
+  float* grad;               // cleared after use
+  float* m;
+  float* v;
+  __nv_bfloat16* shadow;     // optional bf16 copy refreshed in the same pass
+  const long long* step;     // device-side step counter (number of completed steps)
+  long long n;
+  float lr, beta1, beta2, eps, weight_decay;
+  int kind;                  // 0 Adam, 1 AdamW, 2 SGD, 3 ADOPT
+};
+
+__global__ void optimizer_kernel(const OptParams p) {
+  const long long t = *p.step + 1;
+  float bc1 = 1.f, bc2 = 1.f;
+  if (p.kind <= 1) {
+    bc1 = 1.f - powf(p.beta1, static_cast<float>(t));
+    bc2 = 1.f - powf(p.beta2, static_cast<float>(t));
+  }
+  const float clip = powf(static_cast<float>(t - 1), 0.25f);  // ADOPT: clip bound of the current step index
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float w = p.param[i];
+    float g = p.grad[i];
+    p.grad[i] = 0.f;
+    if (p.kind == 0) {
+      g = fmaf(p.weight_decay, w, g);
+      const float m = p.m[i] = fmaf(p.beta1, p.m[i], (1.f - p.beta1) * g);
+      const float v = p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
+      w -= p.lr / bc1 * m / (sqrtf(v) / sqrtf(bc2) + p.eps);
+    } else if (p.kind == 1) {
+      w *= 1.f - p.lr * p.weight_decay;
+      const float m = p.m[i] = fmaf(p.beta1, p.m[i], (1.f - p.beta1) * g);
+      const float v = p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
+      w -= p.lr / bc1 * m / (sqrtf(v) / sqrtf(bc2) + p.eps);
+    } else if (p.kind == 2) {
+      g = fmaf(p.weight_decay, w, g);
+      w -= p.lr * g;
+    } else {  // ADOPT
+      g = fmaf(p.weight_decay, w, g);
+      if (t == 1) {
+        p.v[i] = g * g;
+      } else {
+        float ng = g / fmaxf(sqrtf(p.v[i]), p.eps);
+        ng = fminf(fmaxf(ng, -clip), clip);
+        const float m = p.m[i] = p.m[i] + (1.f - p.beta1) * (ng - p.m[i]);
+        w -= p.lr * m;
+        p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
+      }
+    }
+    p.param[i] = w;
+    if (p.shadow != nullptr) p.shadow[i] = __float2bfloat16_rn(w);
+  }
+}
+
+__global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// loss_out = acc * inv_count; acc = 0; step += 1   (one thread)
+__global__ void finish_step_kernel(double* acc, float* loss_out, double inv_count, long long* step) {
+  *loss_out = static_cast<float>(*acc * inv_count);
+  *acc = 0.0;
+  if (step != nullptr) *step += 1;
+}
+
+template <int K, int VEC>
+static int launch_lookup(const LookupParams& p, cudaStream_t s) {
+  const long long n = static_cast<long long>(p.B) * (p.D / K / VEC);
+  lookup_compose_kernel<K, VEC><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+template <int K, int VEC>
+static int launch_bwd(const ComposeBwdParams& p, cudaStream_t s) {
+  const long long n = static_cast<long long>(p.B) * (p.D / K / VEC);
+  compose_backward_kernel<K, VEC><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace dice
+
+using namespace dice;
+
+// model: 0 DistMult, 1 ComplEx, 2 QMult (relation quaternion-normalised over consecutive 4-tuples when
+// normalize != 0), 3 OMult (relation normalised across its 8 blocks when normalize != 0), 4 Keci Cl(0,1) with
+// coefficient `coeff`.  ent / q_dst are *device* arrays of W / n_dst base pointers.
+extern "C" int dice_lookup_compose(int model, int normalize, const long long* idx_h, const long long* idx_r,
+                                   const float* const* ent, int W, long long num_entities, const float* rel,
+                                   const float* coeff, __nv_bfloat16* const* q_dst, int n_dst,
+                                   long long q_row_offset, float* q_f32, int B, int D, int* status, void* stream) {
+  if (B <= 0) return 0;
+  LookupParams p{idx_h, idx_r, ent, rel, nullptr, q_dst, q_f32, n_dst, q_row_offset, B, D, W, NORM_NONE, status,
+                 num_entities};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (model) {
+    case 0: return launch_lookup<1, 1>(p, s);
+    case 1: if (D % 2) return -6; return launch_lookup<2, 1>(p, s);
+    case 2: if (D % 16) return -6; p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_lookup<4, 4>(p, s);
+    case 3: if (D % 8) return -6; p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_lookup<8, 1>(p, s);
+    case 4: if (D % 2) return -6; p.coeff = coeff; return launch_lookup<2, 1>(p, s);
+    default: return -6;
+  }
+}
+
+extern "C" int dice_compose_backward(int model, int normalize, const long long* idx_h, const long long* idx_r,
+                                     const float* const* ent, int W, const float* rel, const float* coeff,
+                                     const float* dq, float* const* g_ent, float* g_rel, float* g_coeff, int B, int D,
+                                     void* stream) {
+  if (B <= 0) return 0;
+  ComposeBwdParams p{idx_h, idx_r, ent, rel, nullptr, dq, g_ent, g_rel, nullptr, B, D, W, NORM_NONE};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (model) {
+    case 0: return launch_bwd<1, 1>(p, s);
+    case 1: return launch_bwd<2, 1>(p, s);
+    case 2: p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_bwd<4, 4>(p, s);
+    case 3: p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_bwd<8, 1>(p, s);
+    case 4: p.coeff = coeff; p.g_coeff = g_coeff; return launch_bwd<2, 1>(p, s);
+    default: return -6;
+  }
+}
+
+extern "C" int dice_positive_scan(const long long* dp_idx, const long long* offsets, int n, int* first, void* stream) {
+  positive_scan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int dice_positive_correction(const long long* dp_idx, const long long* offsets, const long long* values,
+                                        const int* first, const void* q, const void* e, float* dq, float* de,
+                                        double* loss, float weight, float scale, int n, int D, int W, int rank,
+                                        void* stream) {
+  if (n <= 0) return 0;
+  PositiveParams p{dp_idx, offsets, values, first, static_cast<const __nv_bfloat16*>(q),
+                   static_cast<const __nv_bfloat16*>(e), dq, de, loss, weight, scale, n, W, rank};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = 148 * 4, threads = 256;
+  switch (D) {
+    case 256: positive_correction_kernel<256, 8><<<blocks, threads, 0, s>>>(p); break;
+    case 128: positive_correction_kernel<128, 8><<<blocks, threads, 0, s>>>(p); break;
+    case 64: positive_correction_kernel<64, 8><<<blocks, threads, 0, s>>>(p); break;
+    case 32: positive_correction_kernel<32, 8><<<blocks, threads, 0, s>>>(p); break;
+    default: return -6;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int dice_optimizer_step(int kind, float* param, float* grad, float* m, float* v, void* shadow,
+                                   const long long* step, long long n, float lr, float beta1, float beta2, float eps,
+                                   float weight_decay, void* stream) {
+  if (n <= 0) return 0;
+  OptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), step, n, lr, beta1, beta2, eps, weight_decay, kind};
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  optimizer_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int dice_cast_bf16(const float* src, void* dst, long long n, void* stream) {
+  if (n <= 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, static_cast<__nv_bfloat16*>(dst), n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int dice_finish_step(double* acc, float* loss_out, double inv_count, long long* step, void* stream) {
+  finish_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(acc, loss_out, inv_count, step);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

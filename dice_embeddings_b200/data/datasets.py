@@ -142,6 +142,9 @@ class KvsAll(BatchedDataset):
 
     def make_batch(self, idx, generator=None):
         x = self.train_data[idx]
+        if getattr(self, "sparse_labels", False):
+            # consumers that hold the CSR themselves (the fused engine) only need the data-point ids
+            return x, idx
         rows, cols = self.positives(idx)
         pos, base = self.label_constants()
         y = multihot_from_csr(rows, cols, idx.numel(), self.target_dim, pos, base)
@@ -180,6 +183,8 @@ class OnevsAllDataset(BatchedDataset):
 
     def make_batch(self, idx, generator=None):
         tr = self.train_data[idx]
+        if getattr(self, "sparse_labels", False):
+            return tr[:, :2], idx
         y = torch.zeros(idx.numel(), self.target_dim, device=tr.device)
         y[torch.arange(idx.numel(), device=tr.device), tr[:, 2]] = 1.0
         return tr[:, :2], y

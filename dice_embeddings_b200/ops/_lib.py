@@ -1,0 +1,98 @@
+"""Build and load the sm_100a kernel library.
+
+All CUDA sources under ``csrc/`` are compiled by ``nvcc`` into one shared object that sits next to this file
+(``libdice_b200.so``) and is loaded with :mod:`ctypes`.  The exported entry points are plain ``extern "C"``
+functions taking raw device pointers and a stream handle, so no PyTorch headers are needed to build
+(a full rebuild takes seconds) and non-Python callers can link the same library.  The only supported target is
+``sm_100a``; there is no fallback build for other architectures.
+"""
+from __future__ import annotations
+
+import ctypes
+import glob
+import os
+import subprocess
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(os.path.dirname(_HERE))
+CSRC = os.path.join(_ROOT, "csrc")
+LIB_PATH = os.path.join(_HERE, "libdice_b200.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC"]
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def sources():
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+
+
+def needs_build() -> bool:
+    if not os.path.isfile(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h"))
+    return any(os.path.getmtime(s) > t for s in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile ``csrc/*.cu`` for sm_100a into ``libdice_b200.so`` (no-op when up to date)."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.isfile(nvcc):
+        nvcc = "nvcc"
+    cmd = [nvcc, *NVCC_FLAGS, *sources(), "-o", LIB_PATH + ".tmp"]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stderr)
+    os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    return LIB_PATH
+
+
+def available() -> bool:
+    """True when the library file exists (it may still need a B200 to run)."""
+    return os.path.isfile(LIB_PATH)
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first if the sources are newer and a compiler is present)."""
+    global _lib
+    if _lib is None:
+        if needs_build():
+            try:
+                build()
+            except (RuntimeError, FileNotFoundError):
+                if not os.path.isfile(LIB_PATH):
+                    raise
+        _lib = ctypes.CDLL(LIB_PATH)
+        for name in dir(_Sigs):
+            if name.startswith("dice_"):
+                fn = getattr(_lib, name)
+                fn.restype = ctypes.c_int
+                fn.argtypes = getattr(_Sigs, name)
+    return _lib
+
+
+_p = ctypes.c_void_p
+_i = ctypes.c_int
+_l = ctypes.c_longlong
+_f = ctypes.c_float
+_d = ctypes.c_double
+
+
+class _Sigs:
+    dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p]
+    dice_lookup_compose = [_i, _i, _p, _p, _p, _i, _l, _p, _p, _p, _i, _l, _p, _i, _i, _p, _p]
+    dice_compose_backward = [_i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _p]
+    dice_positive_scan = [_p, _p, _i, _p, _p]
+    dice_positive_correction = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p]
+    dice_optimizer_step = [_i, _p, _p, _p, _p, _p, _p, _l, _f, _f, _f, _f, _f, _p]
+    dice_cast_bf16 = [_p, _p, _l, _p]
+    dice_finish_step = [_p, _p, _d, _p, _p]

@@ -1,0 +1,265 @@
+"""Fused single-GPU training step for bilinear models trained against all entities (KvsAll, AllvsAll, 1vsAll).
+
+One step is seven kernel launches replayed from a CUDA graph:
+
+1. ``lookup_compose``      gather ``E[h]``, ``R[r]`` (fp32 masters), compose the query, write it as bf16
+2. ``kvsall_fused`` (E)    X = bf16 entity table, Y = queries  →  dense part of ``dE`` and of the loss
+3. ``kvsall_fused`` (Q)    X = queries, Y = entity table        →  dense part of ``dQ``
+4. ``positive_scan`` + ``positive_correction``   sparse label term from the CSR of known tails
+5. ``compose_backward``    chain rule of the composition, row gradients scattered into ``dE`` / ``dR``
+6. ``optimizer_step`` ×k   Adam / AdamW / SGD / ADOPT over E (refreshing the bf16 shadow), R and the coefficient
+7. ``finish_step``         loss = accumulator / (B·|E|), accumulator = 0, step += 1
+
+The ``[B, |E|]`` logit and label matrices of the reference's step (``dicee/models/base_model.py:25-46``:
+forward, ``BCEWithLogitsLoss``, backward, optimiser) never exist; labels are the resident CSR.  The model's own
+``nn.Parameter`` storage is updated in place, so evaluation and checkpointing see the trained weights.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import Optional, Tuple
+
+import torch
+
+from ..models.base import IdentityClass
+from . import kernels as K
+
+SUPPORTED_DIMS = (64, 128, 256)
+SUPPORTED_SCORING = ("KvsAll", "AllvsAll", "1vsAll")
+
+
+def fused_model_code(model) -> Optional[int]:
+    """Kernel model code, or ``None`` when the model is outside what the fused path covers."""
+    name = type(model).__name__
+    if name not in K.MODEL_CODE:
+        return None
+    if name in ("Keci", "CKeci") and not (model.p == 0 and model.q == 1):
+        return None
+    if model.input_dropout_rate or not isinstance(model.normalize_head_entity_embeddings, IdentityClass):
+        return None
+    if model.embedding_dim not in SUPPORTED_DIMS or getattr(model, "byte_pair_encoding", False):
+        return None
+    if model.optimizer_name not in K.OPT_CODE:
+        return None
+    return K.MODEL_CODE[name]
+
+
+def build_fused_engine(model, dataset, args, device, strict: bool = False):
+    """Return a :class:`FusedKvsAllEngine` when model, dataset and optimiser qualify, else ``None``
+    (or raise when ``strict``)."""
+    reason = None
+    if fused_model_code(model) is None:
+        reason = f"model {type(model).__name__} (dim {model.embedding_dim}, optim {model.optimizer_name}) is not covered"
+    elif getattr(args, "scoring_technique", None) not in SUPPORTED_SCORING:
+        reason = f"scoring technique {getattr(args, 'scoring_technique', None)} is not covered"
+    elif dataset is None or not hasattr(dataset, "train_data"):
+        reason = "dataset does not expose its index tensors"
+    elif torch.cuda.get_device_capability(device)[0] != 10:
+        reason = "device is not sm_100"
+    if reason is not None:
+        if strict:
+            raise RuntimeError("kernel_backend=cuda requested but " + reason)
+        return None
+    return FusedKvsAllEngine(model, dataset, batch_size=args.batch_size, lr=args.lr,
+                             weight_decay=getattr(args, "weight_decay", 0.0) or 0.0, device=device)
+
+
+class FusedKvsAllEngine:
+    def __init__(self, model, dataset, batch_size: int, lr: float, weight_decay: float = 0.0, device=None,
+                 use_graph: bool = True):
+        self.model = model
+        self.device = torch.device(device or model.device)
+        self.code = fused_model_code(model)
+        assert self.code is not None
+        dev = self.device
+        self.D = model.embedding_dim
+        self.NE, self.NR = model.num_entities, model.num_relations
+        self.B = int(batch_size)
+        self.lr, self.weight_decay = float(lr), float(weight_decay)
+        self.opt_kind = K.OPT_CODE[model.optimizer_name]
+        self.betas = (0.9, 0.9999) if self.opt_kind == 3 else (0.9, 0.999)
+        self.eps = 1e-6 if self.opt_kind == 3 else 1e-8
+        self.use_graph = use_graph
+        self.normalize = type(model).__name__ in ("QMult", "OMult")
+
+        # parameters (updated in place) and their optimiser state
+        self.E = model.entity_embeddings.weight.data
+        self.R = model.relation_embeddings.weight.data
+        assert self.E.is_cuda and self.E.is_contiguous() and self.E.dtype == torch.float32
+        self.coeff = None
+        self.coeff_trainable = False
+        if self.code == 4:
+            self.coeff = model.q_coefficients.weight.data
+            self.coeff_trainable = bool(model.q_coefficients.weight.requires_grad)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.E_bf16 = torch.empty(self.NE, self.D, dtype=torch.bfloat16, device=dev)
+        K.cast_bf16(self.E, self.E_bf16)
+        self.gE, self.gR = torch.zeros_like(self.E), torch.zeros_like(self.R)
+        self.mE, self.vE = torch.zeros_like(self.E), torch.zeros_like(self.E)
+        self.mR, self.vR = torch.zeros_like(self.R), torch.zeros_like(self.R)
+        if self.coeff is not None:
+            self.gC, self.mC, self.vC = (torch.zeros_like(self.coeff) for _ in range(3))
+        self.step_count = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.loss_acc = torch.zeros(1, dtype=torch.float64, device=dev)
+        self.loss_out = torch.zeros(1, **f32)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        # dataset: pairs, CSR of positives, label constants
+        self.dataset = dataset
+        dataset.sparse_labels = True
+        self.pairs = dataset.train_data.to(dev)
+        if hasattr(dataset, "offsets"):
+            self.offsets, self.values = dataset.offsets.to(dev).contiguous(), dataset.values.to(dev).contiguous()
+            pos, base = dataset.label_constants()
+        else:  # 1vsAll: one positive per data point
+            n = self.pairs.shape[0]
+            self.offsets = torch.arange(n + 1, dtype=torch.int64, device=dev)
+            self.values = self.pairs[:, 2].contiguous()
+            pos, base = 1.0, 0.0
+        self.pos_weight, self.base = float(pos - base), float(base)
+
+        self._bufs = {}
+        self._graphs = {}
+
+    # ------------------------------------------------------------------ buffers per batch size
+    def _buffers(self, n: int):
+        if n not in self._bufs:
+            dev = self.device
+            b = SimpleNamespace()
+            b.h = torch.zeros(n, dtype=torch.int64, device=dev)
+            b.r = torch.zeros(n, dtype=torch.int64, device=dev)
+            b.dp = torch.zeros(n, dtype=torch.int64, device=dev)
+            b.Q = torch.zeros(n, self.D, dtype=torch.bfloat16, device=dev)
+            b.dQ = torch.zeros(n, self.D, dtype=torch.float32, device=dev)
+            b.first = torch.zeros(n + 1, dtype=torch.int32, device=dev)
+            b.ent_tab = K.pointer_table([self.E], dev)
+            b.gent_tab = K.pointer_table([self.gE], dev)
+            b.q_tab = K.pointer_table([b.Q], dev)
+            self._bufs[n] = b
+        return self._bufs[n]
+
+    def _launch_all(self, b, n: int) -> None:
+        scale = 1.0 / (float(n) * float(self.NE))
+        K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,
+                         None, n, self.D, self.status)
+        K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True)
+        K.kvsall_fused(b.Q, self.E_bf16, b.dQ, None, self.status, self.base, scale, False)
+        K.positive_scan(b.dp, self.offsets, n, b.first)
+        K.positive_correction(b.dp, self.offsets, self.values, b.first, b.Q, self.E_bf16, b.dQ, self.gE, self.loss_acc,
+                              self.pos_weight, scale, n, self.D, 1, 0)
+        K.compose_backward(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.R, self.coeff, b.dQ, b.gent_tab,
+                           self.gR, self.gC if self.coeff_trainable else None, n, self.D)
+        b.dQ.zero_()
+        b1, b2 = self.betas
+        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, self.lr, b1,
+                         b2, self.eps, self.weight_decay)
+        K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, self.lr, b1, b2,
+                         self.eps, self.weight_decay)
+        if self.coeff_trainable:
+            K.optimizer_step(self.opt_kind, self.coeff, self.gC, self.mC, self.vC, None, self.step_count, self.lr, b1,
+                             b2, self.eps, self.weight_decay)
+        K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
+
+    #: number of kernels of this library launched per step (for launch accounting)
+    def launches_per_step(self) -> int:
+        return 10 + (1 if self.coeff_trainable else 0)
+
+    def _run(self, b, n: int) -> None:
+        key = (n, self.lr)
+        if not self.use_graph:
+            self._launch_all(b, n)
+            return
+        if key not in self._graphs:
+            # warm-up launch outside capture (sets function attributes), then capture
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            state = self._snapshot()
+            with torch.cuda.stream(s):
+                self._launch_all(b, n)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            K.check_status(self.status, "during fused-step warm-up")
+            self._restore(state)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch_all(b, n)
+            self._graphs = {k: v for k, v in self._graphs.items() if k[1] == self.lr}
+            self._graphs[key] = g
+        self._graphs[key].replay()
+
+    def _snapshot(self):
+        t = [self.E, self.R, self.E_bf16, self.mE, self.vE, self.mR, self.vR, self.gE, self.gR, self.step_count,
+             self.loss_acc]
+        if self.coeff is not None:
+            t += [self.coeff, self.gC, self.mC, self.vC]
+        return [(x, x.clone()) for x in t]
+
+    @staticmethod
+    def _restore(state):
+        for x, c in state:
+            x.copy_(c)
+
+    # ------------------------------------------------------------------ public
+    def step(self, batch) -> torch.Tensor:
+        """``batch = (x [n, 2] int64, data-point ids [n] int64)`` on the device; returns the loss (device scalar)."""
+        x, dp = batch[0], batch[1]
+        n = x.shape[0]
+        b = self._buffers(n)
+        b.h.copy_(x[:, 0])
+        b.r.copy_(x[:, 1])
+        b.dp.copy_(dp)
+        self._run(b, n)
+        return self.loss_out[0]
+
+    def step_from_host(self, x_pinned: torch.Tensor, dp_pinned: torch.Tensor) -> float:
+        """End-to-end step: asynchronous host→device copies of the (pinned) index tensors, the fused step, and a
+        device→host read of the loss."""
+        n = x_pinned.shape[0]
+        b = self._buffers(n)
+        if not hasattr(b, "x_in"):
+            b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=self.device)
+        b.x_in.copy_(x_pinned, non_blocking=True)
+        b.dp.copy_(dp_pinned, non_blocking=True)
+        b.h.copy_(b.x_in[:, 0])
+        b.r.copy_(b.x_in[:, 1])
+        self._run(b, n)
+        return float(self.loss_out.item())
+
+    def sync_to_model(self) -> None:
+        """Parameters are updated in place; only kernel failures need surfacing."""
+        K.check_status(self.status, "in fused training step")
+
+    def optimizer_view(self):
+        """Minimal optimiser façade (``param_groups[0]['lr']``) so LR-scheduling callbacks can steer the engine."""
+        return _EngineOptimizer(self)
+
+
+class _EngineOptimizer:
+    def __init__(self, engine: FusedKvsAllEngine):
+        self._e = engine
+        self.param_groups = [_LrGroup(engine)]
+        self.state = {}
+
+    def zero_grad(self, set_to_none: bool = True):
+        pass
+
+    def step(self):
+        pass
+
+    def state_dict(self):
+        e = self._e
+        return {"step": int(e.step_count.item()), "lr": e.lr}
+
+    def load_state_dict(self, sd):
+        self._e.lr = float(sd.get("lr", self._e.lr))
+
+
+class _LrGroup(dict):
+    def __init__(self, engine):
+        super().__init__(lr=engine.lr)
+        self._e = engine
+
+    def __setitem__(self, k, v):
+        super().__setitem__(k, v)
+        if k == "lr":
+            self._e.lr = float(v)

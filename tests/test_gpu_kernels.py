@@ -1,0 +1,164 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same ops."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("CUDA device required", allow_module_level=True)
+
+from dice_embeddings_b200.models import algebra
+from dice_embeddings_b200.ops import kernels as K
+
+DEV = torch.device("cuda:0")
+
+
+def _ref_fused(x, y, base, scale):
+    s = x.float() @ y.float().t()
+    loss = (torch.nn.functional.softplus(s) - base * s).double().sum()
+    ds = torch.sigmoid(s) - base
+    out = scale * (ds.to(torch.bfloat16).float() @ y.float())
+    return loss, out
+
+
+@pytest.mark.parametrize("nx,ny,D", [(128, 128, 64), (300, 200, 64), (257, 130, 128), (300, 520, 256), (1000, 777, 256)])
+@pytest.mark.parametrize("with_loss", [True, False])
+def test_kvsall_fused_matches_reference(nx, ny, D, with_loss):
+    torch.manual_seed(nx + ny + D)
+    x = (torch.randn(nx, D, device=DEV) * 0.3).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.3).to(torch.bfloat16)
+    base, scale = 0.01, 1.0 / 64
+    out = torch.zeros(nx, D, device=DEV)
+    loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.kvsall_fused(x, y, out, loss if with_loss else None, status, base, scale, with_loss)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    ref_loss, ref_out = _ref_fused(x, y, base, scale)
+    denom = ref_out.abs().max().clamp_min(1e-6)
+    assert (out - ref_out).abs().max() / denom < 2e-2
+    if with_loss:
+        assert abs(loss.item() - ref_loss.item()) / abs(ref_loss.item()) < 2e-3
+
+
+def test_kvsall_fused_accumulates_and_splits_work():
+    """Two launches add up; any CTA count gives the same sums (work ranges are arbitrary cuts of the tile grid)."""
+    torch.manual_seed(0)
+    nx, ny, D = 700, 900, 128
+    x = (torch.randn(nx, D, device=DEV) * 0.2).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.2).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = []
+    for ctas in (1, 7, 148):
+        out = torch.zeros(nx, D, device=DEV)
+        loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+        K.kvsall_fused(x, y, out, loss, status, 0.0, 1.0, True, num_ctas=ctas)
+        outs.append((out, loss.item()))
+    torch.cuda.synchronize()
+    K.check_status(status)
+    for o, l in outs[1:]:
+        assert (o - outs[0][0]).abs().max() < 1e-2 * outs[0][0].abs().max()
+        assert abs(l - outs[0][1]) < 1e-6 * abs(outs[0][1])
+
+
+@pytest.mark.parametrize("name,code,norm", [("DistMult", 0, False), ("ComplEx", 1, False), ("QMult", 2, True),
+                                             ("OMult", 3, True), ("Keci", 4, False)])
+def test_lookup_compose_and_backward(name, code, norm):
+    torch.manual_seed(1)
+    NE, NR, B, D = 500, 20, 333, 64
+    E = torch.randn(NE, D, device=DEV, requires_grad=True)
+    R = torch.randn(NR, D, device=DEV, requires_grad=True)
+    c = torch.tensor([[0.7]], device=DEV, requires_grad=True) if code == 4 else None
+    h = torch.randint(0, NE, (B,), device=DEV)
+    r = torch.randint(0, NR, (B,), device=DEV)
+    hv, rv = E[h], R[r]
+    if code == 0:
+        q = algebra.compose_distmult(hv, rv)
+    elif code == 1:
+        q = algebra.compose_complex(hv, rv)
+    elif code == 2:
+        q = algebra.compose_quaternion(hv, algebra.quaternion_normalizer(rv))
+    elif code == 3:
+        q = algebra.compose_octonion(hv, rv, True)
+    else:
+        q, _ = algebra.compose_clifford(hv, rv, D // 2, 0, 1, 0, None, c)
+    Q = torch.zeros(B, D, dtype=torch.bfloat16, device=DEV)
+    Qf = torch.zeros(B, D, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    Ed, Rd = E.detach().contiguous(), R.detach().contiguous()
+    ent_tab = K.pointer_table([Ed], DEV)
+    K.lookup_compose(code, norm, h, r, ent_tab, 1, NE, Rd, None if c is None else c.detach(), K.pointer_table([Q], DEV),
+                     1, 0, Qf, B, D, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    assert torch.allclose(Qf, q.detach(), atol=1e-4, rtol=1e-4)
+    assert torch.allclose(Q.float(), q.detach(), atol=3e-2, rtol=2e-2)
+    dq = torch.randn(B, D, device=DEV)
+    q.backward(dq)
+    gE, gR = torch.zeros_like(Ed), torch.zeros_like(Rd)
+    gC = torch.zeros(1, 1, device=DEV) if c is not None else None
+    K.compose_backward(code, norm, h, r, ent_tab, 1, Rd, None if c is None else c.detach(), dq, K.pointer_table([gE], DEV),
+                       gR, gC, B, D)
+    torch.cuda.synchronize()
+    assert torch.allclose(gE, E.grad, atol=2e-3, rtol=1e-3)
+    assert torch.allclose(gR, R.grad, atol=2e-3, rtol=1e-3)
+    if c is not None:
+        assert torch.allclose(gC, c.grad, atol=1e-2, rtol=1e-3)
+
+
+def test_positive_correction_matches_dense():
+    torch.manual_seed(2)
+    NE, B, D, P = 400, 96, 128, 300
+    q = (torch.randn(B, D, device=DEV) * 0.3).to(torch.bfloat16)
+    e = (torch.randn(NE, D, device=DEV) * 0.3).to(torch.bfloat16)
+    counts = torch.randint(0, 9, (P,))
+    counts[5] = 130  # one heavy data point spanning several chunks
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(DEV)
+    values = torch.cat([torch.randperm(NE)[:int(c)] for c in counts]).to(DEV)
+    dp = torch.randint(0, P, (B,), device=DEV)
+    dp[0] = 5
+    first = torch.zeros(B + 1, dtype=torch.int32, device=DEV)
+    K.positive_scan(dp, offsets, B, first)
+    dq, de = torch.zeros(B, D, device=DEV), torch.zeros(NE, D, device=DEV)
+    loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+    w, scale = 0.9, 1.0 / 37
+    K.positive_correction(dp, offsets, values, first, q, e, dq, de, loss, w, scale, B, D)
+    torch.cuda.synchronize()
+    Y = torch.zeros(B, NE, device=DEV)
+    for i in range(B):
+        d = int(dp[i])
+        Y[i, values[offsets[d]:offsets[d + 1]]] = 1.0
+    assert int(first[-1]) == int(Y.sum())
+    s = q.float() @ e.float().t()
+    assert abs(loss.item() + w * (Y * s).sum().item()) < 1e-3 * (1 + abs(loss.item()))
+    assert torch.allclose(dq, -w * scale * (Y @ e.float()), atol=1e-4, rtol=1e-3)
+    assert torch.allclose(de, -w * scale * (Y.t() @ q.float()), atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("kind,name", [(0, "Adam"), (1, "AdamW"), (2, "SGD"), (3, "Adopt")])
+def test_optimizer_kernels_match_torch(kind, name):
+    torch.manual_seed(3)
+    from dice_embeddings_b200.optim import ADOPT
+    n = 10_000
+    p_ref = torch.nn.Parameter(torch.randn(n, device=DEV))
+    p = p_ref.detach().clone()
+    wd = 0.01 if kind != 3 else 0.0
+    opt = {0: lambda: torch.optim.Adam([p_ref], lr=0.05, weight_decay=wd),
+           1: lambda: torch.optim.AdamW([p_ref], lr=0.05, weight_decay=wd),
+           2: lambda: torch.optim.SGD([p_ref], lr=0.05, weight_decay=wd),
+           3: lambda: ADOPT([p_ref], lr=0.05)}[kind]()
+    m, v, g = torch.zeros_like(p), torch.zeros_like(p), torch.zeros_like(p)
+    shadow = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+    step = torch.zeros(1, dtype=torch.int64, device=DEV)
+    b1, b2, eps = (0.9, 0.9999, 1e-6) if kind == 3 else (0.9, 0.999, 1e-8)
+    for _ in range(4):
+        grad = torch.randn(n, device=DEV)
+        p_ref.grad = grad.clone()
+        opt.step()
+        g.copy_(grad)
+        K.optimizer_step(kind, p, g, m, v, shadow, step, 0.05, b1, b2, eps, wd)
+        step += 1
+    torch.cuda.synchronize()
+    assert torch.allclose(p, p_ref.detach(), atol=1e-5, rtol=1e-4)
+    assert float(g.abs().max()) == 0.0
+    assert torch.allclose(shadow.float(), p, atol=2e-2, rtol=1e-2)
