@@ -95,6 +95,8 @@ struct LookupParams {
   int B, D, W, norm_mode;
   int* status;
   long long num_entities;
+  const long long* dp_src;       // optional: data-point ids of the batch, broadcast next to the queries
+  long long* const* dp_dst;      // [n_dst] destinations (row offset q_row_offset)
 };
 
 template <int K, int VEC>
@@ -110,6 +112,10 @@ __global__ void lookup_compose_kernel(const LookupParams p) {
   if (h < 0 || h >= p.num_entities) { atomicCAS(p.status, 0, ST_BAD_INDEX); return; }
   const float* hrow = p.ent[h % p.W] + (h / p.W) * p.D;
   const float* rrow = p.rel + r_id * p.D;
+  if (j0 == 0 && p.dp_src != nullptr) {
+    const long long d = p.dp_src[i];
+    for (int k = 0; k < p.n_dst; ++k) p.dp_dst[k][p.q_row_offset + i] = d;
+  }
   float hv[K][VEC], rv[K][VEC], rh[K][VEC], nrm[K][VEC];
   load_blocks<K, VEC>(hrow, w, j0, hv);
   load_blocks<K, VEC>(rrow, w, j0, rv);
@@ -283,12 +289,19 @@ struct PositiveParams {
   const __nv_bfloat16* q;      // [n, D]
   const __nv_bfloat16* e;      // local entity shard [rows_local, D], bf16 shadow
   float* dq;                   // [n, D] fp32, red.add
+  float* const* dq_table;      // optional: row i goes to dq_table[i / dq_block_rows] + (i % dq_block_rows) * D
+  int dq_block_rows;
   float* de;                   // [rows_local, D] fp32, red.add
   double* loss;
   float weight;                // label(positive) - label(elsewhere)
   float scale;                 // 1 / (B * |E|)
   int n, W, rank;
 };
+
+__device__ __forceinline__ float* dq_row(const PositiveParams& p, int i, int D) {
+  return p.dq_table != nullptr ? p.dq_table[i / p.dq_block_rows] + static_cast<long long>(i % p.dq_block_rows) * D
+                               : p.dq + static_cast<long long>(i) * D;
+}
 
 template <int D, int CHUNK>
 __global__ void positive_correction_kernel(const PositiveParams p) {
@@ -316,7 +329,7 @@ __global__ void positive_correction_kernel(const PositiveParams p) {
       while (p.first[i + 1] <= pp) {
         if (loaded == i) {
 #pragma unroll
-          for (int u = 0; u < PER; ++u) { atomicAdd(p.dq + static_cast<long long>(i) * D + lane * PER + u, acc[u]); acc[u] = 0.f; }
+          for (int u = 0; u < PER; ++u) { atomicAdd(dq_row(p, i, D) + lane * PER + u, acc[u]); acc[u] = 0.f; }
         }
         ++i;
       }
@@ -345,10 +358,33 @@ __global__ void positive_correction_kernel(const PositiveParams p) {
     }
     if (loaded == i) {
 #pragma unroll
-      for (int u = 0; u < PER; ++u) atomicAdd(p.dq + static_cast<long long>(i) * D + lane * PER + u, acc[u]);
+      for (int u = 0; u < PER; ++u) atomicAdd(dq_row(p, i, D) + lane * PER + u, acc[u]);
     }
   }
   if (lane == 0 && loss_local != 0.f) atomicAdd(p.loss, static_cast<double>(loss_local));
+}
+
+// Label bit masks for the fused scoring kernel.  One warp per batch item walks its slice of the CSR and sets
+//   mask_q[i][tail_local]   (rows = queries,  bit = local entity)   and
+//   mask_e[tail_local][i]   (rows = entities, bit = query),
+// keeping only tails owned by this rank.  Both masks are cleared by the caller before every batch.
+__global__ void build_label_masks_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
+                                         const long long* __restrict__ values, int n, int W, int rank,
+                                         unsigned int* __restrict__ mask_q, int stride_q,
+                                         unsigned int* __restrict__ mask_e, int stride_e) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  if (warp >= n) return;
+  const int i = static_cast<int>(warp);
+  const long long d = dp_idx[i];
+  const long long beg = offsets[d], end = offsets[d + 1];
+  for (long long q = beg + lane; q < end; q += 32) {
+    const long long j = values[q];
+    if (j % W != rank) continue;
+    const long long jl = j / W;
+    atomicOr(mask_q + static_cast<long long>(i) * stride_q + (jl >> 5), 1u << (jl & 31));
+    atomicOr(mask_e + jl * stride_e + (i >> 5), 1u << (i & 31));
+  }
 }
 
 // ------------------------------------------------------------------------------------ optimisers
@@ -362,48 +398,105 @@ struct OptParams {
   long long n;
   float lr, beta1, beta2, eps, weight_decay;
   int kind;                  // 0 Adam, 1 AdamW, 2 SGD, 3 ADOPT
+  const float* const* grad_table;  // optional: gradient = sum over n_grad buffers (one per rank, peer pointers):
+  int n_grad;                      // the all-reduce of replicated parameters folded into their update
 };
 
-__global__ void optimizer_kernel(const OptParams p) {
-  const long long t = *p.step + 1;
-  float bc1 = 1.f, bc2 = 1.f;
-  if (p.kind <= 1) {
-    bc1 = 1.f - powf(p.beta1, static_cast<float>(t));
-    bc2 = 1.f - powf(p.beta2, static_cast<float>(t));
+// One parameter element: returns the updated weight; m / v are updated in place (registers).
+__device__ __forceinline__ float opt_update(int kind, float w, float g, float& m, float& v, float lr, float beta1,
+                                            float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2,
+                                            float clip, bool first_step) {
+  if (kind == 0) {
+    g = fmaf(wd, w, g);
+    m = fmaf(beta1, m, (1.f - beta1) * g);
+    v = fmaf(beta2, v, (1.f - beta2) * g * g);
+    return w - lr * inv_bc1 * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
+  } else if (kind == 1) {
+    w *= 1.f - lr * wd;
+    m = fmaf(beta1, m, (1.f - beta1) * g);
+    v = fmaf(beta2, v, (1.f - beta2) * g * g);
+    return w - lr * inv_bc1 * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
+  } else if (kind == 2) {
+    g = fmaf(wd, w, g);
+    return w - lr * g;
   }
-  const float clip = powf(static_cast<float>(t - 1), 0.25f);  // ADOPT: clip bound of the current step index
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float w = p.param[i];
-    float g = p.grad[i];
-    p.grad[i] = 0.f;
-    if (p.kind == 0) {
-      g = fmaf(p.weight_decay, w, g);
-      const float m = p.m[i] = fmaf(p.beta1, p.m[i], (1.f - p.beta1) * g);
-      const float v = p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
-      w -= p.lr / bc1 * m / (sqrtf(v) / sqrtf(bc2) + p.eps);
-    } else if (p.kind == 1) {
-      w *= 1.f - p.lr * p.weight_decay;
-      const float m = p.m[i] = fmaf(p.beta1, p.m[i], (1.f - p.beta1) * g);
-      const float v = p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
-      w -= p.lr / bc1 * m / (sqrtf(v) / sqrtf(bc2) + p.eps);
-    } else if (p.kind == 2) {
-      g = fmaf(p.weight_decay, w, g);
-      w -= p.lr * g;
-    } else {  // ADOPT
-      g = fmaf(p.weight_decay, w, g);
-      if (t == 1) {
-        p.v[i] = g * g;
-      } else {
-        float ng = g / fmaxf(sqrtf(p.v[i]), p.eps);
-        ng = fminf(fmaxf(ng, -clip), clip);
-        const float m = p.m[i] = p.m[i] + (1.f - p.beta1) * (ng - p.m[i]);
-        w -= p.lr * m;
-        p.v[i] = fmaf(p.beta2, p.v[i], (1.f - p.beta2) * g * g);
+  g = fmaf(wd, w, g);  // ADOPT
+  if (first_step) {
+    v = g * g;
+    return w;
+  }
+  float ng = g / fmaxf(sqrtf(v), eps);
+  ng = fminf(fmaxf(ng, -clip), clip);
+  m = m + (1.f - beta1) * (ng - m);
+  v = fmaf(beta2, v, (1.f - beta2) * g * g);
+  return w - lr * m;
+}
+
+__global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
+  const long long t = *p.step + 1;
+  float inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
+  if (p.kind <= 1) {
+    inv_bc1 = 1.f / (1.f - exp2f(static_cast<float>(t) * log2f(p.beta1)));
+    inv_sqrt_bc2 = rsqrtf(1.f - exp2f(static_cast<float>(t) * log2f(p.beta2)));
+  }
+  const float clip = sqrtf(sqrtf(static_cast<float>(t - 1)));  // ADOPT: clip bound step^(1/4)
+  const bool first_step = (t == 1);
+  float* __restrict__ param = p.param;
+  float* __restrict__ grad = p.grad;
+  float* __restrict__ pm = p.m;
+  float* __restrict__ pv = p.v;
+  __nv_bfloat16* __restrict__ shadow = p.shadow;
+  const long long n4 = p.n >> 2;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(param) | reinterpret_cast<uintptr_t>(grad) |
+                         reinterpret_cast<uintptr_t>(pm) | reinterpret_cast<uintptr_t>(pv)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(shadow) & 7) == 0 && p.grad_table == nullptr;
+  long long done = 0;
+  if (aligned) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
+      float4 w = reinterpret_cast<float4*>(param)[i];
+      float4 g = reinterpret_cast<float4*>(grad)[i];
+      float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+      if (p.kind != 2) {
+        m = reinterpret_cast<float4*>(pm)[i];
+        v = reinterpret_cast<float4*>(pv)[i];
+      }
+      w.x = opt_update(p.kind, w.x, g.x, m.x, v.x, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.y = opt_update(p.kind, w.y, g.y, m.y, v.y, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.z = opt_update(p.kind, w.z, g.z, m.z, v.z, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.w = opt_update(p.kind, w.w, g.w, m.w, v.w, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      reinterpret_cast<float4*>(param)[i] = w;
+      reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.kind != 2) {
+        reinterpret_cast<float4*>(pm)[i] = m;
+        reinterpret_cast<float4*>(pv)[i] = v;
+      }
+      if (shadow != nullptr) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(shadow)[i] = pk;
       }
     }
-    p.param[i] = w;
-    if (p.shadow != nullptr) p.shadow[i] = __float2bfloat16_rn(w);
+    done = n4 << 2;
+  }
+  for (long long i = done + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n; i += stride) {
+    float w = param[i];
+    float g;
+    if (p.grad_table != nullptr) {
+      g = 0.f;
+      for (int k = 0; k < p.n_grad; ++k) g += p.grad_table[k][i];  // owners clear their buffer after the next barrier
+    } else {
+      g = grad[i];
+      grad[i] = 0.f;
+    }
+    float m = 0.f, v = 0.f;
+    if (p.kind != 2) { m = pm[i]; v = pv[i]; }
+    w = opt_update(p.kind, w, g, m, v, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+    param[i] = w;
+    if (p.kind != 2) { pm[i] = m; pv[i] = v; }
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(w);
   }
 }
 
@@ -414,10 +507,46 @@ __global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* _
 }
 
 // loss_out = acc * inv_count; acc = 0; step += 1   (one thread)
-__global__ void finish_step_kernel(double* acc, float* loss_out, double inv_count, long long* step) {
-  *loss_out = static_cast<float>(*acc * inv_count);
-  *acc = 0.0;
+// With acc_table the loss is the sum of every rank's accumulator (peer reads); each owner clears its own later.
+__global__ void finish_step_kernel(double* acc, float* loss_out, double inv_count, long long* step,
+                                   const double* const* acc_table, int n_acc) {
+  if (acc_table != nullptr) {
+    double s = 0.0;
+    for (int k = 0; k < n_acc; ++k) s += *acc_table[k];
+    *loss_out = static_cast<float>(s * inv_count);
+  } else {
+    *loss_out = static_cast<float>(*acc * inv_count);
+    *acc = 0.0;
+  }
   if (step != nullptr) *step += 1;
+}
+
+// Barrier across W ranks (one process per GPU) on per-rank signal arrays in peer-accessible memory.
+// Rank r adds 1 to slot r of every peer's array, then waits until every slot of its own array reaches the
+// number of barriers passed so far.  The wait is bounded; on a time-out the status word is set and the kernel
+// returns, so the host sees an error instead of a hang.
+__global__ void p2p_barrier_kernel(unsigned int* const* sig_table, int rank, int W, unsigned int* count, int* status,
+                                   unsigned int spin_limit) {
+  __shared__ unsigned int target;
+  if (threadIdx.x == 0) {
+    target = *count + 1;
+    *count = target;
+  }
+  __syncthreads();
+  const int peer = threadIdx.x;
+  if (peer < W) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(sig_table[peer] + rank) : "memory");
+    const unsigned int* mine = sig_table[rank] + peer;
+    unsigned int v = 0, it = 0;
+    for (; it < spin_limit; ++it) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int>(v - target) >= 0) break;
+      if (it > 64) __nanosleep(100);
+    }
+    if (it >= spin_limit) atomicCAS(status, 0, ST_TIMEOUT_PEER);
+    __threadfence_system();
+  }
 }
 
 template <int K, int VEC>
@@ -443,10 +572,11 @@ using namespace dice;
 extern "C" int dice_lookup_compose(int model, int normalize, const long long* idx_h, const long long* idx_r,
                                    const float* const* ent, int W, long long num_entities, const float* rel,
                                    const float* coeff, __nv_bfloat16* const* q_dst, int n_dst,
-                                   long long q_row_offset, float* q_f32, int B, int D, int* status, void* stream) {
+                                   long long q_row_offset, float* q_f32, int B, int D, int* status,
+                                   const long long* dp_src, long long* const* dp_dst, void* stream) {
   if (B <= 0) return 0;
   LookupParams p{idx_h, idx_r, ent, rel, nullptr, q_dst, q_f32, n_dst, q_row_offset, B, D, W, NORM_NONE, status,
-                 num_entities};
+                 num_entities, dp_src, dp_dst};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (model) {
     case 0: return launch_lookup<1, 1>(p, s);
@@ -475,6 +605,17 @@ extern "C" int dice_compose_backward(int model, int normalize, const long long* 
   }
 }
 
+extern "C" int dice_build_label_masks(const long long* dp_idx, const long long* offsets, const long long* values, int n,
+                                      int W, int rank, unsigned int* mask_q, int stride_q, unsigned int* mask_e,
+                                      int stride_e, void* stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const long long blocks = (static_cast<long long>(n) * 32 + threads - 1) / threads;
+  build_label_masks_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      dp_idx, offsets, values, n, W, rank, mask_q, stride_q, mask_e, stride_e);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 extern "C" int dice_positive_scan(const long long* dp_idx, const long long* offsets, int n, int* first, void* stream) {
   positive_scan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -483,10 +624,11 @@ extern "C" int dice_positive_scan(const long long* dp_idx, const long long* offs
 extern "C" int dice_positive_correction(const long long* dp_idx, const long long* offsets, const long long* values,
                                         const int* first, const void* q, const void* e, float* dq, float* de,
                                         double* loss, float weight, float scale, int n, int D, int W, int rank,
-                                        void* stream) {
+                                        float* const* dq_table, int dq_block_rows, void* stream) {
   if (n <= 0) return 0;
   PositiveParams p{dp_idx, offsets, values, first, static_cast<const __nv_bfloat16*>(q),
-                   static_cast<const __nv_bfloat16*>(e), dq, de, loss, weight, scale, n, W, rank};
+                   static_cast<const __nv_bfloat16*>(e), dq, dq_table, dq_block_rows > 0 ? dq_block_rows : 1, de, loss,
+                   weight, scale, n, W, rank};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int blocks = 148 * 4, threads = 256;
   switch (D) {
@@ -501,9 +643,10 @@ extern "C" int dice_positive_correction(const long long* dp_idx, const long long
 
 extern "C" int dice_optimizer_step(int kind, float* param, float* grad, float* m, float* v, void* shadow,
                                    const long long* step, long long n, float lr, float beta1, float beta2, float eps,
-                                   float weight_decay, void* stream) {
+                                   float weight_decay, const float* const* grad_table, int n_grad, void* stream) {
   if (n <= 0) return 0;
-  OptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), step, n, lr, beta1, beta2, eps, weight_decay, kind};
+  OptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), step, n, lr, beta1, beta2, eps, weight_decay, kind,
+              grad_table, n_grad};
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -520,7 +663,18 @@ extern "C" int dice_cast_bf16(const float* src, void* dst, long long n, void* st
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int dice_finish_step(double* acc, float* loss_out, double inv_count, long long* step, void* stream) {
-  finish_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(acc, loss_out, inv_count, step);
+extern "C" int dice_finish_step(double* acc, float* loss_out, double inv_count, long long* step,
+                                const double* const* acc_table, int n_acc, void* stream) {
+  finish_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(acc, loss_out, inv_count, step, acc_table, n_acc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// sig_table: device array of W pointers to each rank's unsigned[W] signal array; count: this rank's barrier counter.
+extern "C" int dice_p2p_barrier(unsigned int* const* sig_table, int rank, int W, unsigned int* count, int* status,
+                                unsigned int spin_limit, void* stream) {
+  if (W <= 1) return 0;
+  if (W > 64) return -6;
+  p2p_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(sig_table, rank, W, count, status,
+                                                                      spin_limit ? spin_limit : (1u << 24));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -9,8 +9,10 @@
 //
 // The [x_rows, y_rows] logit matrix is never materialised.  Calling it with X = entity shard, Y = queries gives
 // the entity-table gradient and the loss; calling it with X = queries, Y = entity shard gives the query gradient.
-// Positive labels enter through a separate sparse correction (see elementwise.cu), because
-// BCE(s, y) = softplus(s) − y·s splits into a dense label-free term and a term over the known tails only.
+// Positive labels enter in one of two ways: as a bit mask (one bit per (x, y) pair, built per batch from the CSR of
+// known tails; the epilogue then uses the full label) or, for tables too large for a mask, through a separate sparse
+// correction (see elementwise.cu), because BCE(s, y) = softplus(s) − y·s splits into a dense label-free term and a
+// term over the known tails only.
 //
 // Structure of a CTA (320 threads, one CTA per SM, persistent over a contiguous range of (x-tile, y-tile) pairs):
 //   warp 0      TMA producer: X tile once per segment, Y tiles through a ring of stages
@@ -34,12 +36,17 @@ constexpr int NUM_EPI_WARPS = 8;
 
 struct KvsAllParams {
   float* out;           // [x_rows, D] fp32, accumulated with red.add
+  float* const* out_table;  // optional: row x goes to out_table[x / out_block_rows] + (x % out_block_rows) * D, so
+  int out_block_rows;       // that blocks of rows can live on different GPUs (peer pointers): GEMM -> reduce-scatter
   double* loss;         // scalar accumulator (may be null when LOSS == false)
   int* status;          // 0 = ok, otherwise first failure code
   int x_rows, y_rows;   // valid row counts
   int nx_tiles, ny_tiles;
   float base;           // label value outside the positives (smoothing term)
   float scale;          // factor applied to out (1 / (B * |E|) for a mean-reduced loss)
+  const uint32_t* mask; // MASK: bit y of row x set where (x, y) is a positive label; row stride mask_stride words
+  int mask_stride;      // (a multiple of 4, so the two words a thread needs per tile are one aligned 8-byte load)
+  float pos_delta;      // label(positive) - base
 };
 
 template <int D>
@@ -71,7 +78,7 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
-template <int D, bool LOSS>
+template <int D, bool LOSS, bool MASK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
                     const KvsAllParams p) {
@@ -260,6 +267,12 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
       for (int t = 0; t < n; ++t, ++g) {
         const uint32_t b = g & 1;
+        uint2 mw = make_uint2(0u, 0u);
+        if constexpr (MASK) {
+          if (valid_x)
+            mw = *reinterpret_cast<const uint2*>(p.mask + static_cast<size_t>(x_global) * p.mask_stride +
+                                                 (y0 + t) * 4 + half * 2);
+        }
         if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const int y_valid = p.y_rows - (y0 + t) * BLOCK_Y;  // columns >= y_valid are padding
@@ -271,24 +284,27 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           tmem_ld32(s_addr + col0, r);
           tc_wait_ld();
           uint32_t packed[16];
+          const uint32_t mword = c == 0 ? mw.x : mw.y;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float ds2[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const float s = __uint_as_float(r[i + u]);
+              float label = p.base;
+              if constexpr (MASK) label = ((mword >> (i + u)) & 1u) ? p.base + p.pos_delta : p.base;
               float sig;
               if constexpr (LOSS) {
                 const float e = fast_ex2(-fabsf(s) * LOG2E);       // exp(-|s|)
                 const float inv = fast_rcp(1.f + e);               // sigmoid(|s|)
                 sig = s >= 0.f ? inv : e * inv;
-                float l = fmaxf(s, 0.f) + LN2 * fast_lg2(1.f + e) - p.base * s;
+                float l = fmaxf(s, 0.f) + LN2 * fast_lg2(1.f + e) - label * s;
                 if (col0 + i + u >= y_valid) l = 0.f;
                 seg_loss += l;
               } else {
                 sig = fmaf(fast_tanh(0.5f * s), 0.5f, 0.5f);
               }
-              float d = sig - p.base;
+              float d = sig - label;
               if (col0 + i + u >= y_valid) d = 0.f;
               ds2[u] = d;
             }
@@ -308,7 +324,12 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       // drain the accumulated out tile of this segment
       if (!mbar_wait_bounded(dx_full, seg & 1, s_abort)) { ok = false; break; }
       tc_fence_after();
-      float* out_row = p.out + static_cast<size_t>(x_global) * D;
+      float* out_row = p.out;
+      if (valid_x) {
+        out_row = (p.out_table != nullptr)
+                      ? p.out_table[x_global / p.out_block_rows] + static_cast<size_t>(x_global % p.out_block_rows) * D
+                      : p.out + static_cast<size_t>(x_global) * D;
+      }
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         const int col0 = half * (D / 2) + c * 32;
@@ -378,10 +399,10 @@ static int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, int 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int D, bool LOSS>
+template <int D, bool LOSS, bool MASK>
 static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllParams& p, int num_ctas,
                   cudaStream_t stream) {
-  auto kern = kvsall_fused_kernel<D, LOSS>;
+  auto kern = kvsall_fused_kernel<D, LOSS, MASK>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES) != cudaSuccess)
@@ -395,15 +416,17 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 }  // namespace dice
 
 // x, y: bf16 row-major with 16-byte aligned base; D in {64, 128, 256}.  out must be zero-initialised (or hold a
-// running sum) by the caller; *loss likewise.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
+// running sum) by the caller; *loss likewise.  With out_table != null (a device array of base pointers, one per
+// block of out_block_rows rows, possibly in peer memory) the result rows are scattered to their owners instead.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
 // launch; device-side failures are reported through *status.
 extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out,
                                  double* loss, float base, float scale, int with_loss, int* status, int num_ctas,
-                                 void* stream) {
+                                 float* const* out_table, int out_block_rows, const unsigned int* mask,
+                                 int mask_stride, float pos_delta, void* stream) {
   using namespace dice;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
-      (reinterpret_cast<uintptr_t>(out) & 15))
+      (out_table == nullptr && (reinterpret_cast<uintptr_t>(out) & 15)))
     return -5;
   CUtensorMap tx, ty;
   int rc = make_tmap_bf16(&tx, x, x_rows, D);
@@ -412,6 +435,8 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   if (rc) return rc;
   KvsAllParams p;
   p.out = out;
+  p.out_table = out_table;
+  p.out_block_rows = out_block_rows > 0 ? out_block_rows : 1;
   p.loss = loss;
   p.status = status;
   p.x_rows = x_rows;
@@ -420,6 +445,10 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.ny_tiles = (y_rows + BLOCK_Y - 1) / BLOCK_Y;
   p.base = base;
   p.scale = scale;
+  p.mask = mask;
+  p.mask_stride = mask_stride;
+  p.pos_delta = pos_delta;
+  if (mask != nullptr && ((mask_stride & 3) || (reinterpret_cast<uintptr_t>(mask) & 7))) return -5;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -430,10 +459,15 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   if (num_ctas > total) num_ctas = static_cast<int>(total);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool wl = with_loss != 0;
+  const bool mk = mask != nullptr;
+#define DICE_DISPATCH(DD)                                                                        \
+  case DD:                                                                                       \
+    if (wl) return mk ? launch<DD, true, true>(tx, ty, p, num_ctas, s) : launch<DD, true, false>(tx, ty, p, num_ctas, s); \
+    return mk ? launch<DD, false, true>(tx, ty, p, num_ctas, s) : launch<DD, false, false>(tx, ty, p, num_ctas, s);
   switch (D) {
-    case 256: return wl ? launch<256, true>(tx, ty, p, num_ctas, s) : launch<256, false>(tx, ty, p, num_ctas, s);
-    case 128: return wl ? launch<128, true>(tx, ty, p, num_ctas, s) : launch<128, false>(tx, ty, p, num_ctas, s);
-    case 64: return wl ? launch<64, true>(tx, ty, p, num_ctas, s) : launch<64, false>(tx, ty, p, num_ctas, s);
+    DICE_DISPATCH(256)
+    DICE_DISPATCH(128)
+    DICE_DISPATCH(64)
     default: return -6;
   }
 }

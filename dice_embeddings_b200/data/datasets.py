@@ -76,6 +76,15 @@ class BatchedDataset(torch.utils.data.Dataset):
                 break
             yield self.make_batch(idx, generator)
 
+    def dense_batch(self, idx: torch.Tensor, generator: Optional[torch.Generator] = None):
+        """``make_batch`` with dense labels even while a fused engine has switched the dataset to id-only batches."""
+        sparse = getattr(self, "sparse_labels", False)
+        self.sparse_labels = False
+        try:
+            return self.make_batch(idx, generator)
+        finally:
+            self.sparse_labels = sparse
+
     def num_batches(self, batch_size: int, world_size: int = 1) -> int:
         per = -(-len(self) // world_size)
         return -(-per // batch_size)

@@ -1,11 +1,13 @@
 """Fused single-GPU training step for bilinear models trained against all entities (KvsAll, AllvsAll, 1vsAll).
 
-One step is seven kernel launches replayed from a CUDA graph:
+One step is a short fixed sequence of kernel launches replayed from a CUDA graph:
 
 1. ``lookup_compose``      gather ``E[h]``, ``R[r]`` (fp32 masters), compose the query, write it as bf16
 2. ``kvsall_fused`` (E)    X = bf16 entity table, Y = queries  →  dense part of ``dE`` and of the loss
 3. ``kvsall_fused`` (Q)    X = queries, Y = entity table        →  dense part of ``dQ``
-4. ``positive_scan`` + ``positive_correction``   sparse label term from the CSR of known tails
+4. labels: either ``build_label_masks`` before 2–3 (bit masks of the batch's known tails in both orientations,
+   read by the scoring epilogue) or, for tables too large for masks, ``positive_scan`` + ``positive_correction``
+   after them (sparse label term from the CSR)
 5. ``compose_backward``    chain rule of the composition, row gradients scattered into ``dE`` / ``dR``
 6. ``optimizer_step`` ×k   Adam / AdamW / SGD / ADOPT over E (refreshing the bf16 shadow), R and the coefficient
 7. ``finish_step``         loss = accumulator / (B·|E|), accumulator = 0, step += 1
@@ -16,6 +18,7 @@ forward, ``BCEWithLogitsLoss``, backward, optimiser) never exist; labels are the
 """
 from __future__ import annotations
 
+import os
 from types import SimpleNamespace
 from typing import Optional, Tuple
 
@@ -66,7 +69,7 @@ def build_fused_engine(model, dataset, args, device, strict: bool = False):
 
 class FusedKvsAllEngine:
     def __init__(self, model, dataset, batch_size: int, lr: float, weight_decay: float = 0.0, device=None,
-                 use_graph: bool = True):
+                 use_graph: bool = True, label_mode: Optional[str] = None):
         self.model = model
         self.device = torch.device(device or model.device)
         self.code = fused_model_code(model)
@@ -79,7 +82,7 @@ class FusedKvsAllEngine:
         self.opt_kind = K.OPT_CODE[model.optimizer_name]
         self.betas = (0.9, 0.9999) if self.opt_kind == 3 else (0.9, 0.999)
         self.eps = 1e-6 if self.opt_kind == 3 else 1e-8
-        self.use_graph = use_graph
+        self.use_graph = use_graph and os.environ.get("DICE_B200_NO_GRAPH") != "1"
         self.normalize = type(model).__name__ in ("QMult", "OMult")
 
         # parameters (updated in place) and their optimiser state
@@ -118,6 +121,10 @@ class FusedKvsAllEngine:
             pos, base = 1.0, 0.0
         self.pos_weight, self.base = float(pos - base), float(base)
 
+        # labels reach the scoring kernel as bit masks while both orientations fit a modest budget, else through
+        # the sparse correction kernels
+        mask_bytes = 2 * self.B * self.NE / 8
+        self.label_mode = label_mode or ("mask" if mask_bytes <= (1 << 30) else "sparse")
         self._bufs = {}
         self._graphs = {}
 
@@ -135,6 +142,9 @@ class FusedKvsAllEngine:
             b.ent_tab = K.pointer_table([self.E], dev)
             b.gent_tab = K.pointer_table([self.gE], dev)
             b.q_tab = K.pointer_table([b.Q], dev)
+            if self.label_mode == "mask":
+                b.mask_q = torch.zeros(n, K.mask_stride(self.NE), dtype=torch.int32, device=dev)
+                b.mask_e = torch.zeros(self.NE, K.mask_stride(n), dtype=torch.int32, device=dev)
             self._bufs[n] = b
         return self._bufs[n]
 
@@ -142,11 +152,20 @@ class FusedKvsAllEngine:
         scale = 1.0 / (float(n) * float(self.NE))
         K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,
                          None, n, self.D, self.status)
-        K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True)
-        K.kvsall_fused(b.Q, self.E_bf16, b.dQ, None, self.status, self.base, scale, False)
-        K.positive_scan(b.dp, self.offsets, n, b.first)
-        K.positive_correction(b.dp, self.offsets, self.values, b.first, b.Q, self.E_bf16, b.dQ, self.gE, self.loss_acc,
-                              self.pos_weight, scale, n, self.D, 1, 0)
+        if self.label_mode == "mask":
+            b.mask_q.zero_()
+            b.mask_e.zero_()
+            K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e)
+            K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True,
+                           mask=b.mask_e, pos_delta=self.pos_weight)
+            K.kvsall_fused(b.Q, self.E_bf16, b.dQ, None, self.status, self.base, scale, False,
+                           mask=b.mask_q, pos_delta=self.pos_weight)
+        else:
+            K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True)
+            K.kvsall_fused(b.Q, self.E_bf16, b.dQ, None, self.status, self.base, scale, False)
+            K.positive_scan(b.dp, self.offsets, n, b.first)
+            K.positive_correction(b.dp, self.offsets, self.values, b.first, b.Q, self.E_bf16, b.dQ, self.gE,
+                                  self.loss_acc, self.pos_weight, scale, n, self.D, 1, 0)
         K.compose_backward(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.R, self.coeff, b.dQ, b.gent_tab,
                            self.gR, self.gC if self.coeff_trainable else None, n, self.D)
         b.dQ.zero_()
@@ -162,7 +181,7 @@ class FusedKvsAllEngine:
 
     #: number of kernels of this library launched per step (for launch accounting)
     def launches_per_step(self) -> int:
-        return 10 + (1 if self.coeff_trainable else 0)
+        return (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
 
     def _run(self, b, n: int) -> None:
         key = (n, self.lr)

@@ -47,28 +47,35 @@ def pointer_table(tensors: Sequence[torch.Tensor], device) -> torch.Tensor:
 
 
 def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: Optional[torch.Tensor],
-                 status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0) -> None:
+                 status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0,
+                 out_table: Optional[torch.Tensor] = None, out_block_rows: int = 0,
+                 mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0) -> None:
     """``out[x_rows, D] += scale · (sigmoid(X Yᵀ) − base) · Y`` and optionally
     ``loss_acc += Σ softplus(X Yᵀ) − base · X Yᵀ`` on the tcgen05 path.  ``x``/``y`` bf16, ``out`` fp32."""
     _req(x, torch.bfloat16, "x")
     _req(y, torch.bfloat16, "y")
-    _req(out, torch.float32, "out")
     D = x.shape[1]
-    assert y.shape[1] == D and out.shape[0] >= x.shape[0] and out.shape[1] == D
+    if out_table is None:
+        _req(out, torch.float32, "out")
+        assert out.shape[0] >= x.shape[0] and out.shape[1] == D
+    assert y.shape[1] == D
     if with_loss:
         _req(loss_acc, torch.float64, "loss_acc")
     rc = _lib.lib().dice_kvsall_fused(_ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
                                       float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas),
-                                      _stream())
+                                      _ptr(out_table), int(out_block_rows), _ptr(mask),
+                                      0 if mask is None else mask.shape[1], float(pos_delta), _stream())
     _check(rc, "dice_kvsall_fused")
 
 
 def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.Tensor, W: int, num_entities: int,
                    rel: torch.Tensor, coeff: Optional[torch.Tensor], q_dst_table: torch.Tensor, n_dst: int,
-                   q_row_offset: int, q_f32: Optional[torch.Tensor], B: int, D: int, status: torch.Tensor) -> None:
+                   q_row_offset: int, q_f32: Optional[torch.Tensor], B: int, D: int, status: torch.Tensor,
+                   dp_src: Optional[torch.Tensor] = None, dp_dst_table: Optional[torch.Tensor] = None) -> None:
     rc = _lib.lib().dice_lookup_compose(model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
                                         int(num_entities), _ptr(rel), _ptr(coeff), _ptr(q_dst_table), n_dst,
-                                        int(q_row_offset), _ptr(q_f32), B, D, _ptr(status), _stream())
+                                        int(q_row_offset), _ptr(q_f32), B, D, _ptr(status), _ptr(dp_src),
+                                        _ptr(dp_dst_table), _stream())
     _check(rc, "dice_lookup_compose")
 
 
@@ -80,22 +87,39 @@ def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: in
     _check(rc, "dice_compose_backward")
 
 
+def mask_stride(n_bits: int) -> int:
+    """Words per mask row: one bit per column, padded to a multiple of 4 words (and of the 128-column tile)."""
+    return ((n_bits + 127) // 128) * 4
+
+
+def build_label_masks(dp_idx, offsets, values, n: int, W: int, rank: int, mask_q: torch.Tensor,
+                      mask_e: torch.Tensor) -> None:
+    """Set the positive-label bits of a batch in both mask orientations (masks must be zeroed by the caller)."""
+    _req(mask_q, torch.int32, "mask_q")
+    _req(mask_e, torch.int32, "mask_e")
+    rc = _lib.lib().dice_build_label_masks(_ptr(dp_idx), _ptr(offsets), _ptr(values), n, W, rank, _ptr(mask_q),
+                                           mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], _stream())
+    _check(rc, "dice_build_label_masks")
+
+
 def positive_scan(dp_idx, offsets, n: int, first) -> None:
     _check(_lib.lib().dice_positive_scan(_ptr(dp_idx), _ptr(offsets), n, _ptr(first), _stream()), "dice_positive_scan")
 
 
 def positive_correction(dp_idx, offsets, values, first, q, e, dq, de, loss_acc, weight: float, scale: float, n: int,
-                        D: int, W: int = 1, rank: int = 0) -> None:
+                        D: int, W: int = 1, rank: int = 0, dq_table: Optional[torch.Tensor] = None,
+                        dq_block_rows: int = 0) -> None:
     rc = _lib.lib().dice_positive_correction(_ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), _ptr(q), _ptr(e),
                                              _ptr(dq), _ptr(de), _ptr(loss_acc), float(weight), float(scale), n, D, W,
-                                             rank, _stream())
+                                             rank, _ptr(dq_table), int(dq_block_rows), _stream())
     _check(rc, "dice_positive_correction")
 
 
-def optimizer_step(kind: int, param, grad, m, v, shadow, step, lr, beta1, beta2, eps, weight_decay) -> None:
+def optimizer_step(kind: int, param, grad, m, v, shadow, step, lr, beta1, beta2, eps, weight_decay,
+                   grad_table: Optional[torch.Tensor] = None, n_grad: int = 0) -> None:
     rc = _lib.lib().dice_optimizer_step(kind, _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow), _ptr(step),
                                         param.numel(), float(lr), float(beta1), float(beta2), float(eps),
-                                        float(weight_decay), _stream())
+                                        float(weight_decay), _ptr(grad_table), int(n_grad), _stream())
     _check(rc, "dice_optimizer_step")
 
 
@@ -103,9 +127,16 @@ def cast_bf16(src: torch.Tensor, dst: torch.Tensor) -> None:
     _check(_lib.lib().dice_cast_bf16(_ptr(src), _ptr(dst), src.numel(), _stream()), "dice_cast_bf16")
 
 
-def finish_step(acc, loss_out, inv_count: float, step) -> None:
-    _check(_lib.lib().dice_finish_step(_ptr(acc), _ptr(loss_out), float(inv_count), _ptr(step), _stream()),
-           "dice_finish_step")
+def finish_step(acc, loss_out, inv_count: float, step, acc_table: Optional[torch.Tensor] = None, n_acc: int = 0) -> None:
+    _check(_lib.lib().dice_finish_step(_ptr(acc), _ptr(loss_out), float(inv_count), _ptr(step), _ptr(acc_table),
+                                       int(n_acc), _stream()), "dice_finish_step")
+
+
+def p2p_barrier(sig_table: torch.Tensor, rank: int, world: int, count: torch.Tensor, status: torch.Tensor,
+                spin_limit: int = 0) -> None:
+    """Bounded device-side barrier over the ranks' signal arrays (see ``p2p_barrier_kernel``)."""
+    _check(_lib.lib().dice_p2p_barrier(_ptr(sig_table), rank, world, _ptr(count), _ptr(status), int(spin_limit),
+                                       _stream()), "dice_p2p_barrier")
 
 
 def check_status(status: torch.Tensor, where: str = "") -> None:

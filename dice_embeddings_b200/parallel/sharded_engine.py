@@ -1,0 +1,306 @@
+"""Row-sharded fused training step over several GPUs of one node (one process per GPU).
+
+Entity row ``e`` lives on rank ``e % W`` at local row ``e // W``; relations (and the Keci coefficient) are
+replicated.  With ``comm="p2p"`` every communication step of the reference-free design happens *inside* the
+kernels through peer pointers of a symmetric heap:
+
+====  =====================================================  ==================================================
+step  kernel                                                 traffic over NVLink
+====  =====================================================  ==================================================
+S0    ``p2p_barrier``                                        flags
+1     ``lookup_compose``: pull ``E[h]`` from the owner,       peer loads of rows; peer stores of bf16 query rows
+      compose, push the query row (+ data-point id) to         (the all-gather of Q)
+      every rank's ``Q`` buffer
+S1    ``p2p_barrier``
+2     ``build_label_masks`` + ``kvsall_fused`` (entity-       none (local shard × all queries)
+      stationary): loss and dense ``dE`` of the local shard
+3     ``kvsall_fused`` (query-stationary): ``dQ`` tiles are   peer ``red.add`` into the owner of each query block
+      reduced straight into the owning rank's buffer           (GEMM → reduce-scatter in one kernel)
+S2    ``p2p_barrier``
+4     ``compose_backward``: chain rule, row gradients          peer ``red.add`` into the owner's gradient shard
+S3    ``p2p_barrier``
+5     ``optimizer_step``: local shard; relations read every    peer loads (all-reduce folded into the update)
+      rank's gradient buffer; ``finish_step`` sums the losses
+====  =====================================================  ==================================================
+
+``comm="nccl"`` runs the same local kernels but moves data with ``torch.distributed`` collectives
+(all-gather, reduce-scatter, all-reduce); it is the comparison pipeline.  Buffers are never handed to library
+GEMMs as peer memory, and no load uses cluster multicast.
+"""
+from __future__ import annotations
+
+import os
+from types import SimpleNamespace
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+from ..ops.fused_step import fused_model_code
+from .symm import SymmetricHeap
+
+
+def owner_of(e: torch.Tensor, world: int) -> torch.Tensor:
+    return e % world
+
+
+def local_row(e: torch.Tensor, world: int) -> torch.Tensor:
+    return torch.div(e, world, rounding_mode="floor")
+
+
+def shard_rows(num_rows: int, rank: int, world: int) -> int:
+    """Number of valid rows of the cyclic shard of ``rank``."""
+    return (num_rows - rank + world - 1) // world if num_rows > rank else 0
+
+
+def take_shard(full: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    return full[rank::world]
+
+
+def scatter_shard_back(full: torch.Tensor, shard: torch.Tensor, rank: int, world: int) -> None:
+    full[rank::world] = shard[: shard_rows(full.shape[0], rank, world)]
+
+
+class ShardedKvsAllEngine:
+    def __init__(self, model, dataset, batch_size: int, lr: float, weight_decay: float = 0.0, device=None,
+                 comm: str = "p2p", group=None, use_graph: bool = True):
+        assert dist.is_initialized(), "ShardedKvsAllEngine needs an initialised process group"
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.W = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.model = model
+        self.device = dev = torch.device(device or model.device)
+        self.code = fused_model_code(model)
+        assert self.code is not None, "model is not covered by the fused kernels"
+        assert comm in ("p2p", "nccl")
+        self.comm = comm
+        self.D, self.NE, self.NR = model.embedding_dim, model.num_entities, model.num_relations
+        self.B = int(batch_size)
+        self.lr, self.weight_decay = float(lr), float(weight_decay)
+        self.opt_kind = K.OPT_CODE[model.optimizer_name]
+        self.betas = (0.9, 0.9999) if self.opt_kind == 3 else (0.9, 0.999)
+        self.eps = 1e-6 if self.opt_kind == 3 else 1e-8
+        self.normalize = type(model).__name__ in ("QMult", "OMult")
+        self.use_graph = use_graph and os.environ.get("DICE_B200_NO_GRAPH") != "1"
+        W, B, D = self.W, self.B, self.D
+        self.rows_pad = (self.NE + W - 1) // W
+        self.rows = shard_rows(self.NE, self.rank, W)
+
+        # every rank starts from rank 0's initial weights
+        with torch.no_grad():
+            for prm in model.parameters():
+                dist.broadcast(prm.data, src=dist.get_global_rank(self.group, 0), group=self.group)
+        self.coeff_trainable = self.code == 4 and bool(model.q_coefficients.weight.requires_grad)
+
+        heap = SymmetricHeap(self.group, dev)
+        heap.plan("E", (self.rows_pad, D), torch.float32)
+        heap.plan("gE", (self.rows_pad, D), torch.float32)
+        heap.plan("gR", (self.NR, D), torch.float32)
+        heap.plan("gC", (4,), torch.float32)
+        heap.plan("Q", (W * B, D), torch.bfloat16)
+        heap.plan("dQ", (B, D), torch.float32)
+        heap.plan("dp", (W * B,), torch.int64)
+        heap.plan("loss", (2,), torch.float64)
+        heap.plan("sig", (64,), torch.int32)
+        heap.commit()
+        self.heap = heap
+        self.E, self.gE, self.gR, self.gC = heap.local("E"), heap.local("gE"), heap.local("gR"), heap.local("gC")
+        self.Q, self.dQ, self.dp_all = heap.local("Q"), heap.local("dQ"), heap.local("dp")
+        self.loss_acc = heap.local("loss")
+        self.E[: self.rows].copy_(take_shard(model.entity_embeddings.weight.data, self.rank, W))
+        self.R = model.relation_embeddings.weight.data
+        self.coeff = model.q_coefficients.weight.data if self.code == 4 else None
+        self.E_bf16 = torch.zeros(self.rows_pad, D, dtype=torch.bfloat16, device=dev)
+        K.cast_bf16(self.E, self.E_bf16)
+        self.mE, self.vE = torch.zeros_like(self.E), torch.zeros_like(self.E)
+        self.mR, self.vR = torch.zeros_like(self.R), torch.zeros_like(self.R)
+        if self.coeff is not None:
+            self.mC, self.vC = torch.zeros_like(self.coeff), torch.zeros_like(self.coeff)
+        self.step_count = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.loss_out = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier_count = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        self.tab = SimpleNamespace(E=heap.table("E"), gE=heap.table("gE"), gR=heap.table("gR"), gC=heap.table("gC"),
+                                   Q=heap.table("Q"), dQ=heap.table("dQ"), dp=heap.table("dp"),
+                                   loss=heap.table("loss"), sig=heap.table("sig"))
+
+        # dataset (replicated): pairs and CSR of known tails
+        self.dataset = dataset
+        dataset.sparse_labels = True
+        self.pairs = dataset.train_data.to(dev)
+        if hasattr(dataset, "offsets"):
+            self.offsets, self.values = dataset.offsets.to(dev).contiguous(), dataset.values.to(dev).contiguous()
+            pos, base = dataset.label_constants()
+        else:
+            n = self.pairs.shape[0]
+            self.offsets = torch.arange(n + 1, dtype=torch.int64, device=dev)
+            self.values = self.pairs[:, 2].contiguous()
+            pos, base = 1.0, 0.0
+        self.pos_weight, self.base = float(pos - base), float(base)
+
+        self.h = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.r = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.dp = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.x_in = torch.zeros(B, 2, dtype=torch.int64, device=dev)
+        self.mask_q = torch.zeros(W * B, K.mask_stride(self.rows_pad), dtype=torch.int32, device=dev)
+        self.mask_e = torch.zeros(self.rows_pad, K.mask_stride(W * B), dtype=torch.int32, device=dev)
+        if comm == "nccl":
+            self._init_nccl_buffers()
+        self._graph = None
+        self._graph_lr = None
+        heap.host_barrier()
+
+    # ------------------------------------------------------------------ the step, peer-memory flavour
+    def _barrier(self) -> None:
+        K.p2p_barrier(self.tab.sig, self.rank, self.W, self.barrier_count, self.status)
+
+    def _optimizers_and_finish(self, scale: float, reduced: bool) -> None:
+        """``reduced``: replicated gradients / loss were already summed by a collective (nccl flavour)."""
+        b1, b2 = self.betas
+        a = (self.lr, b1, b2, self.eps, self.weight_decay)
+        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a)
+        if reduced:
+            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a)
+            if self.coeff_trainable:
+                K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a)
+            K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
+        else:
+            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a,
+                             grad_table=self.tab.gR, n_grad=self.W)
+            if self.coeff_trainable:
+                K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a,
+                                 grad_table=self.tab.gC, n_grad=self.W)
+            K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=self.W)
+
+    def _launch_p2p(self) -> None:
+        W, B, D, n = self.W, self.B, self.D, self.W * self.B
+        scale = 1.0 / (float(n) * float(self.NE))
+        self._barrier()                                   # S0: everyone finished the previous step
+        self.gR.zero_()
+        self.gC.zero_()
+        self.loss_acc.zero_()
+        self.mask_q.zero_()
+        self.mask_e.zero_()
+        K.lookup_compose(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.NE, self.R, self.coeff,
+                         self.tab.Q, W, self.rank * B, None, B, D, self.status, dp_src=self.dp, dp_dst_table=self.tab.dp)
+        self._barrier()                                   # S1: all query rows have landed everywhere
+        K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
+        e_loc = self.E_bf16[: self.rows]
+        K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
+                       mask=self.mask_e, pos_delta=self.pos_weight)
+        K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
+                       out_table=self.tab.dQ, out_block_rows=B, mask=self.mask_q, pos_delta=self.pos_weight)
+        self._barrier()                                   # S2: every rank's dQ block is complete
+        K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, self.dQ,
+                           self.tab.gE, self.gR, self.gC if self.coeff_trainable else None, B, D)
+        self.dQ.zero_()
+        self._barrier()                                   # S3: all row gradients reached their owners
+        self._optimizers_and_finish(scale, reduced=False)
+
+    def launches_per_step(self) -> int:
+        return 4 + 9 + (1 if self.coeff_trainable else 0) if self.comm == "p2p" else 9
+
+    # ------------------------------------------------------------------ the step, collective flavour
+    def _init_nccl_buffers(self) -> None:
+        dev, W, B, D = self.device, self.W, self.B, self.D
+        self.n_h_all = torch.zeros(W * B, dtype=torch.int64, device=dev)
+        self.n_rows_all = torch.zeros(W * B, D, dtype=torch.float32, device=dev)
+        self.n_hrows = torch.zeros(B, D, dtype=torch.float32, device=dev)
+        self.n_Q = torch.zeros(B, D, dtype=torch.bfloat16, device=dev)
+        self.n_Qall = torch.zeros(W * B, D, dtype=torch.bfloat16, device=dev)
+        self.n_dp_all = torch.zeros(W * B, dtype=torch.int64, device=dev)
+        self.n_dQall = torch.zeros(W * B, D, dtype=torch.float32, device=dev)
+        self.n_dQ = torch.zeros(B, D, dtype=torch.float32, device=dev)
+        self.n_dh = torch.zeros(B, D, dtype=torch.float32, device=dev)
+        self.n_dh_all = torch.zeros(W * B, D, dtype=torch.float32, device=dev)
+        self.n_arange = torch.arange(B, dtype=torch.int64, device=dev)
+        self.n_tab_h = K.pointer_table([self.n_hrows], dev)
+        self.n_tab_q = K.pointer_table([self.n_Q], dev)
+        self.n_tab_dh = K.pointer_table([self.n_dh], dev)
+
+    def _launch_nccl(self) -> None:
+        W, B, D, n, g = self.W, self.B, self.D, self.W * self.B, self.group
+        scale = 1.0 / (float(n) * float(self.NE))
+        # lookup: all-gather the head ids, every owner contributes its rows, reduce-scatter back
+        dist.all_gather_into_tensor(self.n_h_all, self.h, group=g)
+        dist.all_gather_into_tensor(self.n_dp_all, self.dp, group=g)
+        mine = (self.n_h_all % W) == self.rank
+        self.n_rows_all.zero_()
+        self.n_rows_all[mine] = self.E[torch.div(self.n_h_all[mine], W, rounding_mode="floor")]
+        dist.reduce_scatter_tensor(self.n_hrows, self.n_rows_all, group=g)
+        K.lookup_compose(self.code, self.normalize, self.n_arange, self.r, self.n_tab_h, 1, B, self.R, self.coeff,
+                         self.n_tab_q, 1, 0, None, B, D, self.status)
+        dist.all_gather_into_tensor(self.n_Qall, self.n_Q, group=g)
+        self.mask_q.zero_()
+        self.mask_e.zero_()
+        self.n_dQall.zero_()
+        K.build_label_masks(self.n_dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
+        e_loc = self.E_bf16[: self.rows]
+        K.kvsall_fused(e_loc, self.n_Qall, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
+                       mask=self.mask_e, pos_delta=self.pos_weight)
+        K.kvsall_fused(self.n_Qall, e_loc, self.n_dQall, None, self.status, self.base, scale, False,
+                       mask=self.mask_q, pos_delta=self.pos_weight)
+        dist.reduce_scatter_tensor(self.n_dQ, self.n_dQall, group=g)
+        self.n_dh.zero_()
+        K.compose_backward(self.code, self.normalize, self.n_arange, self.r, self.n_tab_h, 1, self.R, self.coeff,
+                           self.n_dQ, self.n_tab_dh, self.gR, self.gC if self.coeff_trainable else None, B, D)
+        dist.all_gather_into_tensor(self.n_dh_all, self.n_dh, group=g)
+        self.gE.index_add_(0, torch.div(self.n_h_all[mine], W, rounding_mode="floor"), self.n_dh_all[mine])
+        dist.all_reduce(self.gR, group=g)
+        dist.all_reduce(self.gC, group=g)
+        dist.all_reduce(self.loss_acc, group=g)
+        self._optimizers_and_finish(scale, reduced=True)
+
+    # ------------------------------------------------------------------ driving
+    def _run(self) -> None:
+        launch = self._launch_p2p if self.comm == "p2p" else self._launch_nccl
+        if not self.use_graph or self.comm == "nccl":
+            launch()
+            return
+        if self._graph is None or self._graph_lr != self.lr:
+            if self._graph is None and self._graph_lr is None:
+                # first call: plain launches (also sets kernel attributes); every rank does the same
+                launch()
+                self._graph_lr = -1.0
+                return
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                launch()
+            self._graph, self._graph_lr = g, self.lr
+        self._graph.replay()
+
+    def step(self, batch) -> torch.Tensor:
+        """``batch = (x [B, 2], data-point ids [B])`` of *this rank* on the device; returns the global mean loss."""
+        x, dp = batch[0], batch[1]
+        assert x.shape[0] == self.B, "the sharded step needs full batches of the configured size on every rank"
+        self.h.copy_(x[:, 0])
+        self.r.copy_(x[:, 1])
+        self.dp.copy_(dp)
+        self._run()
+        return self.loss_out[0]
+
+    def step_from_host(self, x_pinned: torch.Tensor, dp_pinned: torch.Tensor) -> float:
+        self.x_in.copy_(x_pinned, non_blocking=True)
+        self.dp.copy_(dp_pinned, non_blocking=True)
+        self.h.copy_(self.x_in[:, 0])
+        self.r.copy_(self.x_in[:, 1])
+        self._run()
+        return float(self.loss_out.item())
+
+    def check(self) -> None:
+        K.check_status(self.status, f"on rank {self.rank} of the sharded step")
+
+    @torch.no_grad()
+    def sync_to_model(self) -> None:
+        """Gather the shards into the model's full entity table on every rank (collective)."""
+        self.check()
+        shards = [torch.empty_like(self.E) for _ in range(self.W)]
+        dist.all_gather(shards, self.E.contiguous(), group=self.group)
+        full = self.model.entity_embeddings.weight.data
+        for r, s in enumerate(shards):
+            scatter_shard_back(full, s, r, self.W)
+
+    def optimizer_view(self):
+        from ..ops.fused_step import _EngineOptimizer
+        return _EngineOptimizer(self)
