@@ -678,3 +678,67 @@ extern "C" int dice_p2p_barrier(unsigned int* const* sig_table, int rank, int W,
                                                                       spin_limit ? spin_limit : (1u << 24));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ------------------------------------------------------------------------------------ allocation-free entry point
+// Sparse positive-label correction for callers that must not allocate device memory.
+//
+// dice_positive_scan + dice_positive_correction need an int[n + 1] prefix-sum buffer that the caller allocates.
+// Some callers cannot do that: code running inside a CUDA-graph capture or a stream-ordered region where
+// cudaMalloc is illegal or would synchronise the device, plug-ins living inside another framework's memory
+// budget (a serving process that has handed all free memory to its own pool), and hosts written in languages
+// whose binding layer has no allocator hooked up.  For them the prefix sums live in a fixed array inside the
+// library image instead.
+//
+// * Capacity: n <= DICE_NOALLOC_MAX_BATCH batch items; larger n is rejected with -7 and a message on stderr.
+// * The array (DICE_NOALLOC_MAX_BATCH + 1 ints, 256 KiB) is part of the loaded library: every GPU that loads
+//   the library carries it until the process exits.
+// * The first call on each device looks up the device address of the array (cudaGetSymbolAddress) with that
+//   device current and caches it; make that first call outside any stream capture.
+// * All calls share the one array and it keeps the previous call's contents.  Nothing in it has to start at zero
+//   (the scan overwrites entries 0..n before the correction kernel reads them), but two calls whose kernels
+//   overlap on the GPU (different streams, or different host threads on one device) race on it: serialise them.
+// * Neither this function nor the kernels it launches call cudaMalloc, cudaFree or any allocating routine.
+#include "dice_b200.h"
+
+#include <stdio.h>
+
+#include <mutex>
+
+namespace dice {
+static __device__ __align__(256) int g_noalloc_first[DICE_NOALLOC_MAX_BATCH + 1];
+static int* g_noalloc_first_addr[64] = {nullptr};
+static std::mutex g_noalloc_mutex;
+}  // namespace dice
+
+extern "C" int dice_positive_correction_noalloc(const long long* dp_idx, const long long* offsets,
+                                                const long long* values, const void* q, const void* e, float* dq,
+                                                float* de, double* loss, float weight, float scale, int n, int D,
+                                                int W, int rank, void* stream) {
+  if (n <= 0) return 0;
+  if (n > DICE_NOALLOC_MAX_BATCH) {
+    fprintf(stderr, "dice_positive_correction_noalloc: n = %d exceeds the built-in scratch capacity of %d batch items\n",
+            n, DICE_NOALLOC_MAX_BATCH);
+    return -7;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -8;
+  int* first = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_first_addr[dev] == nullptr) {
+      // In host code the array's name is only a handle; the kernels need its address on the current device.
+      void* addr = nullptr;
+      const cudaError_t rc = cudaGetSymbolAddress(&addr, g_noalloc_first);
+      if (rc != cudaSuccess || addr == nullptr) {
+        fprintf(stderr, "dice_positive_correction_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(rc));
+        return -9;
+      }
+      g_noalloc_first_addr[dev] = static_cast<int*>(addr);
+    }
+    first = g_noalloc_first_addr[dev];
+  }
+  int rc = dice_positive_scan(dp_idx, offsets, n, first, stream);
+  if (rc != 0) return rc;
+  return dice_positive_correction(dp_idx, offsets, values, first, q, e, dq, de, loss, weight, scale, n, D, W, rank,
+                                  nullptr, 0, stream);
+}
