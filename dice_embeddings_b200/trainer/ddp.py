@@ -1,0 +1,124 @@
+"""Data-parallel trainer: one process per device under ``torchrun`` (``--trainer torchDDP``).
+
+The reference wraps the model in ``DistributedDataParallel`` after ``torch.compile`` and hard-codes fp16 autocast
+(``dicee/trainer/torch_trainer_ddp.py:45-191``); every step all-reduces the dense gradient of the whole entity
+table.  Here the name selects, in this order:
+
+1. the row-sharded fused engine (:class:`ShardedKvsAllEngine`) when the model / scoring technique is covered and the
+   ranks run on B200s — no replicated table, no dense-table all-reduce;
+2. otherwise plain data parallelism: every rank holds a replica, processes its slice of each epoch and the
+   gradients are averaged with one flat all-reduce per step.  This path also runs on CPU ranks (Gloo), which is
+   how it is tested without GPUs.
+
+Callbacks fire on global rank 0 at epoch end, as in the reference (``:188-191``); the process group is left alive
+for the executor to tear down.
+"""
+from __future__ import annotations
+
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+from .base import AbstractTrainer, BatchLoader
+
+
+class TorchDDPTrainer(AbstractTrainer):
+    def __init__(self, args, callbacks=None):
+        super().__init__(args, callbacks)
+        if dist.is_initialized():
+            self.global_rank, self.world_size = dist.get_rank(), dist.get_world_size()
+        else:
+            self.global_rank, self.world_size = 0, 1
+        self.local_rank = int(os.environ.get("LOCAL_RANK", 0))
+        self.is_global_zero = self.global_rank == 0
+        if torch.cuda.is_available() and (not dist.is_initialized() or dist.get_backend() == "nccl"):
+            self.device = torch.device(f"cuda:{self.local_rank}")
+        else:
+            self.device = torch.device("cpu")
+        self.engine = None
+
+    # ------------------------------------------------------------------
+    def _maybe_sharded_engine(self, model, loader):
+        backend = getattr(self.attributes, "kernel_backend", "auto")
+        if backend == "torch" or self.device.type != "cuda" or self.world_size < 2:
+            return None
+        try:
+            from ..ops.fused_step import SUPPORTED_SCORING, fused_model_code
+            if fused_model_code(model) is None or self.attributes.scoring_technique not in SUPPORTED_SCORING \
+                    or torch.cuda.get_device_capability(self.device)[0] != 10:
+                if backend == "cuda":
+                    raise RuntimeError("kernel_backend=cuda requested but the model / scoring technique is not covered")
+                return None
+            from ..parallel.sharded_engine import ShardedKvsAllEngine
+            return ShardedKvsAllEngine(model, loader.dataset, batch_size=self.attributes.batch_size, lr=self.attributes.lr,
+                                       weight_decay=getattr(self.attributes, "weight_decay", 0.0) or 0.0,
+                                       device=self.device, comm=getattr(self.attributes, "comm", "p2p"))
+        except ImportError:
+            if backend == "cuda":
+                raise
+            return None
+
+    def _allreduce_grads(self, params) -> None:
+        grads = [p.grad for p in params if p.grad is not None]
+        if not grads or self.world_size == 1:
+            return
+        flat = torch._utils._flatten_dense_tensors(grads)
+        dist.all_reduce(flat)
+        flat.div_(self.world_size)
+        for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+            g.copy_(f)
+
+    def fit(self, *args, train_dataloaders, **kwargs) -> None:
+        model, = args
+        self.model = model
+        model.to(self.device)
+        loader = train_dataloaders
+        if isinstance(loader, BatchLoader):
+            loader.rank, loader.world_size = self.global_rank, self.world_size
+            loader.dataset.to(self.device)
+        if self.world_size > 1:  # identical start on every rank
+            for p in model.parameters():
+                dist.broadcast(p.data, src=0)
+        self.engine = self._maybe_sharded_engine(model, loader)
+        if self.engine is not None:
+            loader.drop_last = True
+        self.optimizer = self.engine.optimizer_view() if self.engine is not None else model.configure_optimizers()
+        params = [p for p in model.parameters() if p.requires_grad]
+        use_bf16 = getattr(self.attributes, "compute_dtype", "fp32") == "bf16" and self.device.type == "cuda"
+        if self.is_global_zero:
+            self.on_fit_start(self, model)
+        for epoch in range(self.attributes.num_epochs):
+            self.current_epoch = epoch
+            if hasattr(loader, "set_epoch"):
+                loader.set_epoch(epoch)
+            model.train()
+            total = torch.zeros((), device=self.device)
+            nb = 0
+            t0 = time.time()
+            for i, batch in enumerate(loader):
+                batch = tuple(b.to(self.device, non_blocking=True) if isinstance(b, torch.Tensor) else b for b in batch)
+                if self.engine is not None:
+                    loss = self.engine.step(batch)
+                else:
+                    self.optimizer.zero_grad(set_to_none=True)
+                    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=use_bf16):
+                        loss = model.training_step(batch)
+                    loss.backward()
+                    self._allreduce_grads(params)
+                    self.optimizer.step()
+                total += loss.detach()
+                nb += 1
+            if self.engine is None and self.world_size > 1:
+                dist.all_reduce(total)
+                total /= self.world_size
+            if self.engine is not None:
+                self.engine.sync_to_model()
+            epoch_loss = float(total) / max(nb, 1)
+            model.loss_history.append(epoch_loss)
+            if self.is_global_zero:
+                print(f"Epoch:{epoch + 1} | Loss:{epoch_loss:.8f} | Runtime:{(time.time() - t0) / 60:.3f}mins")
+                self.on_train_epoch_end(self, model)
+        if self.is_global_zero:
+            self.on_fit_end(self, model)
