@@ -185,6 +185,10 @@ class FusedKvsAllEngine:
 
     def _run(self, b, n: int) -> None:
         key = (n, self.lr)
+        if self.use_graph and key not in self._graphs and len({k[1] for k in self._graphs}) >= 3:
+            # the learning rate is a launch argument; a per-step schedule would re-capture every step
+            self.use_graph = False
+            self._graphs.clear()
         if not self.use_graph:
             self._launch_all(b, n)
             return
@@ -202,7 +206,6 @@ class FusedKvsAllEngine:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._launch_all(b, n)
-            self._graphs = {k: v for k, v in self._graphs.items() if k[1] == self.lr}
             self._graphs[key] = g
         self._graphs[key].replay()
 

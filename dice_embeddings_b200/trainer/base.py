@@ -111,6 +111,12 @@ class AbstractTrainer:
         for c in self.callbacks:
             c.on_train_epoch_end(*args, **kwargs)
 
+    def on_train_batch_start(self, *args, **kwargs):
+        for c in self.callbacks:
+            hook = getattr(c, "on_train_batch_start", None)
+            if hook is not None:
+                hook(*args, **kwargs)
+
     def on_train_batch_end(self, *args, **kwargs):
         for c in self.callbacks:
             c.on_train_batch_end(*args, **kwargs)

@@ -77,6 +77,7 @@ class TorchTrainer(AbstractTrainer):
             t0 = time.time()
             for i, batch in enumerate(train_dataloaders):
                 batch = _to_device(batch, self.device)
+                self.on_train_batch_start(self, self.model, batch, i)
                 if self.engine is not None:
                     loss = self.engine.step(batch)
                 else:
