@@ -367,7 +367,7 @@ class LRScheduler(AbstractCallback):
             name = f"snapshot_epoch_{trainer.current_epoch}.pt"
             torch.save({k: v.detach().cpu() for k, v in model.state_dict().items()}, os.path.join(self.snapshot_dir, name))
             loss = outputs["loss"] if isinstance(outputs, dict) else outputs
-            self.snapshot_loss[name] = float(loss) if loss is not None else 0.0
+            self.snapshot_loss[name] = float(loss.detach() if hasattr(loss, "detach") else loss) if loss is not None else 0.0
 
     def _calculate_snap_weights(self):
         import numpy as np
