@@ -149,6 +149,7 @@ class ShardedKvsAllEngine:
             self._init_nccl_buffers()
         self._graph = None
         self._graph_lr = None
+        self._phase_events = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
         heap.host_barrier()
 
     # ------------------------------------------------------------------ the step, peer-memory flavour
@@ -173,10 +174,31 @@ class ShardedKvsAllEngine:
                                  grad_table=self.tab.gC, n_grad=self.W)
             K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=self.W)
 
+    def _mark(self, name: str) -> None:
+        """Phase timing (enabled with ``DICE_B200_PHASE_TIMING=1`` together with ``DICE_B200_NO_GRAPH=1``): records a
+        CUDA event after each phase; :meth:`phase_times` returns the mean milliseconds per phase."""
+        if self._phase_events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._phase_events.append((name, e))
+
+    def phase_times(self):
+        torch.cuda.synchronize(self.device)
+        out, prev, last = {}, None, None
+        for name, e in self._phase_events or []:
+            if name == "start":
+                prev = e
+                continue
+            out.setdefault(name, []).append(prev.elapsed_time(e))
+            prev = e
+        return {k: sum(v) / len(v) for k, v in out.items()}
+
     def _launch_p2p(self) -> None:
         W, B, D, n = self.W, self.B, self.D, self.W * self.B
         scale = 1.0 / (float(n) * float(self.NE))
+        self._mark("start")
         self._barrier()                                   # S0: everyone finished the previous step
+        self._mark("S0")
         self.gR.zero_()
         self.gC.zero_()
         self.loss_acc.zero_()
@@ -184,19 +206,28 @@ class ShardedKvsAllEngine:
         self.mask_e.zero_()
         K.lookup_compose(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.NE, self.R, self.coeff,
                          self.tab.Q, W, self.rank * B, None, B, D, self.status, dp_src=self.dp, dp_dst_table=self.tab.dp)
+        self._mark("zero+lookup")
         self._barrier()                                   # S1: all query rows have landed everywhere
+        self._mark("S1")
         K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
+        self._mark("masks")
         e_loc = self.E_bf16[: self.rows]
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
                        mask=self.mask_e, pos_delta=self.pos_weight)
+        self._mark("fused_E")
         K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
                        out_table=self.tab.dQ, out_block_rows=B, mask=self.mask_q, pos_delta=self.pos_weight)
+        self._mark("fused_Q+rs")
         self._barrier()                                   # S2: every rank's dQ block is complete
+        self._mark("S2")
         K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, self.dQ,
                            self.tab.gE, self.gR, self.gC if self.coeff_trainable else None, B, D)
         self.dQ.zero_()
+        self._mark("compose_bwd")
         self._barrier()                                   # S3: all row gradients reached their owners
+        self._mark("S3")
         self._optimizers_and_finish(scale, reduced=False)
+        self._mark("optim")
 
     def launches_per_step(self) -> int:
         return 4 + 9 + (1 if self.coeff_trainable else 0) if self.comm == "p2p" else 9
