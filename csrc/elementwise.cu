@@ -97,6 +97,7 @@ struct LookupParams {
   long long num_entities;
   const long long* dp_src;       // optional: data-point ids of the batch, broadcast next to the queries
   long long* const* dp_dst;      // [n_dst] destinations (row offset q_row_offset)
+  int additive;                  // translation models: q = h + r instead of the algebra product
 };
 
 template <int K, int VEC>
@@ -132,6 +133,7 @@ __global__ void lookup_compose_kernel(const LookupParams p) {
       float q = 0.f;
 #pragma unroll
       for (int a = 0; a < K; ++a) q = fmaf(Alg<K>::sgn(k, a) * hv[a][u], rh[Alg<K>::idx(k, a)][u], q);
+      if (p.additive) q = hv[k][u] + rh[k][u];
       const long long col = k * w + j0 + u;
       const __nv_bfloat16 qb = __float2bfloat16_rn(q);
       for (int d = 0; d < p.n_dst; ++d) p.q_dst[d][(p.q_row_offset + i) * p.D + col] = qb;
@@ -151,6 +153,7 @@ struct ComposeBwdParams {
   float* g_rel;                // [R, D]
   float* g_coeff;              // single float or null
   int B, D, W, norm_mode;
+  int additive;
 };
 
 template <int K, int VEC>
@@ -191,6 +194,12 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
           dh[a][u] = fmaf(g, rh[Alg<K>::idx(k, a)][u], dh[a][u]);
           drh[Alg<K>::idx(k, a)][u] = fmaf(g, hv[a][u], drh[Alg<K>::idx(k, a)][u]);
         }
+    if (p.additive) {
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) { dh[a][u] = dq[a][u]; drh[a][u] = dq[a][u]; }
+    }
     if (p.coeff != nullptr) {
       // hv[K-1] = c * h_raw, rh[K-1] = c * r_raw  =>  d/dc collects both, raw grads pick up a factor c
 #pragma unroll
@@ -568,7 +577,7 @@ using namespace dice;
 
 // model: 0 DistMult, 1 ComplEx, 2 QMult (relation quaternion-normalised over consecutive 4-tuples when
 // normalize != 0), 3 OMult (relation normalised across its 8 blocks when normalize != 0), 4 Keci Cl(0,1) with
-// coefficient `coeff`.  ent / q_dst are *device* arrays of W / n_dst base pointers.
+// coefficient `coeff`, 5 translation (q = h + r).  ent / q_dst are *device* arrays of W / n_dst base pointers.
 extern "C" int dice_lookup_compose(int model, int normalize, const long long* idx_h, const long long* idx_r,
                                    const float* const* ent, int W, long long num_entities, const float* rel,
                                    const float* coeff, __nv_bfloat16* const* q_dst, int n_dst,
@@ -584,6 +593,7 @@ extern "C" int dice_lookup_compose(int model, int normalize, const long long* id
     case 2: if (D % 16) return -6; p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_lookup<4, 4>(p, s);
     case 3: if (D % 8) return -6; p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_lookup<8, 1>(p, s);
     case 4: if (D % 2) return -6; p.coeff = coeff; return launch_lookup<2, 1>(p, s);
+    case 5: p.additive = 1; return launch_lookup<1, 1>(p, s);
     default: return -6;
   }
 }
@@ -601,6 +611,7 @@ extern "C" int dice_compose_backward(int model, int normalize, const long long* 
     case 2: p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_bwd<4, 4>(p, s);
     case 3: p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_bwd<8, 1>(p, s);
     case 4: p.coeff = coeff; p.g_coeff = g_coeff; return launch_bwd<2, 1>(p, s);
+    case 5: p.additive = 1; return launch_bwd<1, 1>(p, s);
     default: return -6;
   }
 }

@@ -1,0 +1,252 @@
+// Kernels of the sampled-candidate training steps (negative sampling, 1vsSample, KvsSample):
+//
+//   dice_neg_sample      corrupted triples + labels generated on the device from a counter-based generator
+//   dice_uniform_int     uniform integers in [0, high)
+//   dice_candidate_bce   scores of each query against its own list of candidate entities, BCE-with-logits loss,
+//                        and the gradients w.r.t. the query vectors and the candidate rows, in one pass
+//
+// The query vectors come from dice_lookup_compose (any of its algebras) and their gradient goes back through
+// dice_compose_backward, so one scoring kernel serves every model of the bilinear family plus the translation model.
+#include "ptx_sm100.cuh"
+
+namespace dice {
+namespace triple {
+
+// ------------------------------------------------------------------------------------ Philox-4x32-10
+struct Philox {
+  uint32_t key[2];
+  __device__ __forceinline__ Philox(unsigned long long seed) {
+    key[0] = static_cast<uint32_t>(seed);
+    key[1] = static_cast<uint32_t>(seed >> 32);
+  }
+  __device__ __forceinline__ uint4 operator()(unsigned long long counter, unsigned long long stream) const {
+    uint32_t c0 = static_cast<uint32_t>(counter), c1 = static_cast<uint32_t>(counter >> 32);
+    uint32_t c2 = static_cast<uint32_t>(stream), c3 = static_cast<uint32_t>(stream >> 32);
+    uint32_t k0 = key[0], k1 = key[1];
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+      const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+      const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+      const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+      c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+    return make_uint4(c0, c1, c2, c3);
+  }
+};
+
+// Maps 64 random bits to [0, high) by the multiply-high reduction (bias below high / 2^64).
+__device__ __forceinline__ long long bounded(uint32_t a, uint32_t b, long long high) {
+  const unsigned long long x = (static_cast<unsigned long long>(a) << 32) | b;
+  return static_cast<long long>(__umul64hi(x, static_cast<unsigned long long>(high)));
+}
+
+__global__ void uniform_int_kernel(long long* __restrict__ out, long long n, long long high, unsigned long long seed,
+                                   unsigned long long offset) {
+  const Philox rng(seed);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; 2 * i < n; i += stride) {
+    const uint4 r = rng(static_cast<unsigned long long>(i), offset);
+    out[2 * i] = bounded(r.x, r.y, high);
+    if (2 * i + 1 < n) out[2 * i + 1] = bounded(r.z, r.w, high);
+  }
+}
+
+// Output layout: rows [0, B) are the positives, row B + j * B + i is the j-th corruption of positive i.
+// mode 0: one coin per call decides whether all heads or all tails are replaced; mode 1: one coin per negative.
+// step_ptr (optional) is added to offset on the device, so a captured launch draws new samples at every replay.
+__global__ void neg_sample_kernel(const long long* __restrict__ pos, int B, int k, long long num_entities,
+                                  unsigned long long seed, unsigned long long offset,
+                                  const long long* __restrict__ step_ptr, int mode, float label_pos, float label_neg,
+                                  long long* __restrict__ x, long long* __restrict__ h_out,
+                                  long long* __restrict__ r_out, long long* __restrict__ t_out,
+                                  float* __restrict__ y) {
+  const Philox rng(seed);
+  if (step_ptr != nullptr) offset += static_cast<unsigned long long>(*step_ptr);
+  const bool batch_heads = (rng(~0ull, offset).x & 1u) != 0u;
+  const long long total = static_cast<long long>(B) * (1 + k);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long n = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; n < total; n += stride) {
+    const int i = static_cast<int>(n % B);
+    long long h = pos[3 * i], r = pos[3 * i + 1], t = pos[3 * i + 2];
+    float label = label_pos;
+    if (n >= B) {
+      const uint4 u = rng(static_cast<unsigned long long>(n), offset);
+      const long long e = bounded(u.x, u.y, num_entities);
+      const bool heads = mode == 0 ? batch_heads : (u.z & 1u) != 0u;
+      if (heads) h = e; else t = e;
+      label = label_neg;
+    }
+    if (x != nullptr) {
+      x[3 * n] = h;
+      x[3 * n + 1] = r;
+      x[3 * n + 2] = t;
+    }
+    if (h_out != nullptr) {
+      h_out[n] = h;
+      r_out[n] = r;
+      t_out[n] = t;
+    }
+    y[n] = label;
+  }
+}
+
+// ------------------------------------------------------------------------------------ candidate scoring
+struct CandParams {
+  const float* q;             // [N, D] query vectors (fp32)
+  const long long* cand;      // candidate entity ids: entry (n, c) at cand[n * cand_stride + c * cand_step]
+  long long cand_stride, cand_step;
+  int C;                      // candidates per query
+  const float* labels;        // [N, C] targets in [0, 1]
+  const float* const* ent;    // [W] fp32 entity shards, entity e lives in shard e % W at row e / W
+  float* const* g_ent;        // [W] gradient shards (red.add); null = forward only
+  float* dq;                  // [N, D] gradient w.r.t. q (written, not accumulated); null = forward only
+  float* scores;              // [N, C] or null
+  double* loss;               // accumulator of sum(BCE) * scale, or null
+  float scale;                // 1 / (N * C) for a mean-reduced loss
+  float margin;               // distance kind: score = margin - ||q + eps - t||
+  float eps;
+  int N, D, W, kind;          // kind 0: dot product, 1: negative Euclidean distance
+};
+
+// One warp per query: the query stays in registers while its candidates stream through.
+template <int NV>  // float4 chunks per lane: D <= NV * 128
+__global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  double loss_local = 0.0;
+  for (int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; n < p.N; n += warps) {
+    float4 qv[NV], dqv[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int d = (v * 32 + lane) * 4;
+      qv[v] = d < p.D ? *reinterpret_cast<const float4*>(p.q + static_cast<size_t>(n) * p.D + d)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      dqv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int c = 0; c < p.C; ++c) {
+      const long long e = p.cand[n * p.cand_stride + c * p.cand_step];
+      const size_t row = static_cast<size_t>(e / p.W) * p.D;
+      const float* trow = p.ent[e % p.W] + row;
+      float4 tv[NV];
+      float acc = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int d = (v * 32 + lane) * 4;
+        if (d < p.D) {
+          tv[v] = *reinterpret_cast<const float4*>(trow + d);
+          if (p.kind == 0) {
+            acc = fmaf(qv[v].x, tv[v].x, acc); acc = fmaf(qv[v].y, tv[v].y, acc);
+            acc = fmaf(qv[v].z, tv[v].z, acc); acc = fmaf(qv[v].w, tv[v].w, acc);
+          } else {
+            const float a = qv[v].x + p.eps - tv[v].x, b = qv[v].y + p.eps - tv[v].y;
+            const float cc = qv[v].z + p.eps - tv[v].z, dd = qv[v].w + p.eps - tv[v].w;
+            acc += a * a + b * b + cc * cc + dd * dd;
+          }
+        } else {
+          tv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      float dist = 0.f;
+      float s = acc;
+      if (p.kind == 1) {
+        dist = sqrtf(acc);
+        s = p.margin - dist;
+      }
+      const size_t flat = static_cast<size_t>(n) * p.C + c;
+      if (lane == 0 && p.scores != nullptr) p.scores[flat] = s;
+      if (p.labels == nullptr) continue;
+      const float y = p.labels[flat];
+      if (lane == 0) loss_local += static_cast<double>(fmaxf(s, 0.f) - s * y + log1pf(expf(-fabsf(s))));
+      if (p.dq == nullptr) continue;
+      float g = (1.f / (1.f + expf(-s)) - y) * p.scale;  // dL/ds
+      float* grow = p.g_ent[e % p.W] + row;
+      if (p.kind == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int d = (v * 32 + lane) * 4;
+          if (d < p.D) {
+            dqv[v].x = fmaf(g, tv[v].x, dqv[v].x); dqv[v].y = fmaf(g, tv[v].y, dqv[v].y);
+            dqv[v].z = fmaf(g, tv[v].z, dqv[v].z); dqv[v].w = fmaf(g, tv[v].w, dqv[v].w);
+            red_add_v4(grow + d, g * qv[v].x, g * qv[v].y, g * qv[v].z, g * qv[v].w);
+          }
+        }
+      } else {
+        // s = margin - dist, d dist / d q = (q + eps - t) / dist
+        g = dist > 0.f ? -g / dist : 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int d = (v * 32 + lane) * 4;
+          if (d < p.D) {
+            const float a = g * (qv[v].x + p.eps - tv[v].x), b = g * (qv[v].y + p.eps - tv[v].y);
+            const float cc = g * (qv[v].z + p.eps - tv[v].z), dd = g * (qv[v].w + p.eps - tv[v].w);
+            dqv[v].x += a; dqv[v].y += b; dqv[v].z += cc; dqv[v].w += dd;
+            red_add_v4(grow + d, -a, -b, -cc, -dd);
+          }
+        }
+      }
+    }
+    if (p.dq != nullptr) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int d = (v * 32 + lane) * 4;
+        if (d < p.D) *reinterpret_cast<float4*>(p.dq + static_cast<size_t>(n) * p.D + d) = dqv[v];
+      }
+    }
+  }
+  if (p.loss != nullptr && lane == 0 && loss_local != 0.0) atomicAdd(p.loss, loss_local * p.scale);
+}
+
+}  // namespace triple
+}  // namespace dice
+
+extern "C" int dice_uniform_int(long long* out, long long n, long long high, unsigned long long seed,
+                                unsigned long long offset, void* stream) {
+  if (n <= 0) return 0;
+  if (high <= 0) return -6;
+  long long blocks = ((n + 1) / 2 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dice::triple::uniform_int_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      out, n, high, seed, offset);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// pos: [B, 3] int64 triples; outputs for N = B * (1 + k) rows: x [N, 3] (optional) and / or the columns h, r, t [N]
+// (optional, all three or none), y [N] fp32.  The same (seed, offset + *step_ptr) reproduces the same corruptions.
+extern "C" int dice_neg_sample(const long long* pos, int B, int k, long long num_entities, unsigned long long seed,
+                               unsigned long long offset, const long long* step_ptr, int mode, float label_pos,
+                               float label_neg, long long* x, long long* h, long long* r, long long* t, float* y,
+                               void* stream) {
+  if (B <= 0) return 0;
+  if (k < 0 || num_entities <= 0) return -6;
+  long long blocks = (static_cast<long long>(B) * (1 + k) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dice::triple::neg_sample_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos, B, k, num_entities, seed, offset, step_ptr, mode, label_pos, label_neg, x, h, r, t, y);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Scores query n against candidates cand[n * cand_stride + c * cand_step], c < C.  With labels it accumulates the
+// BCE-with-logits loss (times scale) and, when dq / g_ent are given, writes dq and adds the candidate-row gradients.
+// D must be a multiple of 4 and at most 512; q, dq and the entity shards must be 16-byte aligned.
+extern "C" int dice_candidate_bce(const float* q, const long long* cand, long long cand_stride, long long cand_step,
+                                  int C, const float* labels, const float* const* ent, float* const* g_ent, float* dq,
+                                  float* scores, double* loss, float scale, int kind, float margin, float eps, int N,
+                                  int D, int W, void* stream) {
+  using namespace dice::triple;
+  if (N <= 0 || C <= 0) return 0;
+  if (D % 4 || D > 512 || W <= 0) return -6;
+  if ((dq == nullptr) != (g_ent == nullptr)) return -6;
+  CandParams p{q, cand, cand_stride, cand_step, C, labels, ent, g_ent, dq, scores, loss, scale, margin, eps, N, D, W, kind};
+  const int threads = 256;
+  long long blocks = (static_cast<long long>(N) * 32 + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D <= 128) candidate_bce_kernel<1><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  else if (D <= 256) candidate_bce_kernel<2><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  else candidate_bce_kernel<4><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

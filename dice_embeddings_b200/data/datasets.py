@@ -222,6 +222,9 @@ class TriplePredictionDataset(BatchedDataset):
         self.neg_sample_ratio = int(neg_sample_ratio)
         self.label_smoothing_rate = float(label_smoothing_rate)
         self._generator = None
+        #: set by the fused training engine: batches then carry only the positives and the corruptions are drawn
+        #: by the device-side generator inside the step
+        self.defer_sampling = False
 
     def __len__(self):
         return int(self.train_set.shape[0])
@@ -251,6 +254,8 @@ class TriplePredictionDataset(BatchedDataset):
         return x, label
 
     def make_batch(self, idx, generator=None):
+        if self.defer_sampling:
+            return self.train_set[idx], None
         return self.corrupt(self.train_set[idx], generator)
 
 

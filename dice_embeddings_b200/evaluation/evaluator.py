@@ -123,7 +123,8 @@ class Evaluator:
         if form_of_labelling == "RelationPrediction":
             ranks = relation_ranks(model, triple_idx, self._ee(), bs)
         else:
-            ranks = tail_ranks(model, triple_idx, self.er_vocab, bs)
+            fused = False if getattr(self.args, "kernel_backend", "auto") == "torch" else None
+            ranks = tail_ranks(model, triple_idx, self.er_vocab, bs, fused=fused)
         assert ranks.numel() == len(triple_idx)
         res = metrics_from_ranks(ranks, divisor=len(triple_idx))
         if info and not self.during_training:

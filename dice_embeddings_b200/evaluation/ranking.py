@@ -69,12 +69,51 @@ def filter_coordinates(vocab, a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.T
     return _dict_filter(vocab, zip(a.tolist(), b.tolist()), a.device)
 
 
+def filter_csr(vocab, a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-query CSR ``(ptr [B+1] int64, cols int32)`` of the known answers of the pairs ``(a_i, b_i)``."""
+    rows, cols = filter_coordinates(vocab, a, b)
+    ptr = torch.zeros(a.shape[0] + 1, dtype=torch.int64, device=a.device)
+    if rows.numel():
+        ptr[1:] = torch.cumsum(torch.bincount(rows, minlength=a.shape[0]), 0)
+    return ptr, cols.to(torch.int32)
+
+
+def _use_fused(model, fused: Optional[bool]) -> bool:
+    if fused is False:
+        return False
+    from ..ops import eval_rank
+    ok = eval_rank.supports(model)
+    if fused and not ok:
+        raise RuntimeError("fused ranking requested but the model is not bilinear / not on a CUDA device / too wide")
+    return ok
+
+
 @torch.no_grad()
-def tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 1024, device=None) -> torch.Tensor:
-    """Filtered rank of the true tail among all entities for every ``(h, r, t)`` row."""
+def fused_tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 4096, ranker=None) -> torch.Tensor:
+    """:func:`tail_ranks` through the tcgen05 ranking kernel: no ``[B, |E|]`` score matrix, no sort.  Operands are
+    rounded to bf16 (fp32 accumulation), so ranks of near-tied entities can differ from the fp32 path."""
+    from ..ops import eval_rank
+    ranker = ranker or eval_rank.ranker_for_model(model)
+    dev = ranker.device
+    out = []
+    for i in range(0, triples.shape[0], batch_size):
+        b = triples[i:i + batch_size].to(dev)
+        q, _ = eval_rank.model_queries(model, b[:, :2])
+        ptr, cols = filter_csr(er_vocab, b[:, 0], b[:, 1])
+        out.append(ranker.ranks(q, b[:, 2], ptr, cols).cpu())
+    return torch.cat(out) if out else torch.zeros(0, dtype=torch.long)
+
+
+@torch.no_grad()
+def tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 1024, device=None,
+               fused: Optional[bool] = None) -> torch.Tensor:
+    """Filtered rank of the true tail among all entities for every ``(h, r, t)`` row.  ``fused``: ``None`` picks
+    the tcgen05 ranking kernel whenever the model supports it, ``False`` forces the PyTorch path."""
     device = device or getattr(model, "device", torch.device("cpu"))
     out = []
     triples = torch.as_tensor(np.asarray(triples)).long()
+    if _use_fused(model, fused):
+        return fused_tail_ranks(model, triples, er_vocab, max(batch_size, 1024))
     for i in range(0, triples.shape[0], batch_size):
         b = triples[i:i + batch_size].to(device)
         scores = model(b[:, :2])

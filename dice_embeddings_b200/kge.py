@@ -298,6 +298,23 @@ class KGE:
                 scores[i * width:j * width] = s.flatten().cpu()
         return (scores.flatten(), indices.flatten()) if return_indices else scores
 
+    @torch.no_grad()
+    def _fused_topk(self, pairs: torch.Tensor, topk: int, batch_size: int):
+        """Top-k tails through the tcgen05 ranking kernel (no ``[B, |E|]`` score matrix); ``None`` when the model is
+        outside what the kernel covers."""
+        from .ops import eval_rank
+        if not eval_rank.supports(self.model):
+            return None
+        ranker = eval_rank.ranker_for_model(self.model)  # rebuilt per call: the weights may have been trained since
+        dev = self.model.device
+        scores, indices = [], []
+        for i in range(0, pairs.shape[0], batch_size):
+            q, bias = eval_rank.model_queries(self.model, pairs[i:i + batch_size].to(dev))
+            s, ix = ranker.topk(q, topk)
+            scores.append((s if bias is None else s + bias.reshape(-1, 1)).cpu())
+            indices.append(ix.cpu())
+        return torch.cat(scores).flatten(), torch.cat(indices).flatten()
+
     def predict_missing_head_entity(self, relation: StrOrList, tail_entity: StrOrList, within=None,
                                     batch_size: int = 2, topk: int = 1, return_indices: bool = False):
         """Scores of every entity as head for each ``(tail, relation)`` of the Cartesian product.  When every
@@ -348,6 +365,10 @@ class KGE:
         pairs = torch.cartesian_prod(self._ent_ids(head_entity), self._rel_ids(relation))
         T = len(self.entity_to_idx)
         dev = self.model.device
+        if return_indices and topk <= 32 and dev.type == "cuda":
+            fused = self._fused_topk(pairs, topk, max(batch_size, 1024))
+            if fused is not None:
+                return fused
         return self._collect(pairs.shape[0], T, batch_size, topk, return_indices,
                              lambda i, j: self.model(pairs[i:j].to(dev)).view(j - i, T))
 

@@ -1,0 +1,153 @@
+"""Filtered ranking and top-k over an entity table without materialising the score matrix.
+
+``rank = 1 + #{j : s_j > s_target} − #{j ∈ known answers, j ≠ target : s_j > s_target}``: the dense count comes
+from the tcgen05 kernel ``dice_eval_rank`` (GEMM tiles in TMEM, counting epilogue), the target score and the
+filtered count from gather-dots (``dice_eval_sparse``).  With a process group every rank holds a row shard of the
+table (contiguous or cyclic); target scores, counts and top-k candidates are merged across ranks.
+
+The reference sorts a dense ``[B, |E|]`` matrix per batch (``dicee/evaluation/evaluator.py:484-508``) and uses
+``torch.topk`` over all scores for ``predict_topk`` (``dicee/knowledge_graph_embeddings.py:533-607``).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import kernels
+
+SUPPORTED_D = (64, 128, 256)
+
+
+def pad_dim(d: int) -> Optional[int]:
+    for s in SUPPORTED_D:
+        if d <= s:
+            return s
+    return None
+
+
+def to_kernel_operand(x: torch.Tensor, d_pad: int) -> torch.Tensor:
+    """bf16, contiguous, zero-padded to ``d_pad`` columns."""
+    x = x.detach()
+    if x.shape[1] == d_pad:
+        return x.to(torch.bfloat16).contiguous()
+    out = torch.zeros(x.shape[0], d_pad, dtype=torch.bfloat16, device=x.device)
+    out[:, :x.shape[1]] = x
+    return out
+
+
+class FusedRanker:
+    """Holds one (shard of an) entity table in kernel layout and answers rank / top-k queries against it.
+
+    ``table`` rows are entities ``y_offset + c * y_stride``; ``col_bias`` (fp32, per local row) is added to every
+    score of that entity.  ``group``: process group over which the table is sharded (``None`` = whole table here).
+    """
+
+    def __init__(self, table: torch.Tensor, col_bias: Optional[torch.Tensor] = None, y_offset: int = 0,
+                 y_stride: int = 1, group=None):
+        assert table.is_cuda, "the fused ranker runs on a CUDA device"
+        self.d = table.shape[1]
+        self.d_pad = pad_dim(self.d)
+        if self.d_pad is None:
+            raise ValueError(f"embedding width {self.d} exceeds the kernel's limit of {SUPPORTED_D[-1]}")
+        self.table = to_kernel_operand(table, self.d_pad)
+        self.col_bias = None if col_bias is None else col_bias.detach().float().contiguous()
+        self.y_offset, self.y_stride, self.group = int(y_offset), int(y_stride), group
+        self.device = table.device
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def _all_reduce(self, *tensors):
+        if self.group is not None:
+            import torch.distributed as dist
+            for t in tensors:
+                dist.all_reduce(t, group=self.group)
+
+    @torch.no_grad()
+    def ranks(self, q: torch.Tensor, target: torch.Tensor, filt_ptr: Optional[torch.Tensor] = None,
+              filt_cols: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Filtered ranks ``[B]`` (int64) of entity ``target[i]`` for query vector ``q[i]``.  The filter of query
+        ``i`` is ``filt_cols[filt_ptr[i]:filt_ptr[i+1]]`` (global entity ids; the target itself is ignored)."""
+        B = q.shape[0]
+        qk = to_kernel_operand(q, self.d_pad)
+        tgt_idx = target.to(torch.int32).contiguous()
+        tgt_score = torch.zeros(B, dtype=torch.float32, device=self.device)
+        greater = torch.zeros(B, dtype=torch.int32, device=self.device)
+        filtered = torch.zeros(B, dtype=torch.int32, device=self.device)
+        if filt_ptr is not None:
+            filt_ptr = filt_ptr.to(torch.int64).contiguous()
+            filt_cols = filt_cols.to(torch.int32).contiguous()
+        sharded = self.group is not None
+        if sharded:  # phase 1: owners score their targets, phase 2: everybody counts against the merged scores
+            kernels.eval_sparse(qk, self.table, tgt_idx, tgt_score, None, col_bias=self.col_bias,
+                                y_offset=self.y_offset, y_stride=self.y_stride)
+            self._all_reduce(tgt_score)
+            if filt_ptr is not None:
+                kernels.eval_sparse(qk, self.table, tgt_idx, None, filtered, filt_ptr, filt_cols,
+                                    col_bias=self.col_bias, target_in=tgt_score, y_offset=self.y_offset,
+                                    y_stride=self.y_stride)
+        else:
+            kernels.eval_sparse(qk, self.table, tgt_idx, tgt_score, filtered if filt_ptr is not None else None,
+                                filt_ptr, filt_cols, col_bias=self.col_bias)
+        kernels.eval_rank(qk, self.table, tgt_score, tgt_idx, greater, self.status, col_bias=self.col_bias,
+                          y_offset=self.y_offset, y_stride=self.y_stride)
+        if sharded:
+            self._all_reduce(greater, filtered)
+        kernels.check_status(self.status, "in dice_eval_rank")
+        return (1 + greater - filtered).long()
+
+    @torch.no_grad()
+    def topk(self, q: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``(scores [B, k], entity ids [B, k])`` of the best entities per query, best first."""
+        B = q.shape[0]
+        n_local = self.table.shape[0]
+        qk = to_kernel_operand(q, self.d_pad)
+        if k > 32:  # beyond the in-kernel list: plain matmul in slices (rare; interactive use)
+            s = qk.float() @ self.table.float().t()
+            if self.col_bias is not None:
+                s = s + self.col_bias
+            sc, ix = torch.topk(s, min(k, n_local), dim=1)
+            ix = ix * self.y_stride + self.y_offset
+        else:
+            kk = min(k, n_local)
+            cap = kernels.eval_rank_cand_cap(B, n_local, kk)
+            cs = torch.full((B, cap), float("-inf"), dtype=torch.float32, device=self.device)
+            ci = torch.full((B, cap), -1, dtype=torch.int32, device=self.device)
+            cc = torch.zeros(B, dtype=torch.int32, device=self.device)
+            kernels.eval_rank(qk, self.table, None, None, None, self.status, col_bias=self.col_bias,
+                              y_offset=self.y_offset, y_stride=self.y_stride, k=kk, cand_score=cs, cand_idx=ci,
+                              cand_count=cc)
+            kernels.check_status(self.status, "in dice_eval_rank (top-k)")
+            sc, pos = torch.topk(cs, kk, dim=1)
+            ix = torch.gather(ci, 1, pos).long()
+        if self.group is not None:
+            import torch.distributed as dist
+            W = dist.get_world_size(self.group)
+            all_s = [torch.empty_like(sc) for _ in range(W)]
+            all_i = [torch.empty_like(ix) for _ in range(W)]
+            dist.all_gather(all_s, sc.contiguous(), group=self.group)
+            dist.all_gather(all_i, ix.contiguous(), group=self.group)
+            cat_s, cat_i = torch.cat(all_s, 1), torch.cat(all_i, 1)
+            sc, pos = torch.topk(cat_s, min(k, cat_s.shape[1]), dim=1)
+            ix = torch.gather(cat_i, 1, pos)
+        return sc, ix
+
+
+def supports(model) -> bool:
+    """True when ``model`` can be ranked by the fused path: bilinear contract, CUDA parameters, width ≤ 256."""
+    try:
+        w = model.entity_embeddings.weight
+    except AttributeError:
+        return False
+    return bool(getattr(model, "bilinear", False)) and w.is_cuda and pad_dim(w.shape[1]) is not None \
+        and kernels._lib.available()
+
+
+def ranker_for_model(model) -> FusedRanker:
+    return FusedRanker(model.entity_embeddings.weight)
+
+
+@torch.no_grad()
+def model_queries(model, hr: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``(q, bias)`` of the model's bilinear form for index pairs ``hr [B, 2]``."""
+    h, r = model.get_head_relation_representation(hr)
+    return model.compose(h, r)

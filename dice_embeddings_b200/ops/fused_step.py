@@ -34,7 +34,7 @@ SUPPORTED_SCORING = ("KvsAll", "AllvsAll", "1vsAll")
 def fused_model_code(model) -> Optional[int]:
     """Kernel model code, or ``None`` when the model is outside what the fused path covers."""
     name = type(model).__name__
-    if name not in K.MODEL_CODE:
+    if name not in K.MODEL_CODE or name == "TransE":  # the translation model is not a dot product against E
         return None
     if name in ("Keci", "CKeci") and not (model.p == 0 and model.q == 1):
         return None

@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-MODEL_CODE = {"DistMult": 0, "ComplEx": 1, "QMult": 2, "OMult": 3, "Keci": 4, "CKeci": 4}
+MODEL_CODE = {"DistMult": 0, "ComplEx": 1, "QMult": 2, "OMult": 3, "Keci": 4, "CKeci": 4, "TransE": 5}
 OPT_CODE = {"Adam": 0, "AdamW": 1, "SGD": 2, "Adopt": 3}
 
 STATUS_TEXT = {0: "ok", 1: "producer wait timed out", 2: "mma wait timed out", 3: "epilogue wait timed out",
@@ -137,6 +137,116 @@ def p2p_barrier(sig_table: torch.Tensor, rank: int, world: int, count: torch.Ten
     """Bounded device-side barrier over the ranks' signal arrays (see ``p2p_barrier_kernel``)."""
     _check(_lib.lib().dice_p2p_barrier(_ptr(sig_table), rank, world, _ptr(count), _ptr(status), int(spin_limit),
                                        _stream()), "dice_p2p_barrier")
+
+
+def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0) -> None:
+    """Fill ``out`` (int64) with uniform integers in ``[0, high)`` from the counter-based generator."""
+    _req(out, torch.int64, "out")
+    _check(_lib.lib().dice_uniform_int(_ptr(out), out.numel(), int(high), int(seed) & (2 ** 64 - 1),
+                                       int(offset) & (2 ** 64 - 1), _stream()), "dice_uniform_int")
+
+
+def neg_sample(pos: torch.Tensor, k: int, num_entities: int, seed: int, offset: int, y: torch.Tensor,
+               x: Optional[torch.Tensor] = None, hrt: Optional[Sequence[torch.Tensor]] = None,
+               label_pos: float = 1.0, label_neg: float = 0.0, per_negative_coin: bool = False,
+               step: Optional[torch.Tensor] = None) -> None:
+    """Row ``i < B`` of the output is ``pos[i]``; row ``B + j·B + i`` is the j-th corruption of ``pos[i]`` (head or
+    tail replaced by a uniform entity).  Written as ``x [N, 3]`` and / or three column tensors ``hrt``; ``y`` gets
+    the labels.  ``step`` (device int64 scalar) is added to ``offset`` on the device."""
+    _req(pos, torch.int64, "pos")
+    _req(y, torch.float32, "y")
+    B = pos.shape[0]
+    N = B * (1 + k)
+    assert y.numel() >= N
+    if x is not None:
+        _req(x, torch.int64, "x")
+        assert x.shape[0] >= N
+    h = r = t = None
+    if hrt is not None:
+        h, r, t = hrt
+        for c in (h, r, t):
+            _req(c, torch.int64, "hrt")
+            assert c.numel() >= N
+    _check(_lib.lib().dice_neg_sample(_ptr(pos), B, int(k), int(num_entities), int(seed) & (2 ** 64 - 1),
+                                      int(offset) & (2 ** 64 - 1), _ptr(step), int(per_negative_coin),
+                                      float(label_pos), float(label_neg), _ptr(x), _ptr(h), _ptr(r), _ptr(t),
+                                      _ptr(y), _stream()), "dice_neg_sample")
+
+
+def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_step: int, C: int,
+                  labels: Optional[torch.Tensor], ent_table: torch.Tensor, W: int,
+                  g_ent_table: Optional[torch.Tensor] = None, dq: Optional[torch.Tensor] = None,
+                  scores: Optional[torch.Tensor] = None, loss_acc: Optional[torch.Tensor] = None,
+                  scale: float = 1.0, kind: int = 0, margin: float = 0.0, eps: float = 0.0) -> None:
+    """Scores of every query against its own candidate list, BCE loss and gradients (see ``dice_candidate_bce``)."""
+    _req(q, torch.float32, "q")
+    _req(cand, torch.int64, "cand")
+    if labels is not None:
+        _req(labels, torch.float32, "labels")
+    if dq is not None:
+        _req(dq, torch.float32, "dq")
+    if loss_acc is not None:
+        _req(loss_acc, torch.float64, "loss_acc")
+    N, D = q.shape
+    _check(_lib.lib().dice_candidate_bce(_ptr(q), _ptr(cand), int(cand_stride), int(cand_step), int(C), _ptr(labels),
+                                         _ptr(ent_table), _ptr(g_ent_table), _ptr(dq), _ptr(scores), _ptr(loss_acc),
+                                         float(scale), int(kind), float(margin), float(eps), N, D, int(W),
+                                         _stream()), "dice_candidate_bce")
+
+
+def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], target_idx: Optional[torch.Tensor],
+              greater: Optional[torch.Tensor], status: torch.Tensor, col_bias: Optional[torch.Tensor] = None,
+              y_offset: int = 0, y_stride: int = 1, k: int = 0, cand_score: Optional[torch.Tensor] = None,
+              cand_idx: Optional[torch.Tensor] = None, cand_count: Optional[torch.Tensor] = None,
+              num_ctas: int = 0) -> None:
+    """``greater[i] += #{c : (x_i · y_c + col_bias[c]) > target[i], c != column of target_idx[i]}`` on the tcgen05
+    path, plus per-segment top-``k`` candidates appended to ``cand_*`` when ``k > 0``.  Nothing of the score matrix
+    is written to memory."""
+    _req(x, torch.bfloat16, "x")
+    _req(y, torch.bfloat16, "y")
+    assert x.shape[1] == y.shape[1]
+    if target is not None:
+        _req(target, torch.float32, "target")
+    if target_idx is not None:
+        _req(target_idx, torch.int32, "target_idx")
+    if greater is not None:
+        _req(greater, torch.int32, "greater")
+    if col_bias is not None:
+        _req(col_bias, torch.float32, "col_bias")
+    cap = 0
+    if k > 0:
+        _req(cand_score, torch.float32, "cand_score")
+        _req(cand_idx, torch.int32, "cand_idx")
+        _req(cand_count, torch.int32, "cand_count")
+        cap = cand_score.shape[1]
+    rc = _lib.lib().dice_eval_rank(_ptr(x), x.shape[0], _ptr(y), y.shape[0], x.shape[1], _ptr(target),
+                                   _ptr(target_idx), _ptr(col_bias), int(y_offset), int(y_stride), _ptr(greater),
+                                   int(k), int(cap), _ptr(cand_score), _ptr(cand_idx), _ptr(cand_count),
+                                   _ptr(status), int(num_ctas), _stream())
+    _check(rc, "dice_eval_rank")
+
+
+def eval_rank_cand_cap(x_rows: int, y_rows: int, k: int, num_ctas: int = 0) -> int:
+    return int(_lib.lib().dice_eval_rank_cand_cap(int(x_rows), int(y_rows), int(k), int(num_ctas)))
+
+
+def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, target_score: Optional[torch.Tensor],
+                filtered_greater: Optional[torch.Tensor], filt_ptr: Optional[torch.Tensor] = None,
+                filt_cols: Optional[torch.Tensor] = None, col_bias: Optional[torch.Tensor] = None,
+                target_in: Optional[torch.Tensor] = None, y_offset: int = 0, y_stride: int = 1) -> None:
+    """Gather-dots of the ranking protocol: the target score of each query and the number of filtered entities (CSR
+    ``filt_ptr`` int64 / ``filt_cols`` int32) that beat it."""
+    _req(q, torch.bfloat16, "q")
+    _req(y, torch.bfloat16, "y")
+    _req(target_idx, torch.int32, "target_idx")
+    if filt_ptr is not None:
+        _req(filt_ptr, torch.int64, "filt_ptr")
+        _req(filt_cols, torch.int32, "filt_cols")
+    rc = _lib.lib().dice_eval_sparse(_ptr(q), _ptr(y), q.shape[0], q.shape[1], y.shape[0], int(y_offset),
+                                     int(y_stride), _ptr(target_idx), _ptr(col_bias), _ptr(target_in),
+                                     _ptr(filt_ptr), _ptr(filt_cols), _ptr(target_score), _ptr(filtered_greater),
+                                     _stream())
+    _check(rc, "dice_eval_sparse")
 
 
 def check_status(status: torch.Tensor, where: str = "") -> None:

@@ -45,12 +45,15 @@ class TorchTrainer(AbstractTrainer):
             return None
         try:
             from ..ops.fused_step import build_fused_engine
+            from ..ops.sampled_step import SUPPORTED_SCORING as SAMPLED, build_sampled_engine
         except Exception:
             if backend == "cuda":
                 raise
             return None
-        return build_fused_engine(model, getattr(loader, "dataset", None), self.attributes, self.device,
-                                  strict=(backend == "cuda"))
+        ds = getattr(loader, "dataset", None)
+        if getattr(self.attributes, "scoring_technique", None) in SAMPLED:
+            return build_sampled_engine(model, ds, self.attributes, self.device, strict=(backend == "cuda"))
+        return build_fused_engine(model, ds, self.attributes, self.device, strict=(backend == "cuda"))
 
     def fit(self, *args, train_dataloaders, **kwargs) -> None:
         assert len(args) == 1
