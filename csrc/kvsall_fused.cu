@@ -14,12 +14,14 @@
 // correction (see elementwise.cu), because BCE(s, y) = softplus(s) − y·s splits into a dense label-free term and a
 // term over the known tails only.
 //
-// Structure of a CTA (320 threads, one CTA per SM, persistent over a contiguous range of (x-tile, y-tile) pairs):
-//   warp 0      TMA producer: X tile once per segment, Y tiles through a ring of stages
-//   warp 1      tcgen05.mma issuer (one elected lane); owns the TMEM allocation
-//   warps 2..9  epilogue: tcgen05.ld S → sigmoid / loss → tcgen05.st dS (bf16, packed) → final drain of out
+// Structure of a CTA (576 threads, one CTA per SM, persistent over a contiguous range of (x-tile, y-tile) pairs):
+//   warp 0       TMA producer: X tile once per segment, Y tiles through a ring of stages
+//   warp 1       tcgen05.mma issuer (one elected lane); owns the TMEM allocation
+//   warps 2..17  epilogue: tcgen05.ld S → sigmoid / loss → tcgen05.st dS (bf16, packed) → final drain of out
 // TMEM columns: [0, D) out accumulator, [256, 384) and [384, 512) the double-buffered S tiles; dS overwrites
-// columns of the S buffer it was computed from (its own half, so no other warp's unread data is touched).
+// columns of the S buffer it was computed from (the warp's own 32 columns, so no other warp's unread data is
+// touched).  Sixteen epilogue warps (four per scheduler) keep the special-function unit busy: with eight the
+// epilogue of the loss variant took 1.7x the time of the two GEMMs of a tile.
 // Every mbarrier wait is bounded; on a time-out the kernel records a status code, drains its TMA copies, frees
 // TMEM and returns.
 #include "ptx_sm100.cuh"
@@ -32,8 +34,8 @@ namespace dice {
 constexpr int BLOCK_X = 128;
 constexpr int BLOCK_Y = 128;
 constexpr int SLAB_BYTES = 128 * 128;  // 128 rows x 64 bf16 (one 128-byte swizzle span per row)
-constexpr int NUM_THREADS = 320;
-constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_EPI_WARPS = 16;   // four per TMEM lane quarter, each owning 32 of a tile's 128 S columns
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 
 struct KvsAllParams {
   float* out;           // [x_rows, D] fp32, accumulated with red.add
@@ -48,6 +50,7 @@ struct KvsAllParams {
   const uint32_t* mask; // MASK: bit y of row x set where (x, y) is a positive label; row stride mask_stride words
   int mask_stride;      // (a multiple of 4, so the two words a thread needs per tile are one aligned 8-byte load)
   float pos_delta;      // label(positive) - base
+  long long* trace;     // optional [64 tiles][8] clock64 stamps written by CTA 0 (pipeline diagnostics), else null
 };
 
 template <int D>
@@ -79,6 +82,81 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
+
+// Position of one GEMM stream inside this CTA's range of flattened (x tile, y tile) pairs; a segment is a run of
+// tiles sharing the x tile.
+struct TileCursor {
+  long long w, w_end;
+  int ny, t, n;
+  uint32_t seg;
+  __device__ __forceinline__ int seglen() const {
+    const int y0 = static_cast<int>(w % ny);
+    return static_cast<int>(min(static_cast<long long>(ny - y0), w_end - w));
+  }
+  __device__ __forceinline__ void start(long long wb, long long we, int ny_tiles) {
+    w = wb; w_end = we; ny = ny_tiles; t = 0; seg = 0;
+    n = w < w_end ? seglen() : 0;
+  }
+  __device__ __forceinline__ bool done() const { return w >= w_end; }
+  __device__ __forceinline__ bool first() const { return t == 0; }
+  __device__ __forceinline__ bool last() const { return t + 1 == n; }
+  __device__ __forceinline__ void advance() {
+    if (++t == n) {
+      w += n;
+      ++seg;
+      t = 0;
+      if (w < w_end) n = seglen();
+    }
+  }
+};
+
+// log1p(e) / e on [0, 1] (degree-5 minimax fit, absolute error of log1p below 7e-6): keeps the logarithm of the
+// loss off the special-function unit, which the exponential and the reciprocal already occupy.
+__device__ __forceinline__ float log1p_over_e(float e) {
+  float q = -0.02397957257926464f;
+  q = fmaf(q, e, 0.10150004923343658f);
+  q = fmaf(q, e, -0.2102936953306198f);
+  q = fmaf(q, e, 0.3252951502799988f);
+  q = fmaf(q, e, -0.49937260150909424f);
+  q = fmaf(q, e, 0.9999918341636658f);
+  return q;
+}
+
+// One thread's 32 logits of a tile: dS = sigmoid(s) - label packed as bf16 pairs (low half = even column) and, with
+// LOSS, the BCE-with-logits terms added to loss.  FULL: all 32 columns are valid entries of Y.
+template <bool LOSS, bool MASK, bool FULL>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t mword, float base, float label_pos,
+                                               int y_valid, uint32_t (&packed)[16], float& loss) {
+  constexpr float LOG2E = 1.4426950408889634f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float ds2[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float s = __uint_as_float(r[i + u]);
+      float label = base;
+      if constexpr (MASK) label = ((mword >> (i + u)) & 1u) ? label_pos : base;
+      float sig;
+      if constexpr (LOSS) {
+        const float e = fast_ex2(-fabsf(s) * LOG2E);       // exp(-|s|)
+        const float inv = fast_rcp(1.f + e);               // sigmoid(|s|)
+        sig = s >= 0.f ? inv : e * inv;
+        float l = fmaf(log1p_over_e(e), e, fmaxf(s, 0.f)); // softplus(s)
+        l = fmaf(-label, s, l);
+        if (!FULL && i + u >= y_valid) l = 0.f;
+        loss += l;
+      } else {
+        sig = fmaf(fast_tanh(0.5f * s), 0.5f, 0.5f);
+      }
+      float d = sig - label;
+      if (!FULL && i + u >= y_valid) d = 0.f;
+      ds2[u] = d;
+    }
+    __nv_bfloat162 v = __floats2bfloat162_rn(ds2[0], ds2[1]);  // .x (low 16 bits) = even K element
+    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
 template <int D, bool LOSS, bool MASK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
@@ -95,10 +173,10 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   uint64_t* dx_empty = bars + 3;
   uint64_t* s_full = bars + 4;       // [2]
   uint64_t* ds_full = bars + 6;      // [2]
-  uint64_t* y_full = bars + 8;       // [NSTAGE]
-  uint64_t* y_empty = bars + 8 + 4;  // [NSTAGE]
-  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
+  uint64_t* y_empty = bars + 8;      // [NSTAGE]
+  uint64_t* y_full = bars + 12;      // [NSTAGE][4]: one per 64-column slab, so the S GEMM starts on the first slab
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 28);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 29);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -118,10 +196,10 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(ds_full + i, NUM_EPI_WARPS);
     }
     for (int i = 0; i < C::NSTAGE; ++i) {
-      mbar_init(y_full + i, 1);
       mbar_init(y_empty + i, 1);
+      for (int sl = 0; sl < C::NSLAB; ++sl) mbar_init(y_full + i * 4 + sl, 1);
     }
-    *reinterpret_cast<volatile uint64_t*>(bars + 17) = 0;  // abort flag and an always-zero word next to it
+    *reinterpret_cast<volatile uint64_t*>(bars + 29) = 0;  // abort flag and an always-zero word next to it
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -143,6 +221,10 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     atomicCAS(p.status, 0, code);
     *s_abort = 1;
   };
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  auto stamp = [&](uint32_t tile, int slot) {
+    if (tracing && tile < 64) p.trace[tile * 8 + slot] = clock64();
+  };
 
   if (warp == 0) {
     // =========================================================================== TMA producer
@@ -161,10 +243,12 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int t = 0; t < n; ++t, ++ycount) {
           const uint32_t st = ycount % C::NSTAGE;
           if (!mbar_wait_bounded(y_empty + st, ((ycount / C::NSTAGE) & 1) ^ 1, s_abort)) { ok = false; break; }
-          mbar_arrive_expect_tx(y_full + st, C::TILE_BYTES);
+          stamp(ycount, 0);
           uint8_t* dst = sY + st * C::TILE_BYTES;
-          for (int s = 0; s < C::NSLAB; ++s)
-            tma_load_2d(dst + s * SLAB_BYTES, &tmap_y, s * 64, (y0 + t) * BLOCK_Y, y_full + st);
+          for (int s = 0; s < C::NSLAB; ++s) {
+            mbar_arrive_expect_tx(y_full + st * 4 + s, SLAB_BYTES);
+            tma_load_2d(dst + s * SLAB_BYTES, &tmap_y, s * 64, (y0 + t) * BLOCK_Y, y_full + st * 4 + s);
+          }
         }
         if (!ok) { fail(ST_TIMEOUT_PRODUCER); break; }
         w += n;
@@ -176,87 +260,110 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (x_loads > 0) drained &= mbar_wait_bounded(x_full, (x_loads - 1) & 1, s_abort + 1 /*always 0*/, 1u << 20);
         for (uint32_t i = 0; i < C::NSTAGE && i < ycount; ++i) {
           const uint32_t last = ycount - 1 - i;  // the most recent use of each stage
-          drained &= mbar_wait_bounded(y_full + (last % C::NSTAGE), (last / C::NSTAGE) & 1, s_abort + 1, 1u << 20);
+          for (int sl = 0; sl < C::NSLAB; ++sl)
+            drained &= mbar_wait_bounded(y_full + (last % C::NSTAGE) * 4 + sl, (last / C::NSTAGE) & 1, s_abort + 1,
+                                         1u << 20);
         }
         if (!drained) atomicExch(p.status, ST_TIMEOUT_DRAIN);
       }
     }
   } else if (warp == 1) {
     // =========================================================================== MMA issuer
+    // The two GEMMs of consecutive tiles are issued in whichever order their inputs become ready: the second GEMM
+    // of tile g (needs dS from the epilogue) ahead of the first GEMM of tile g + 2 (needs the Y stage that the
+    // former releases), so that the tensor pipe has work while that stage is being refilled.
     if (lane == 0) {
       constexpr uint32_t IDESC_G1 = make_idesc_bf16(BLOCK_X, BLOCK_Y, 0, 0);  // S = X · Yᵀ, both K-major
       constexpr uint32_t IDESC_G2 = make_idesc_bf16(BLOCK_X, D, 0, 1);        // out += dS · Y, Y read MN-major
-      const uint32_t sx_addr = smem_u32(sX);
-      uint32_t g = 0, seg = 0;
-      bool ok = true;
+      // descriptors are built once; per MMA only the 14-bit start-address field (16-byte units) is advanced
+      const uint64_t xdesc = make_sw128_desc(smem_u32(sX), 16, 1024);
+      const uint64_t ydesc_g1 = make_sw128_desc(smem_u32(sY), 16, 1024);
+      const uint64_t ydesc_g2 = make_sw128_desc(smem_u32(sY), SLAB_BYTES, 1024);
 
       auto issue_g1 = [&](uint32_t gi) -> bool {
         const uint32_t st = gi % C::NSTAGE;
-        if (!mbar_wait_bounded(y_full + st, (gi / C::NSTAGE) & 1, s_abort)) return false;
+        const uint32_t par = (gi / C::NSTAGE) & 1;
+        stamp(gi, 1);
         tc_fence_after();
-        const uint32_t sy_addr = smem_u32(sY + st * C::TILE_BYTES);
+        const uint64_t yd = ydesc_g1 + st * (C::TILE_BYTES >> 4);
         const uint32_t d_tmem = tmem_s0 + (gi & 1) * BLOCK_Y;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * SLAB_BYTES + (k & 3) * 32;  // 16 bf16 = 32 bytes inside the swizzle span
-          mma_ss(d_tmem, make_sw128_desc(sx_addr + off, 16, 1024), make_sw128_desc(sy_addr + off, 16, 1024),
-                 IDESC_G1, k > 0 ? 1u : 0u);
+        for (int sl = 0; sl < C::NSLAB; ++sl) {
+          if (sl > 0) {  // slab 0 was probed by the caller
+            if (!mbar_wait_bounded(y_full + st * 4 + sl, par, s_abort)) return false;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t off16 = sl * (SLAB_BYTES >> 4) + kk * 2;  // 16 bf16 = 32 bytes inside the swizzle span
+            if (sl == 0 && kk == 0) mma_ss(d_tmem, xdesc + off16, yd + off16, IDESC_G1, 0u);
+            else mma_ss(d_tmem, xdesc + off16, yd + off16, IDESC_G1, 1u);
+          }
         }
         tc_commit(s_full + (gi & 1));
         return true;
       };
-      auto issue_g2 = [&](uint32_t gi, bool first, bool last) -> bool {
+      auto issue_g2 = [&](uint32_t gi, bool first, bool last) {
         const uint32_t st = gi % C::NSTAGE;
-        const uint32_t b = gi & 1;
-        if (!mbar_wait_bounded(ds_full + b, (gi >> 1) & 1, s_abort)) return false;
-        if (first && !mbar_wait_bounded(dx_empty, (seg & 1) ^ 1, s_abort)) return false;
+        stamp(gi, 2);
         tc_fence_after();
-        const uint32_t sy_addr = smem_u32(sY + st * C::TILE_BYTES);
-        const uint32_t a_base = tmem_s0 + b * BLOCK_Y;
+        const uint64_t yd = ydesc_g2 + st * (C::TILE_BYTES >> 4);
+        const uint32_t a_base = tmem_s0 + (gi & 1) * BLOCK_Y;
 #pragma unroll
         for (int k = 0; k < BLOCK_Y / 16; ++k) {
-          // dS columns: K elements 0..63 live in columns [0, 32), 64..127 in columns [64, 96) of the S buffer
-          const uint32_t a_tmem = a_base + (k < 4 ? 8 * k : 64 + 8 * (k - 4));
-          // Y tile as [K = 128 rows, N = D]: N blocks of 64 are one slab apart, groups of 8 K-rows 1024 B apart
-          mma_ts(tmem_out, a_tmem, make_sw128_desc(sy_addr + k * 16 * 128, SLAB_BYTES, 1024), IDESC_G2,
-                 (first && k == 0) ? 0u : 1u);
+          // dS: the 32 K elements of column group c are packed into columns [32 c, 32 c + 16) of the S buffer
+          const uint32_t a_tmem = a_base + 32 * (k >> 1) + 8 * (k & 1);
+          // Y tile as [K = 128 rows, N = D]: N blocks of 64 are one slab apart, groups of 8 K-rows 1024 B apart;
+          // 16 K-rows = 2048 bytes
+          if (k == 0) mma_ts(tmem_out, a_tmem, yd, IDESC_G2, first ? 0u : 1u);
+          else mma_ts(tmem_out, a_tmem, yd + k * 128, IDESC_G2, 1u);
         }
         tc_commit(y_empty + st);
         if (last) tc_commit(dx_full);
-        return true;
       };
 
-      for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
-        const int y0 = static_cast<int>(w % p.ny_tiles);
-        const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
-        if (!mbar_wait_bounded(x_full, seg & 1, s_abort)) { ok = false; break; }
-        tc_fence_after();
-        ok = issue_g1(g);
-        if (ok && n == 1) tc_commit(x_empty);
-        for (int t = 0; t < n && ok; ++t) {
-          if (t + 1 < n) {
-            ok = issue_g1(g + t + 1);
-            if (ok && t + 2 == n) tc_commit(x_empty);  // last S GEMM of the segment: X buffer may be refilled
-          }
-          if (ok) ok = issue_g2(g + t, t == 0, t + 1 == n);
+      TileCursor c1, c2;
+      c1.start(w_begin, w_end, p.ny_tiles);
+      c2.start(w_begin, w_end, p.ny_tiles);
+      uint32_t g1 = 0, g2 = 0, idle = 0;
+      bool ok = true;
+      while (!c2.done() && ok && !*s_abort) {
+        bool progressed = false;
+        if (g2 < g1 && mbar_try_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
+            (!c2.first() || mbar_try_wait(dx_empty, (c2.seg & 1) ^ 1))) {
+          issue_g2(g2, c2.first(), c2.last());
+          ++g2;
+          c2.advance();
+          progressed = true;
         }
-        g += n;
-        w += n;
-        ++seg;
+        if (!progressed && !c1.done() && g1 - g2 < 2 && (!c1.first() || mbar_try_wait(x_full, c1.seg & 1)) &&
+            mbar_try_wait(y_full + (g1 % C::NSTAGE) * 4, (g1 / C::NSTAGE) & 1)) {
+          if (!issue_g1(g1)) { ok = false; break; }
+          if (c1.last()) tc_commit(x_empty);  // last S GEMM of the segment: the X buffer may be refilled
+          ++g1;
+          c1.advance();
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > DICE_WAIT_LIMIT) {
+          ok = false;
+        } else if (idle > 256) {
+          __nanosleep(32);
+        }
       }
       if (!ok) fail(ST_TIMEOUT_MMA);
     }
   } else {
     // =========================================================================== epilogue warps
     const int quarter = warp & 3;              // TMEM lane group this warp may access
-    const int half = (warp - 2) >> 2;          // which 64 of the 128 S columns
+    const int cg = (warp - 2) >> 2;            // which 32 of the 128 S columns
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const int row = quarter * 32 + lane;
     float loss_acc = 0.f;
     uint32_t g = 0, seg = 0;
     bool ok = true;
-    constexpr float LOG2E = 1.4426950408889634f;
-    constexpr float LN2 = 0.6931471805599453f;
+    const float label_pos = p.base + p.pos_delta;
 
     for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
       const int x = static_cast<int>(w / p.ny_tiles);
@@ -268,61 +375,35 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
       for (int t = 0; t < n; ++t, ++g) {
         const uint32_t b = g & 1;
-        uint2 mw = make_uint2(0u, 0u);
+        uint32_t mword = 0u;
         if constexpr (MASK) {
-          if (valid_x)
-            mw = *reinterpret_cast<const uint2*>(p.mask + static_cast<size_t>(x_global) * p.mask_stride +
-                                                 (y0 + t) * 4 + half * 2);
+          if (valid_x) mword = p.mask[static_cast<size_t>(x_global) * p.mask_stride + (y0 + t) * 4 + cg];
         }
         if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1, s_abort)) { ok = false; break; }
+        if (warp == 2 && lane == 0) stamp(g, 3);
         tc_fence_after();
-        const int y_valid = p.y_rows - (y0 + t) * BLOCK_Y;  // columns >= y_valid are padding
-        const uint32_t s_addr = tmem_s0 + b * BLOCK_Y + lane_sel;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = half * 64 + c * 32;
-          uint32_t r[32];
-          tmem_ld32(s_addr + col0, r);
-          tc_wait_ld();
-          uint32_t packed[16];
-          const uint32_t mword = c == 0 ? mw.x : mw.y;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float ds2[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const float s = __uint_as_float(r[i + u]);
-              float label = p.base;
-              if constexpr (MASK) label = ((mword >> (i + u)) & 1u) ? p.base + p.pos_delta : p.base;
-              float sig;
-              if constexpr (LOSS) {
-                const float e = fast_ex2(-fabsf(s) * LOG2E);       // exp(-|s|)
-                const float inv = fast_rcp(1.f + e);               // sigmoid(|s|)
-                sig = s >= 0.f ? inv : e * inv;
-                float l = fmaxf(s, 0.f) + LN2 * fast_lg2(1.f + e) - label * s;
-                if (col0 + i + u >= y_valid) l = 0.f;
-                seg_loss += l;
-              } else {
-                sig = fmaf(fast_tanh(0.5f * s), 0.5f, 0.5f);
-              }
-              float d = sig - label;
-              if (col0 + i + u >= y_valid) d = 0.f;
-              ds2[u] = d;
-            }
-            __nv_bfloat162 v = __floats2bfloat162_rn(ds2[0], ds2[1]);  // .x (low 16 bits) = even K element
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
-          }
-          tmem_st16(s_addr + half * 64 + c * 16, packed);
+        const int y_valid = p.y_rows - (y0 + t) * BLOCK_Y - cg * 32;  // columns >= y_valid of this chunk are padding
+        const uint32_t s_addr = tmem_s0 + b * BLOCK_Y + lane_sel + cg * 32;
+        uint32_t r[32];
+        tmem_ld32(s_addr, r);
+        tc_wait_ld();
+        uint32_t packed[16];
+        if (y_valid >= 32) {
+          epilogue_chunk<LOSS, MASK, true>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+        } else {
+          epilogue_chunk<LOSS, MASK, false>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
         }
+        tmem_st16(s_addr, packed);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
+        if (warp == 2 && lane == 0) stamp(g, 4);
         if (lane == 0) mbar_arrive(ds_full + b);
       }
       if (!ok) break;
       if (valid_x) loss_acc += seg_loss;
 
-      // drain the accumulated out tile of this segment
+      // drain the accumulated out tile of this segment: this warp owns D / 4 of its columns
       if (!mbar_wait_bounded(dx_full, seg & 1, s_abort)) { ok = false; break; }
       tc_fence_after();
       float* out_row = p.out;
@@ -331,21 +412,36 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                       ? p.out_table[x_global / p.out_block_rows] + static_cast<size_t>(x_global % p.out_block_rows) * D
                       : p.out + static_cast<size_t>(x_global) * D;
       }
+      constexpr int DC = D / 4;
+      if constexpr (DC >= 32) {
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        const int col0 = half * (D / 2) + c * 32;
-        uint32_t r[32];
-        tmem_ld32(tmem_out + lane_sel + col0, r);
+        for (int c = 0; c < DC / 32; ++c) {
+          const int col0 = cg * DC + c * 32;
+          uint32_t r[32];
+          tmem_ld32(tmem_out + lane_sel + col0, r);
+          tc_wait_ld();
+          if (valid_x) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              red_add_v4(out_row + col0 + i, __uint_as_float(r[i]) * p.scale, __uint_as_float(r[i + 1]) * p.scale,
+                         __uint_as_float(r[i + 2]) * p.scale, __uint_as_float(r[i + 3]) * p.scale);
+          }
+        }
+      } else {
+        const int col0 = cg * DC;
+        uint32_t r[16];
+        tmem_ld16(tmem_out + lane_sel + col0, r);
         tc_wait_ld();
         if (valid_x) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
+          for (int i = 0; i < 16; i += 4)
             red_add_v4(out_row + col0 + i, __uint_as_float(r[i]) * p.scale, __uint_as_float(r[i + 1]) * p.scale,
                        __uint_as_float(r[i + 2]) * p.scale, __uint_as_float(r[i + 3]) * p.scale);
         }
       }
       tc_fence_before();
       __syncwarp();
+      if (warp == 2 && lane == 0) stamp(g - 1, 5);
       if (lane == 0) mbar_arrive(dx_empty);
       w += n;
       ++seg;
@@ -385,6 +481,15 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 
 }  // namespace dice
 
+// Pipeline diagnostics: when a device buffer of 64 * 8 int64 is registered here, CTA 0 of every following launch
+// writes clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
+// 4 epilogue wrote dS, 5 out tile drained).  Pass null to switch it off again.
+static long long* g_trace_buffer = nullptr;
+extern "C" int dice_kvsall_set_trace(long long* buffer) {
+  g_trace_buffer = buffer;
+  return 0;
+}
+
 // x, y: bf16 row-major with 16-byte aligned base; D in {64, 128, 256}.  out must be zero-initialised (or hold a
 // running sum) by the caller; *loss likewise.  With out_table != null (a device array of base pointers, one per
 // block of out_block_rows rows, possibly in peer memory) the result rows are scattered to their owners instead.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
@@ -418,6 +523,7 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.mask = mask;
   p.mask_stride = mask_stride;
   p.pos_delta = pos_delta;
+  p.trace = g_trace_buffer;
   if (mask != nullptr && ((mask_stride & 3) || (reinterpret_cast<uintptr_t>(mask) & 7))) return -5;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;

@@ -139,6 +139,15 @@ def p2p_barrier(sig_table: torch.Tensor, rank: int, world: int, count: torch.Ten
                                        _stream()), "dice_p2p_barrier")
 
 
+def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
+    """Register (or clear with ``None``) a ``[64, 8]`` int64 device buffer receiving per-tile clock stamps of CTA 0 of
+    every following ``kvsall_fused`` launch (pipeline diagnostics; see ``profile_fused --trace``)."""
+    if buffer is not None:
+        _req(buffer, torch.int64, "trace buffer")
+        assert buffer.numel() >= 512
+    _lib.lib().dice_kvsall_set_trace(_ptr(buffer))
+
+
 def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0) -> None:
     """Fill ``out`` (int64) with uniform integers in ``[0, high)`` from the counter-based generator."""
     _req(out, torch.int64, "out")

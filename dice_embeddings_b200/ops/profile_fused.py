@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mask", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="print per-tile pipeline stamps of CTA 0 (cycles)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
@@ -60,6 +61,19 @@ def main():
         tf = flop / (ms * 1e-3) / 1e12
         print(f"{name:20s} nx={a.nx} ny={a.ny} D={a.d} mask={a.mask}: {ms * 1e3:8.1f} us  {tf:7.1f} TFLOP/s  "
               f"{tf / peak:.2f} {tag} ({peak:.0f})")
+        if a.trace:
+            buf = torch.zeros(64, 8, dtype=torch.int64, device=dev)
+            K.kvsall_set_trace(buf)
+            fn()
+            torch.cuda.synchronize()
+            K.kvsall_set_trace(None)
+            t = buf.cpu()
+            t0 = int(t[0, 0])
+            print("  tile | Y load issued | S gemm issued | 2nd gemm issued | epi sees S | epi wrote dS | out drained")
+            for g in range(64):
+                if int(t[g, 0]) == 0:
+                    break
+                print("  %4d | %s" % (g, " | ".join("%8d" % (int(v) - t0) if int(v) else "       -" for v in t[g, :6])))
     K.check_status(status)
 
 
