@@ -332,6 +332,43 @@ class ShardedKvsAllEngine:
         for r, s in enumerate(shards):
             scatter_shard_back(full, s, r, self.W)
 
+    # ------------------------------------------------------------------ checkpoint / resume
+    def _replicated_state(self):
+        rep = {"relation_embeddings.weight": self.R, "m_R": self.mR, "v_R": self.vR}
+        if self.coeff is not None:
+            rep.update({"q_coefficients.weight": self.coeff, "m_C": self.mC, "v_C": self.vC})
+        return rep
+
+    @torch.no_grad()
+    def save_checkpoint(self, directory: str) -> None:
+        """Collective: every rank writes its rows of the entity table and of the Adam moments, rank 0 the replicated
+        parameters and the manifest (see :mod:`dice_embeddings_b200.io.sharded_checkpoint`)."""
+        from ..io import sharded_checkpoint as sc
+        self.check()
+        torch.cuda.synchronize(self.device)
+        sc.save_shard(directory, self.rank, self.W, self.NE, {"E": self.E, "mE": self.mE, "vE": self.vE},
+                      replicated=self._replicated_state() if self.rank == 0 else None,
+                      step=int(self.step_count.item()),
+                      extra={"lr": self.lr, "optimizer": self.model.optimizer_name, "model": type(self.model).__name__})
+        dist.barrier(group=self.group)
+
+    @torch.no_grad()
+    def load_checkpoint(self, directory: str) -> None:
+        """Collective: resume from a sharded checkpoint written with any world size."""
+        from ..io import sharded_checkpoint as sc
+        man = sc.read_manifest(directory)
+        assert man["num_entities"] == self.NE and man["dim"] == self.D, "checkpoint belongs to another table shape"
+        t = sc.load_shard(directory, self.rank, self.W, self.device)
+        for name, dst in (("E", self.E), ("mE", self.mE), ("vE", self.vE)):
+            dst[: self.rows].copy_(t[name])
+        rep = sc.load_replicated(directory, self.device)
+        for k, dst in self._replicated_state().items():
+            if k in rep:
+                dst.copy_(rep[k])
+        self.step_count.fill_(int(man["step"]))
+        K.cast_bf16(self.E, self.E_bf16)   # the captured graph stays valid: all buffers keep their addresses
+        dist.barrier(group=self.group)
+
     def optimizer_view(self):
         from ..ops.fused_step import _EngineOptimizer
         return _EngineOptimizer(self)

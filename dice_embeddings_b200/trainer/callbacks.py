@@ -5,6 +5,7 @@ import datetime
 import os
 import time
 
+import numpy as np
 import pandas as pd
 import torch
 
@@ -58,6 +59,52 @@ class KGESaveCallback(AbstractCallback):
             save_checkpoint_model(model, path=os.path.join(
                 self.path, f"model_at_{self.epoch_counter}_epoch_{datetime.datetime.now()}.pt"))
         self.epoch_counter += 1
+
+
+class PseudoLabellingCallback(AbstractCallback):
+    """Self-training: after each epoch a random batch of unlabelled triples is scored and those with
+    ``sigmoid(score) >= threshold`` are appended to the training triples (reference ``callbacks.py:110-147``)."""
+
+    def __init__(self, data_module, kg, batch_size: int, threshold: float = 0.9):
+        super().__init__()
+        self.data_module, self.kg, self.batch_size, self.threshold = data_module, kg, int(batch_size), threshold
+        self.unlabelled_size = len(self.kg.unlabelled_set)
+
+    def create_random_data(self) -> torch.Tensor:
+        e = torch.randint(0, self.kg.num_entities, (self.batch_size, 2))
+        r = torch.randint(0, self.kg.num_relations, (self.batch_size,))
+        return torch.stack((e[:, 0], r, e[:, 1]), dim=1)
+
+    def on_epoch_end(self, trainer, model):
+        return self.on_train_epoch_end(trainer, model)
+
+    def on_train_epoch_end(self, trainer, model):
+        model.eval()
+        with torch.no_grad():
+            pool = torch.as_tensor(np.asarray(self.kg.unlabelled_set)).long()
+            batch = pool[torch.randint(0, self.unlabelled_size, (self.batch_size,))]
+            conf = torch.sigmoid(model(batch.to(model.device))).cpu()
+            chosen = batch[conf >= self.threshold]
+        if len(chosen):
+            self.data_module.train_set_idx = np.concatenate(
+                (np.asarray(self.data_module.train_set_idx), chosen.numpy().astype(np.asarray(self.data_module.train_set_idx).dtype)), axis=0)
+            if hasattr(self.data_module, "train_dataloader"):
+                trainer.train_dataloader = self.data_module.train_dataloader()
+            print(f"\tEpoch:{trainer.current_epoch}: Pseudo-labelling\t |D|= {len(self.data_module.train_set_idx)}")
+        model.train()
+
+
+def estimate_q(eps) -> float:
+    """Rate of convergence ``q`` estimated from an error sequence (reference ``callbacks.py:150-156``)."""
+    eps = np.asarray(eps, dtype=np.float64)
+    x = np.arange(len(eps) - 1)
+    y = np.log(np.abs(np.diff(np.log(eps))))
+    return float(np.exp(np.polyfit(x, y, 1)[0]))
+
+
+def compute_convergence(seq, i: int) -> float:
+    assert len(seq) >= i > 0
+    return estimate_q(np.asarray(seq[-i:], dtype=np.float64) / (np.arange(i) + 1))
 
 
 class Eval(AbstractCallback):

@@ -162,3 +162,24 @@ def test_optimizer_kernels_match_torch(kind, name):
     assert torch.allclose(p, p_ref.detach(), atol=1e-5, rtol=1e-4)
     assert float(g.abs().max()) == 0.0
     assert torch.allclose(shadow.float(), p, atol=2e-2, rtol=1e-2)
+
+
+def test_p2p_barrier_wait_is_bounded():
+    """A barrier whose peer never signals gives up after its spin limit and reports it; the context stays usable."""
+    sig0 = torch.zeros(2, dtype=torch.int32, device=DEV)
+    sig1 = torch.zeros(2, dtype=torch.int32, device=DEV)
+    table = K.pointer_table([sig0, sig1], DEV)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.p2p_barrier(table, 0, 2, count, status, spin_limit=2000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4                     # peer wait timed out
+    assert int(sig1[0].item()) == 1                    # our own signal was delivered
+    with pytest.raises(K.KernelError):
+        K.check_status(status)
+    # the peer "arrives": the next barrier of the pair completes
+    sig0[1] = 2
+    K.p2p_barrier(table, 0, 2, count, status, spin_limit=2000)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    assert (torch.ones(4, device=DEV) * 2).sum().item() == 8.0

@@ -59,3 +59,63 @@ def test_vector_search_service(run_dir):
     assert np.allclose(v, vecs[1], atol=1e-5)
     b = client.post("/api/search_batch", json={"queries": names[:2], "k": 2}).json()
     assert set(b["results"]) == set(names[:2])
+
+
+def test_multi_hop_evaluate_matches_loop_definition():
+    """The vectorised filtered ranking of query answers equals the definition: rank of each hard answer among all
+    entities after removing every other answer."""
+    from dice_embeddings_b200 import evaluate
+    rng = np.random.default_rng(0)
+    ents = {f"e{i}": i for i in range(50)}
+    scores, easy, hard = {}, {}, {}
+    for q in range(6):
+        s = rng.normal(size=50)
+        ans = rng.choice(50, size=8, replace=False)
+        scores[q], easy[q], hard[q] = s, {f"e{i}" for i in ans[:5]}, {f"e{i}" for i in ans[5:]}
+    mrr, h1, h3, h10 = evaluate(ents, scores, easy, hard)
+    exp = []
+    for q in range(6):
+        s = scores[q]
+        rr = []
+        for a in hard[q]:
+            i = ents[a]
+            others = {ents[e] for e in (easy[q] | hard[q])} - {i}
+            rank = 1 + sum(1 for j in range(50) if j not in others and j != i and s[j] > s[i])
+            rr.append(1.0 / rank)
+        exp.append(np.mean(rr))
+    assert abs(mrr - np.mean(exp)) < 1e-12 and 0 <= h1 <= h3 <= h10 <= 1
+
+
+def test_helper_functions(tmp_path):
+    import dice_embeddings_b200 as d
+    from dice_embeddings_b200.trainer.callbacks import compute_convergence, estimate_q
+    a = np.arange(12).reshape(4, 3)
+    d.save_numpy_ndarray(data=a, file_path=str(tmp_path / "a.npy"))
+    assert (d.load_numpy(str(tmp_path / "a.npy")) == a).all()
+    assert d.numpy_data_type_changer(a, 100).dtype == np.int8 and d.numpy_data_type_changer(a, 70000).dtype == np.int32
+    w = d.exponential_function(np.arange(5), 0.5)
+    assert abs(float(w.sum()) - 1) < 1e-6 and w[0] < w[-1]
+    assert 0 < estimate_q(np.array([1, .5, .25, .125, .0625]) * 0.1 + 1e-3) < 2
+    assert compute_convergence(np.array([.9, .5, .3, .2, .15, .12]), 5) > 0
+    import pandas as pd
+    df = d.create_recipriocal_triples(pd.DataFrame({"subject": ["a"], "relation": ["r"], "object": ["b"]}))
+    assert df.iloc[1].tolist() == ["b", "r_inverse", "a"]
+
+
+def test_pseudo_labelling_callback_grows_training_set():
+    import torch
+    from types import SimpleNamespace
+    from dice_embeddings_b200.trainer.callbacks import PseudoLabellingCallback
+
+    class M(torch.nn.Module):
+        device = torch.device("cpu")
+
+        def forward(self, x):
+            return torch.where(x[:, 0] % 2 == 0, torch.tensor(5.0), torch.tensor(-5.0))
+
+    kg = SimpleNamespace(unlabelled_set=np.stack([np.arange(100), np.zeros(100, int), np.arange(100)], 1),
+                         num_entities=100, num_relations=1)
+    dm = SimpleNamespace(train_set_idx=np.zeros((3, 3), dtype=np.int64))
+    cb = PseudoLabellingCallback(dm, kg, batch_size=40)
+    cb.on_train_epoch_end(SimpleNamespace(current_epoch=0), M())
+    assert len(dm.train_set_idx) > 3 and (dm.train_set_idx[3:, 0] % 2 == 0).all()
