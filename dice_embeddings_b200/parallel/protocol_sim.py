@@ -96,6 +96,7 @@ class SimBarrier:
         self.count = [0] * world
         self.drop = drop or (lambda sender, peer, count: False)
         self._lock = threading.Lock()
+        self.abort = threading.Event()   # set when a rank has failed: the others stop waiting at once
 
     def arrive_and_wait(self, rank: int) -> int:
         """Returns ``ST_OK`` or ``ST_TIMEOUT_PEER`` (never blocks for ever)."""
@@ -108,6 +109,8 @@ class SimBarrier:
         for _ in range(self.poll_limit):
             if all(self.sig[rank][p] >= c for p in range(self.world)):
                 return ST_OK
+            if self.abort.is_set():
+                break
             time.sleep(self.poll_sleep)
         return ST_TIMEOUT_PEER
 
@@ -209,15 +212,17 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 losses[rank] = loss
         except BaseException as exc:  # noqa: BLE001 - reported to the caller
             errors[rank] = exc
+            bar.abort.set()
 
     threads = [threading.Thread(target=work, args=(k,), daemon=True) for k in range(W) if k != absent_rank]
     for t in threads:
         t.start()
     for t in threads:
         t.join()
-    for e in errors:
-        if e is not None:
-            raise e
+    failed = [e for e in errors if e is not None]
+    if failed:  # the root cause first: a hazard on one rank makes the others time out at their next barrier
+        failed.sort(key=lambda e: 0 if isinstance(e, ProtocolHazard) else 1)
+        raise failed[0]
     E_new = np.zeros_like(E)
     for e in range(NE):
         E_new[e] = heap.bufs["E"][e % W][e // W]
