@@ -11,6 +11,7 @@
 // epilogue, one persistent CTA per SM over a contiguous range of (x-tile, y-tile) pairs) but there is no second
 // GEMM, so all 512 TMEM columns hold four S buffers.  Every wait is bounded and reports through the status word.
 #include "ptx_sm100.cuh"
+#include "tile_map.cuh"
 #include "tma_host.cuh"
 
 #include <math_constants.h>
@@ -34,6 +35,7 @@ struct EvalParams {
   int* greater;            // [x_rows] += number of columns with s > target
   int* status;
   int x_rows, y_rows, nx_tiles, ny_tiles;
+  TileMap map;             // visiting order of the (x tile, y tile) pairs
   int y_offset, y_stride;  // global id of column c is y_offset + c * y_stride (contiguous or cyclic row shards)
   // top-k (TOPK variants): every (segment, row, half) appends its k best to the row's candidate list
   int k;
@@ -113,9 +115,9 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (lane == 0) {
       uint32_t ycount = 0, seg = 0, x_loads = 0;
       for (long long w = w_begin; w < w_end && !*s_abort;) {
-        const int x = static_cast<int>(w / p.ny_tiles);
-        const int y0 = static_cast<int>(w % p.ny_tiles);
-        const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
+        int x, y0, run;
+        p.map.locate(w, x, y0, run);
+        const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
         if (!mbar_wait_bounded(x_empty, (seg & 1) ^ 1, s_abort)) { fail(ST_TIMEOUT_PRODUCER); break; }
         mbar_arrive_expect_tx(x_full, C::TILE_BYTES);
         for (int s = 0; s < C::NSLAB; ++s) tma_load_2d(sX + s * SLAB_BYTES, &tmap_x, s * 64, x * BLOCK_X, x_full);
@@ -151,8 +153,9 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       uint32_t g = 0, seg = 0;
       bool ok = true;
       for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
-        const int y0 = static_cast<int>(w % p.ny_tiles);
-        const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
+        int x, y0, run;
+        p.map.locate(w, x, y0, run);
+        const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
         if (!mbar_wait_bounded(x_full, seg & 1, s_abort)) { ok = false; break; }
         for (int t = 0; t < n; ++t, ++g) {
           const uint32_t st = g % C::NSTAGE;
@@ -189,9 +192,9 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     int top_i[TOPK ? KMAX : 1];
 
     for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
-      const int x = static_cast<int>(w / p.ny_tiles);
-      const int y0 = static_cast<int>(w % p.ny_tiles);
-      const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
+      int x, y0, run;
+      p.map.locate(w, x, y0, run);
+      const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
       const int x_global = x * BLOCK_X + row;
       const bool valid_x = x_global < p.x_rows;
       const float tgt = (valid_x && p.target != nullptr) ? p.target[x_global] : CUDART_INF_F;
@@ -394,6 +397,7 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   p.y_rows = y_rows;
   p.nx_tiles = (x_rows + BLOCK_X - 1) / BLOCK_X;
   p.ny_tiles = (y_rows + BLOCK_Y - 1) / BLOCK_Y;
+  p.map = TileMap::make(p.nx_tiles, p.ny_tiles, BLOCK_Y * D * 2, 48ll << 20);
   p.y_offset = y_offset;
   p.y_stride = y_stride > 0 ? y_stride : 1;
   p.k = k;
@@ -418,8 +422,10 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   }
 }
 
-// Upper bound on the number of candidate entries one row can receive from dice_eval_rank with the given shape.
-extern "C" int dice_eval_rank_cand_cap(int x_rows, int y_rows, int k, int num_ctas) {
+// Number of candidate entries one row can receive from dice_eval_rank with the given shape: k per (segment, half),
+// where the segments are found by walking every CTA's range in the kernel's own visiting order.
+extern "C" int dice_eval_rank_cand_cap(int x_rows, int y_rows, int D, int k, int num_ctas) {
+  using namespace dice;
   using namespace dice::evalk;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;
@@ -427,13 +433,25 @@ extern "C" int dice_eval_rank_cand_cap(int x_rows, int y_rows, int k, int num_ct
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     num_ctas = sms;
   }
-  const long long nx = (x_rows + BLOCK_X - 1) / BLOCK_X, ny = (y_rows + BLOCK_Y - 1) / BLOCK_Y;
-  const long long total = nx * ny;
+  const int nx = (x_rows + BLOCK_X - 1) / BLOCK_X, ny = (y_rows + BLOCK_Y - 1) / BLOCK_Y;
+  const TileMap map = TileMap::make(nx, ny, BLOCK_Y * D * 2, 48ll << 20);
+  const long long total = map.total();
   if (num_ctas > total) num_ctas = static_cast<int>(total);
-  const long long per_cta = total / num_ctas;  // every CTA gets at least this many consecutive tiles
-  long long segs = per_cta > 0 ? ny / per_cta + 2 : num_ctas;
-  if (segs > num_ctas) segs = num_ctas;
-  return static_cast<int>(segs * 2 * k);
+  int* per_x = new int[nx]();
+  for (int c = 0; c < num_ctas; ++c) {
+    const long long w_end = total * (c + 1) / num_ctas;
+    for (long long w = total * c / num_ctas; w < w_end;) {
+      int x, y, run;
+      map.locate(w, x, y, run);
+      const long long n = run < w_end - w ? run : w_end - w;
+      ++per_x[x];
+      w += n;
+    }
+  }
+  int worst = 1;
+  for (int x = 0; x < nx; ++x) worst = per_x[x] > worst ? per_x[x] : worst;
+  delete[] per_x;
+  return worst * 2 * k;
 }
 
 extern "C" int dice_eval_sparse(const void* q, const void* y, int n, int D, int y_rows, int y_offset, int y_stride,

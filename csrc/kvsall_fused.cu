@@ -25,6 +25,7 @@
 // Every mbarrier wait is bounded; on a time-out the kernel records a status code, drains its TMA copies, frees
 // TMEM and returns.
 #include "ptx_sm100.cuh"
+#include "tile_map.cuh"
 #include "tma_host.cuh"
 
 #include <stdio.h>
@@ -45,6 +46,7 @@ struct KvsAllParams {
   int* status;          // 0 = ok, otherwise first failure code
   int x_rows, y_rows;   // valid row counts
   int nx_tiles, ny_tiles;
+  TileMap map;          // visiting order of the (x tile, y tile) pairs
   float base;           // label value outside the positives (smoothing term)
   float scale;          // factor applied to out (1 / (B * |E|) for a mean-reduced loss)
   const uint32_t* mask; // MASK: bit y of row x set where (x, y) is a positive label; row stride mask_stride words
@@ -87,15 +89,17 @@ __device__ __forceinline__ float fast_tanh(float x) {
 // tiles sharing the x tile.
 struct TileCursor {
   long long w, w_end;
-  int ny, t, n;
+  TileMap map;
+  int x, y0, t, n;
   uint32_t seg;
-  __device__ __forceinline__ int seglen() const {
-    const int y0 = static_cast<int>(w % ny);
-    return static_cast<int>(min(static_cast<long long>(ny - y0), w_end - w));
+  __device__ __forceinline__ void load() {
+    int run;
+    map.locate(w, x, y0, run);
+    n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
   }
-  __device__ __forceinline__ void start(long long wb, long long we, int ny_tiles) {
-    w = wb; w_end = we; ny = ny_tiles; t = 0; seg = 0;
-    n = w < w_end ? seglen() : 0;
+  __device__ __forceinline__ void start(long long wb, long long we, const TileMap& m) {
+    w = wb; w_end = we; map = m; t = 0; seg = 0; x = 0; y0 = 0; n = 0;
+    if (w < w_end) load();
   }
   __device__ __forceinline__ bool done() const { return w >= w_end; }
   __device__ __forceinline__ bool first() const { return t == 0; }
@@ -105,7 +109,7 @@ struct TileCursor {
       w += n;
       ++seg;
       t = 0;
-      if (w < w_end) n = seglen();
+      if (w < w_end) load();
     }
   }
 };
@@ -232,9 +236,9 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       uint32_t ycount = 0, seg = 0;
       uint32_t x_loads = 0;
       for (long long w = w_begin; w < w_end && !*s_abort;) {
-        const int x = static_cast<int>(w / p.ny_tiles);
-        const int y0 = static_cast<int>(w % p.ny_tiles);
-        const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
+        int x, y0, run;
+        p.map.locate(w, x, y0, run);
+        const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
         if (!mbar_wait_bounded(x_empty, (seg & 1) ^ 1, s_abort)) { fail(ST_TIMEOUT_PRODUCER); break; }
         mbar_arrive_expect_tx(x_full, C::TILE_BYTES);
         for (int s = 0; s < C::NSLAB; ++s) tma_load_2d(sX + s * SLAB_BYTES, &tmap_x, s * 64, x * BLOCK_X, x_full);
@@ -323,8 +327,8 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       };
 
       TileCursor c1, c2;
-      c1.start(w_begin, w_end, p.ny_tiles);
-      c2.start(w_begin, w_end, p.ny_tiles);
+      c1.start(w_begin, w_end, p.map);
+      c2.start(w_begin, w_end, p.map);
       uint32_t g1 = 0, g2 = 0, idle = 0;
       bool ok = true;
       while (!c2.done() && ok && !*s_abort) {
@@ -366,18 +370,27 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const float label_pos = p.base + p.pos_delta;
 
     for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
-      const int x = static_cast<int>(w / p.ny_tiles);
-      const int y0 = static_cast<int>(w % p.ny_tiles);
-      const int n = static_cast<int>(min(static_cast<long long>(p.ny_tiles - y0), w_end - w));
+      int x, y0, run;
+      p.map.locate(w, x, y0, run);
+      const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
       const int x_global = x * BLOCK_X + row;
       const bool valid_x = x_global < p.x_rows;
       float seg_loss = 0.f;
 
+      // label words are fetched one tile ahead: the strided global load would otherwise sit on the critical path
+      const uint32_t* mrow = nullptr;
+      uint32_t mnext = 0u;
+      if constexpr (MASK) {
+        if (valid_x) {
+          mrow = p.mask + static_cast<size_t>(x_global) * p.mask_stride + y0 * 4 + cg;
+          mnext = mrow[0];
+        }
+      }
       for (int t = 0; t < n; ++t, ++g) {
         const uint32_t b = g & 1;
-        uint32_t mword = 0u;
+        const uint32_t mword = mnext;
         if constexpr (MASK) {
-          if (valid_x) mword = p.mask[static_cast<size_t>(x_global) * p.mask_stride + (y0 + t) * 4 + cg];
+          if (valid_x && t + 1 < n) mnext = mrow[(t + 1) * 4];
         }
         if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1, s_abort)) { ok = false; break; }
         if (warp == 2 && lane == 0) stamp(g, 3);
@@ -518,6 +531,7 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.y_rows = y_rows;
   p.nx_tiles = (x_rows + BLOCK_X - 1) / BLOCK_X;
   p.ny_tiles = (y_rows + BLOCK_Y - 1) / BLOCK_Y;
+  p.map = TileMap::make(p.nx_tiles, p.ny_tiles, BLOCK_Y * D * 2, 48ll << 20);
   p.base = base;
   p.scale = scale;
   p.mask = mask;

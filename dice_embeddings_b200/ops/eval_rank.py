@@ -109,7 +109,7 @@ class FusedRanker:
             ix = ix * self.y_stride + self.y_offset
         else:
             kk = min(k, n_local)
-            cap = kernels.eval_rank_cand_cap(B, n_local, kk)
+            cap = kernels.eval_rank_cand_cap(B, n_local, self.d_pad, kk)
             cs = torch.full((B, cap), float("-inf"), dtype=torch.float32, device=self.device)
             ci = torch.full((B, cap), -1, dtype=torch.int32, device=self.device)
             cc = torch.zeros(B, dtype=torch.int32, device=self.device)

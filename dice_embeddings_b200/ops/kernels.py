@@ -235,8 +235,9 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
     _check(rc, "dice_eval_rank")
 
 
-def eval_rank_cand_cap(x_rows: int, y_rows: int, k: int, num_ctas: int = 0) -> int:
-    return int(_lib.lib().dice_eval_rank_cand_cap(int(x_rows), int(y_rows), int(k), int(num_ctas)))
+def eval_rank_cand_cap(x_rows: int, y_rows: int, D: int, k: int, num_ctas: int = 0) -> int:
+    """Capacity (entries per row) the candidate lists of ``eval_rank`` need for this problem shape."""
+    return int(_lib.lib().dice_eval_rank_cand_cap(int(x_rows), int(y_rows), int(D), int(k), int(num_ctas)))
 
 
 def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, target_score: Optional[torch.Tensor],

@@ -1,0 +1,78 @@
+"""Stand-alone timing of the ranking kernel: ``python -m dice_embeddings_b200.ops.profile_eval``.
+
+Times ``eval_rank`` (counting mode and top-k mode) with CUDA events after warm-up, flushing L2 between launches, and
+reports the achieved tensor throughput (one GEMM of ``2·B·|E|·D`` FLOP per launch) as a fraction of the cuBLAS bf16
+figure in ``MEASURED_PEAKS.json``.  With ``--compare`` it also times the PyTorch formulation of the same counts
+(``torch.mm`` per 1024 queries + comparison + row sum).  It is the small, self-terminating program used for ``ncu``
+captures of this kernel."""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from ..utils.profiling import measured_peaks
+from . import kernels as K
+from .eval_rank import FusedRanker
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--queries", type=int, default=4096)
+    ap.add_argument("--entities", type=int, default=262144)
+    ap.add_argument("--d", type=int, default=256)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--topk", type=int, default=0, help="also time top-k mode with this k on the first 256 queries")
+    ap.add_argument("--compare", action="store_true")
+    a = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    q = (torch.randn(a.queries, a.d, device=dev) * 0.3).to(torch.bfloat16)
+    y = (torch.randn(a.entities, a.d, device=dev) * 0.3).to(torch.bfloat16)
+    tgt = torch.randint(0, a.entities, (a.queries,), device=dev, dtype=torch.int32)
+    ts = torch.zeros(a.queries, device=dev)
+    greater = torch.zeros(a.queries, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    K.eval_sparse(q, y, tgt, ts, None)
+    pk = measured_peaks()
+
+    def timed(fn, iters):
+        for _ in range(a.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ms = 0.0
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms += e0.elapsed_time(e1)
+        return ms / iters
+
+    ms = timed(lambda: K.eval_rank(q, y, ts, tgt, greater, status), a.iters)
+    tf = 2.0 * a.queries * a.entities * a.d / (ms * 1e-3) / 1e12
+    print(f"eval_rank  B={a.queries} E={a.entities} D={a.d}: {ms * 1e3:9.1f} us  {tf:7.1f} TFLOP/s  "
+          f"{tf / pk['bf16_tflops']:.2f} of {pk['source']} ({pk['bf16_tflops']:.0f})")
+    if a.topk:
+        r = FusedRanker(y)
+        n = min(256, a.queries)
+        ms = timed(lambda: r.topk(q[:n], a.topk), max(a.iters // 2, 1))
+        print(f"top-{a.topk} of {n} queries over {a.entities} entities: {ms * 1e3:9.1f} us")
+    if a.compare:
+        def torch_counts():
+            out = []
+            for i in range(0, a.queries, 1024):
+                s = q[i:i + 1024] @ y.t()
+                out.append((s > ts[i:i + 1024, None].to(s.dtype)).sum(1))
+            return torch.cat(out)
+        ms = timed(torch_counts, max(a.iters // 3, 1))
+        print(f"torch.mm + compare + sum (1024-query slices): {ms * 1e3:9.1f} us")
+    K.check_status(status)
+
+
+if __name__ == "__main__":
+    main()

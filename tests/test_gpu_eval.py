@@ -99,7 +99,7 @@ def test_eval_rank_bias_and_cyclic_shards_add_up():
     cands = []
     for rank in range(2):
         ys, bs = y[rank::2].contiguous(), bias[rank::2].contiguous()
-        cap = K.eval_rank_cand_cap(nx, ys.shape[0], 5)
+        cap = K.eval_rank_cand_cap(nx, ys.shape[0], D, 5)
         cs = torch.full((nx, cap), float("-inf"), device=DEV)
         ci = torch.full((nx, cap), -1, dtype=torch.int32, device=DEV)
         cc = torch.zeros(nx, dtype=torch.int32, device=DEV)
