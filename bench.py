@@ -115,15 +115,19 @@ def run_ours(args) -> dict:
         import torch.distributed as dist
         dist.init_process_group("nccl", init_method="env://", device_id=dev)
 
-    NE, NR, NT, D, B = 14541, 237, 272115, 256, 4096
-    triples = zipf_kg(NE, NR, NT, 1.1, 1.3, seed=0)
-    ds = KvsAll(triples, NE, NR, "EntityPrediction", label_smoothing_rate=0.1)
+    from dice_embeddings_b200.models import MODEL_REGISTRY
+    c = KVSALL_CONFIGS[args.config]
+    mname = args.model or c["model"]
+    NE, NR, NT, D, B = c["entities"], c["relations"], c["triples"], c["dim"], c["batch"]
+    triples = zipf_kg(NE, NR, NT, c["zipf_e"], c["zipf_r"], seed=0)
+    ds = KvsAll(triples, NE, NR, "EntityPrediction", label_smoothing_rate=c["smoothing"])
     num_pairs = len(ds)
     triples_per_pair = NT / num_pairs
     torch.manual_seed(0)
-    margs = dict(model="ComplEx", embedding_dim=D, num_entities=NE, num_relations=NR, optim="Adam", learning_rate=0.1,
-                 scoring_technique="KvsAll")
-    model = ComplEx(margs).to(dev)
+    margs = dict(model=mname, embedding_dim=D, num_entities=NE, num_relations=NR, optim="Adam", learning_rate=0.1,
+                 scoring_technique="KvsAll", p=0, q=1)
+    with torch.device(dev):   # parameters are created on the GPU: a 10 GB table is not staged through host memory
+        model = MODEL_REGISTRY[mname][0](margs)
 
     if world == 1:
         from dice_embeddings_b200.ops.fused_step import FusedKvsAllEngine
@@ -196,9 +200,10 @@ def run_ours(args) -> dict:
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None if BASELINE_PUBLISHED is None else value / BASELINE_PUBLISHED,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "ComplEx KvsAll d=256", "global_batch": B * world, "seq_len": None,
+        "config": {"model": f"{mname} KvsAll d={D}", "global_batch": B * world, "seq_len": None,
                    "parallelism": parallelism, "entities": NE, "relations": NR, "train_triples": NT,
-                   "data_points": num_pairs, "label_smoothing": 0.1, "optimizer": "Adam lr=0.1",
+                   "data_points": num_pairs, "label_smoothing": c["smoothing"], "optimizer": "Adam lr=0.1",
+                   "labels": engine.label_mode, "note": c["note"],
                    "weights": "random init, fp32 master + bf16 tensor-core operands",
                    "l2": "256 MiB buffer written between timed steps (L2 flush); per-step CUDA events summed"},
         "clocks": clocks,
@@ -210,6 +215,167 @@ def run_ours(args) -> dict:
     if world > 1:
         torch.distributed.destroy_process_group()
     return out if rank == 0 else None
+
+
+def run_ours_cpu(args) -> dict:
+    """Config 1: Keci KvsAll on the CPU through ``Execute(...).start()`` with the generic PyTorch trainer; K steps
+    are timed on the host between optimiser steps, exactly as the reference arm is timed."""
+    import shutil
+    import tempfile
+    import time
+    import torch
+    from torch.optim.optimizer import register_optimizer_step_pre_hook
+    from dice_embeddings_b200 import Execute, Namespace
+    from dice_embeddings_b200.data.synthetic import make_umls_like
+
+    class _Stop(Exception):
+        pass
+
+    base = os.path.join(tempfile.gettempdir(), "dice_ours_bench_c1")
+    shutil.rmtree(base, ignore_errors=True)
+    kg = make_umls_like(os.path.join(base, "kg"), 0)
+    a = Namespace(dataset_dir=kg, path_to_store_single_run=os.path.join(base, "run"), model="Keci", p=0, q=1,
+                  scoring_technique="KvsAll", trainer="torchCPUTrainer", embedding_dim=32, batch_size=1024, lr=0.1,
+                  optim="Adam", label_smoothing_rate=0.0, num_epochs=10 ** 6, eval_model="None", num_core=0,
+                  random_seed=0)
+    st = {"n": 0, "t0": None, "t1": None}
+
+    def tick(opt, a_, k_):
+        if st["n"] == args.warmup:
+            st["t0"] = time.perf_counter()
+        elif st["n"] == args.warmup + args.steps:
+            st["t1"] = time.perf_counter()
+            raise _Stop()
+        st["n"] += 1
+
+    handle = register_optimizer_step_pre_hook(tick)
+    torch.manual_seed(0)
+    try:
+        Execute(a).start()
+        raise RuntimeError("training finished before the requested number of steps")
+    except _Stop:
+        pass
+    finally:
+        handle.remove()
+    ms = (st["t1"] - st["t0"]) * 1e3
+    import numpy as np
+    train = np.load(os.path.join(base, "run", "train_set.npy"))
+    pairs = len({(int(h), int(r)) for h, r, _ in train})
+    steps_per_epoch = -(-pairs // 1024)
+    triples_per_step = len(train) / steps_per_epoch
+    value = triples_per_step * args.steps / (ms / 1e3)
+    return {"metric": "train triples/sec (host-timed, CPU)", "value": value, "unit": "triples/s", "n_gpus": 0,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "ours",
+            "config": {"model": "Keci KvsAll d=32", "global_batch": 1024, "seq_len": None,
+                       "parallelism": "single process, CPU", "entities": 135, "relations": 46,
+                       "train_triples": int(len(train)), "data_points": pairs}, "gpu_launches": 0}
+
+
+def run_eval(args) -> dict:
+    """Config 5: filtered link-prediction ranks and top-10 over a (row-sharded) 10 M x 256 ComplEx table.
+
+    Every rank holds the cyclic shard ``rank::world`` of the bf16 table; queries are composed from random-init ComplEx
+    embeddings of (h, r) pairs drawn from a Zipf triple distribution, every query has the target plus 15 further
+    known tails as its filter.  Timed region per batch of 8192 queries: target scores, filtered counts, the tcgen05
+    counting GEMM, the cross-rank sums and a read-back of the ranks; top-10 is timed separately on 1024 queries."""
+    import numpy as np
+    import torch
+    from dice_embeddings_b200.evaluation.ranking import metrics_from_ranks
+    from dice_embeddings_b200.ops.eval_rank import FusedRanker
+    rank, local_rank, world = _dist_env()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", init_method="env://", device_id=dev)
+        group = dist.group.WORLD
+    NE, D, NQ, QB, NF = 10_000_000, 256, 98304, 8192, 16
+    g = torch.Generator(device=dev).manual_seed(7)
+    rows = (NE - rank + world - 1) // world
+    shard = (torch.randn(rows, D, device=dev, generator=g) * 0.05).to(torch.bfloat16)   # random-init table shard
+    ranker = FusedRanker(shard, y_offset=rank, y_stride=world, group=group)
+    gq = torch.Generator().manual_seed(11)                                              # same queries on every rank
+    u = torch.rand(NQ, NF, generator=gq)
+    tails = (NE * u ** 3).long().clamp_(max=NE - 1)        # heavy-tailed ids standing in for Zipf degrees
+    q_host = (torch.randn(NQ, D, generator=gq) * 0.05).pin_memory()
+    tgt_host = tails[:, 0].contiguous().pin_memory()
+    ptr = (torch.arange(QB + 1) * NF).to(dev)
+    nb = NQ // QB
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ranks_out = []
+
+    def one(i):
+        sl = slice(i * QB, (i + 1) * QB)
+        q = q_host[sl].to(dev, non_blocking=True)
+        t = tgt_host[sl].to(dev, non_blocking=True)
+        cols = tails[sl].reshape(-1).to(dev, non_blocking=True).to(torch.int32)
+        r = ranker.ranks(q, t, ptr, cols)
+        return r.cpu()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    for i in range(min(args.warmup, nb)):
+        one(i)
+    barrier()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    steps = min(args.steps, nb)
+    ms = 0.0
+    for i in range(steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ranks_out.append(one(i))
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms += e0.elapsed_time(e1)
+    barrier()
+    qk = q_host[:1024].to(dev)
+    ranker.topk(qk, 10)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    ranker.topk(qk, 10)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms_topk = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler is not None else None
+    if world > 1:
+        t = torch.tensor([ms, ms_topk], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, ms_topk = float(t[0]), float(t[1])
+        torch.distributed.destroy_process_group()
+    met = metrics_from_ranks(torch.cat(ranks_out))
+    value = QB * steps / (ms / 1e3)
+    out = {"metric": "eval queries/s (filtered ranks over all entities, device-timed incl. H2D of queries and D2H of ranks)",
+           "value": value, "unit": "queries/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+           "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "bf16", "data": "synthetic", "impl": "ours",
+           "config": {"model": "ComplEx d=256 (random init)", "global_batch": QB, "seq_len": None,
+                      "parallelism": f"cyclic row shards x{world}", "entities": NE, "queries": QB * steps,
+                      "filter_size": NF, "l2": "256 MiB buffer written between timed batches",
+                      "topk10_ms_per_1024_queries": ms_topk, "metrics_random_init": met},
+           "clocks": clocks,
+           "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": QB * D * 4 + QB * 8 + QB * NF * 8,
+                   "d2h_bytes_per_step": QB * 8, "note": "the timed region is already end to end"},
+           "gpu_launches": 2 * steps + 2}
+    return out if rank == 0 else None
+
+
+# KvsAll training configurations (numbering of the benchmark list): 2 = FB15k-237-shaped headline config, 3 = a
+# 10 M x 256 entity table.  Config 3 stores 4 M synthetic triples instead of 500 M: the step scores the batch
+# against all entities, so its cost depends on batch and table size, not on the number of stored triples.
+KVSALL_CONFIGS = {
+    2: dict(model="ComplEx", entities=14541, relations=237, triples=272115, dim=256, batch=4096, zipf_e=1.1,
+            zipf_r=1.3, smoothing=0.1, note="headline config"),
+    3: dict(model="DistMult", entities=10_000_000, relations=1000, triples=4_000_000, dim=256, batch=65536,
+            zipf_e=1.05, zipf_r=1.3, smoothing=0.1,
+            note="full-size 10M x 256 table and 65536-query batch; triple store scaled to 4M triples"),
+}
 
 
 # ------------------------------------------------------------------------------------------ reference arm
@@ -258,11 +424,19 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 5])
+    ap.add_argument("--model", default=None, help="override the model of the chosen config (ours arm)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        res = run_reference(args)
+    elif args.config == 1:
+        res = run_ours_cpu(args)
+    elif args.config == 5:
+        res = run_eval(args)
+    else:
+        res = run_ours(args)
     if res is not None:
         print(json.dumps(res), flush=True)
 

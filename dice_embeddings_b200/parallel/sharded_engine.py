@@ -64,7 +64,7 @@ def scatter_shard_back(full: torch.Tensor, shard: torch.Tensor, rank: int, world
 
 class ShardedKvsAllEngine:
     def __init__(self, model, dataset, batch_size: int, lr: float, weight_decay: float = 0.0, device=None,
-                 comm: str = "p2p", group=None, use_graph: bool = True):
+                 comm: str = "p2p", group=None, use_graph: bool = True, label_mode: Optional[str] = None):
         assert dist.is_initialized(), "ShardedKvsAllEngine needs an initialised process group"
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.W = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -143,8 +143,18 @@ class ShardedKvsAllEngine:
         self.r = torch.zeros(B, dtype=torch.int64, device=dev)
         self.dp = torch.zeros(B, dtype=torch.int64, device=dev)
         self.x_in = torch.zeros(B, 2, dtype=torch.int64, device=dev)
-        self.mask_q = torch.zeros(W * B, K.mask_stride(self.rows_pad), dtype=torch.int32, device=dev)
-        self.mask_e = torch.zeros(self.rows_pad, K.mask_stride(W * B), dtype=torch.int32, device=dev)
+        # labels: bit masks of the positives in both orientations while they fit a modest budget, else the sparse
+        # correction kernels driven by the CSR (tables of millions of rows)
+        mask_bytes = 2.0 * W * B * self.rows_pad / 8
+        self.label_mode = label_mode or ("mask" if mask_bytes <= (1 << 30) else "sparse")
+        assert self.label_mode in ("mask", "sparse")
+        if self.label_mode == "mask":
+            self.mask_q = torch.zeros(W * B, K.mask_stride(self.rows_pad), dtype=torch.int32, device=dev)
+            self.mask_e = torch.zeros(self.rows_pad, K.mask_stride(W * B), dtype=torch.int32, device=dev)
+        else:
+            assert comm == "p2p", "the sparse label path is implemented for the peer-memory flavour"
+            self.mask_q = self.mask_e = None
+            self.first = torch.zeros(W * B + 1, dtype=torch.int32, device=dev)
         if comm == "nccl":
             self._init_nccl_buffers()
         self._graph = None
@@ -202,15 +212,18 @@ class ShardedKvsAllEngine:
         self.gR.zero_()
         self.gC.zero_()
         self.loss_acc.zero_()
-        self.mask_q.zero_()
-        self.mask_e.zero_()
+        masks = self.label_mode == "mask"
+        if masks:
+            self.mask_q.zero_()
+            self.mask_e.zero_()
         K.lookup_compose(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.NE, self.R, self.coeff,
                          self.tab.Q, W, self.rank * B, None, B, D, self.status, dp_src=self.dp, dp_dst_table=self.tab.dp)
         self._mark("zero+lookup")
         self._barrier()                                   # S1: all query rows have landed everywhere
         self._mark("S1")
-        K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
-        self._mark("masks")
+        if masks:
+            K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
+            self._mark("masks")
         e_loc = self.E_bf16[: self.rows]
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
                        mask=self.mask_e, pos_delta=self.pos_weight)
@@ -218,6 +231,13 @@ class ShardedKvsAllEngine:
         K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
                        out_table=self.tab.dQ, out_block_rows=B, mask=self.mask_q, pos_delta=self.pos_weight)
         self._mark("fused_Q+rs")
+        if not masks:
+            # label term of the positives whose tail lives in this shard: loss, dE rows here, dQ rows at their owners
+            K.positive_scan(self.dp_all, self.offsets, n, self.first)
+            K.positive_correction(self.dp_all, self.offsets, self.values, self.first, self.Q, self.E_bf16, self.dQ,
+                                  self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, W, self.rank,
+                                  dq_table=self.tab.dQ, dq_block_rows=B)
+            self._mark("positives")
         self._barrier()                                   # S2: every rank's dQ block is complete
         self._mark("S2")
         K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, self.dQ,
@@ -230,7 +250,9 @@ class ShardedKvsAllEngine:
         self._mark("optim")
 
     def launches_per_step(self) -> int:
-        return 4 + 9 + (1 if self.coeff_trainable else 0) if self.comm == "p2p" else 9
+        if self.comm != "p2p":
+            return 9
+        return 4 + (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
 
     # ------------------------------------------------------------------ the step, collective flavour
     def _init_nccl_buffers(self) -> None:

@@ -42,10 +42,11 @@ def main():
 
     g = torch.Generator().manual_seed(5)
     results = {}
-    for comm in ("p2p", "nccl"):
+    for comm in ("p2p", "p2p-sparse", "nccl"):
         ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(dev)
         model = make()
-        eng = ShardedKvsAllEngine(model, ds, batch_size=B, lr=lr, device=dev, comm=comm)
+        eng = ShardedKvsAllEngine(model, ds, batch_size=B, lr=lr, device=dev, comm=comm.split("-")[0],
+                                  label_mode="sparse" if comm.endswith("sparse") else "mask")
         g.manual_seed(5)
         losses = []
         for _ in range(steps):
@@ -65,6 +66,13 @@ def main():
     d_r = (rp - rn).abs().max().item() / rn.abs().max().item()
     ok &= d_e < 2e-2 and d_r < 2e-2
     msg.append(f"p2p vs nccl: losses {lp} / {ln}; rel diff E {d_e:.2e} R {d_r:.2e}")
+    lsp, esp, rsp = results["p2p-sparse"]
+    for a, b in zip(lsp, lp):
+        ok &= abs(a - b) < 2e-3 * abs(b) + 1e-6
+    d_e = (esp - ep).abs().max().item() / ep.abs().max().item()
+    d_r = (rsp - rp).abs().max().item() / rp.abs().max().item()
+    ok &= d_e < 2e-2 and d_r < 2e-2
+    msg.append(f"sparse labels vs masks: losses {lsp} / {lp}; rel diff E {d_e:.2e} R {d_r:.2e}")
     if rank == 0:
         ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(dev)
         model = make()
