@@ -154,6 +154,7 @@ struct ComposeBwdParams {
   float* g_coeff;              // single float or null
   int B, D, W, norm_mode;
   int additive;
+  unsigned char* const* touched;  // optional [W] per-row flags of the gradient shards: set where a row gets a gradient
 };
 
 template <int K, int VEC>
@@ -233,6 +234,7 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
     }
     float* ge = p.g_ent[h % p.W] + (h / p.W) * p.D;
     float* gr = p.g_rel + r_id * p.D;
+    if (p.touched != nullptr && j0 == 0) p.touched[h % p.W][h / p.W] = 1;
 #pragma unroll
     for (int a = 0; a < K; ++a)
 #pragma unroll
@@ -601,9 +603,9 @@ extern "C" int dice_lookup_compose(int model, int normalize, const long long* id
 extern "C" int dice_compose_backward(int model, int normalize, const long long* idx_h, const long long* idx_r,
                                      const float* const* ent, int W, const float* rel, const float* coeff,
                                      const float* dq, float* const* g_ent, float* g_rel, float* g_coeff, int B, int D,
-                                     void* stream) {
+                                     unsigned char* const* touched, void* stream) {
   if (B <= 0) return 0;
-  ComposeBwdParams p{idx_h, idx_r, ent, rel, nullptr, dq, g_ent, g_rel, nullptr, B, D, W, NORM_NONE};
+  ComposeBwdParams p{idx_h, idx_r, ent, rel, nullptr, dq, g_ent, g_rel, nullptr, B, D, W, NORM_NONE, 0, touched};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (model) {
     case 0: return launch_bwd<1, 1>(p, s);

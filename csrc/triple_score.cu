@@ -43,13 +43,18 @@ __device__ __forceinline__ long long bounded(uint32_t a, uint32_t b, long long h
 }
 
 __global__ void uniform_int_kernel(long long* __restrict__ out, long long n, long long high, unsigned long long seed,
-                                   unsigned long long offset) {
+                                   unsigned long long offset, const long long* __restrict__ step_ptr,
+                                   long long out_stride, long long row_len) {
   const Philox rng(seed);
+  if (step_ptr != nullptr) offset += static_cast<unsigned long long>(*step_ptr);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; 2 * i < n; i += stride) {
     const uint4 r = rng(static_cast<unsigned long long>(i), offset);
-    out[2 * i] = bounded(r.x, r.y, high);
-    if (2 * i + 1 < n) out[2 * i + 1] = bounded(r.z, r.w, high);
+    // element j of the flat sequence lands at row j / row_len, column j % row_len of a matrix with row stride
+    // out_stride (row_len == out_stride == n for a plain vector)
+    const long long j0 = 2 * i, j1 = 2 * i + 1;
+    out[(j0 / row_len) * out_stride + j0 % row_len] = bounded(r.x, r.y, high);
+    if (j1 < n) out[(j1 / row_len) * out_stride + j1 % row_len] = bounded(r.z, r.w, high);
   }
 }
 
@@ -101,6 +106,7 @@ struct CandParams {
   const float* labels;        // [N, C] targets in [0, 1]
   const float* const* ent;    // [W] fp32 entity shards, entity e lives in shard e % W at row e / W
   float* const* g_ent;        // [W] gradient shards (red.add); null = forward only
+  unsigned char* const* touched;  // optional [W] per-row flags of the gradient shards
   float* dq;                  // [N, D] gradient w.r.t. q (written, not accumulated); null = forward only
   float* scores;              // [N, C] or null
   double* loss;               // accumulator of sum(BCE) * scale, or null
@@ -164,6 +170,7 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
       if (p.dq == nullptr) continue;
       float g = (1.f / (1.f + expf(-s)) - y) * p.scale;  // dL/ds
       float* grow = p.g_ent[e % p.W] + row;
+      if (p.touched != nullptr && lane == 0) p.touched[e % p.W][e / p.W] = 1;
       if (p.kind == 0) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
@@ -200,17 +207,107 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
   if (p.loss != nullptr && lane == 0 && loss_local != 0.0) atomicAdd(p.loss, loss_local * p.scale);
 }
 
+// ------------------------------------------------------------------------------------ row-wise sparse optimiser
+// One warp per group of 32 rows: the flags are read with one coalesced load, then the warp walks the flagged rows.
+// Only rows that received a gradient are touched: their moments decay lazily (as in torch.optim.SparseAdam), the
+// bias correction uses the global step.  The gradient row and the flag are cleared on the way out.
+struct SparseOptParams {
+  float* param;
+  float* grad;
+  float* m;
+  float* v;
+  __nv_bfloat16* shadow;      // optional bf16 copy of the parameters, refreshed for updated rows
+  unsigned char* touched;
+  long long rows;
+  int D, kind;                // 0 Adam, 1 AdamW, 2 SGD
+  const long long* step;      // completed steps (the update uses step + 1)
+  float lr, beta1, beta2, eps, weight_decay;
+};
+
+__global__ void __launch_bounds__(256) sparse_rows_optimizer_kernel(const SparseOptParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const float t = static_cast<float>(*p.step + 1);
+  const float bc1 = 1.f - exp2f(t * log2f(p.beta1)), bc2 = 1.f - exp2f(t * log2f(p.beta2));
+  for (long long base = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * 32; base < p.rows;
+       base += warps * 32) {
+    const long long mine = base + lane;
+    const bool flag = mine < p.rows && p.touched[mine] != 0;
+    unsigned int todo = __ballot_sync(0xffffffffu, flag);
+    if (flag) p.touched[mine] = 0;
+    while (todo) {
+      const int k = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const size_t off = static_cast<size_t>(base + k) * p.D;
+      for (int d = lane * 4; d < p.D; d += 128) {
+        const float4 g4 = *reinterpret_cast<const float4*>(p.grad + off + d);
+        const float4 w4 = *reinterpret_cast<const float4*>(p.param + off + d);
+        *reinterpret_cast<float4*>(p.grad + off + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+        float gp[4] = {g4.x, g4.y, g4.z, g4.w};
+        float wp[4] = {w4.x, w4.y, w4.z, w4.w};
+        if (p.kind == 2) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) wp[u] -= p.lr * (gp[u] + p.weight_decay * wp[u]);
+        } else {
+          const float4 m4 = *reinterpret_cast<const float4*>(p.m + off + d);
+          const float4 v4 = *reinterpret_cast<const float4*>(p.v + off + d);
+          float mp[4] = {m4.x, m4.y, m4.z, m4.w};
+          float vp[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float gu = gp[u];
+            if (p.kind == 0) gu += p.weight_decay * wp[u];
+            else wp[u] *= 1.f - p.lr * p.weight_decay;
+            mp[u] = p.beta1 * mp[u] + (1.f - p.beta1) * gu;
+            vp[u] = p.beta2 * vp[u] + (1.f - p.beta2) * gu * gu;
+            wp[u] -= p.lr * (mp[u] / bc1) / (sqrtf(vp[u] / bc2) + p.eps);
+          }
+          *reinterpret_cast<float4*>(p.m + off + d) = make_float4(mp[0], mp[1], mp[2], mp[3]);
+          *reinterpret_cast<float4*>(p.v + off + d) = make_float4(vp[0], vp[1], vp[2], vp[3]);
+        }
+        *reinterpret_cast<float4*>(p.param + off + d) = make_float4(wp[0], wp[1], wp[2], wp[3]);
+        if (p.shadow != nullptr) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(wp[0], wp[1]), hi = __floats2bfloat162_rn(wp[2], wp[3]);
+          uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          *reinterpret_cast<uint2*>(p.shadow + off + d) = pk;
+        }
+      }
+    }
+  }
+}
+
 }  // namespace triple
 }  // namespace dice
 
+// Row-wise sparse update of a [rows, D] table: rows with touched[row] != 0 are updated from grad (then grad row and
+// flag are cleared), all other rows are left alone.  kind: 0 Adam, 1 AdamW, 2 SGD.  D must be a multiple of 4.
+extern "C" int dice_sparse_rows_optimizer(int kind, float* param, float* grad, float* m, float* v, void* shadow,
+                                          unsigned char* touched, long long rows, int D, const long long* step,
+                                          float lr, float beta1, float beta2, float eps, float weight_decay,
+                                          void* stream) {
+  using namespace dice::triple;
+  if (rows <= 0) return 0;
+  if (D % 4 || kind < 0 || kind > 2) return -6;
+  SparseOptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), touched, rows, D, kind, step, lr, beta1,
+                    beta2, eps, weight_decay};
+  long long blocks = ((rows + 31) / 32 * 32 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  sparse_rows_optimizer_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// With row_len > 0 the n draws fill a [n / row_len, row_len] block of a matrix whose rows are out_stride apart
+// (e.g. the negative columns of a candidate matrix); step_ptr (optional, device) is added to offset.
 extern "C" int dice_uniform_int(long long* out, long long n, long long high, unsigned long long seed,
-                                unsigned long long offset, void* stream) {
+                                unsigned long long offset, const long long* step_ptr, long long out_stride,
+                                long long row_len, void* stream) {
   if (n <= 0) return 0;
   if (high <= 0) return -6;
+  if (row_len <= 0) { row_len = n; out_stride = n; }
   long long blocks = ((n + 1) / 2 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   dice::triple::uniform_int_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      out, n, high, seed, offset);
+      out, n, high, seed, offset, step_ptr, out_stride, row_len);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -235,12 +332,13 @@ extern "C" int dice_neg_sample(const long long* pos, int B, int k, long long num
 extern "C" int dice_candidate_bce(const float* q, const long long* cand, long long cand_stride, long long cand_step,
                                   int C, const float* labels, const float* const* ent, float* const* g_ent, float* dq,
                                   float* scores, double* loss, float scale, int kind, float margin, float eps, int N,
-                                  int D, int W, void* stream) {
+                                  int D, int W, unsigned char* const* touched, void* stream) {
   using namespace dice::triple;
   if (N <= 0 || C <= 0) return 0;
   if (D % 4 || D > 512 || W <= 0) return -6;
   if ((dq == nullptr) != (g_ent == nullptr)) return -6;
-  CandParams p{q, cand, cand_stride, cand_step, C, labels, ent, g_ent, dq, scores, loss, scale, margin, eps, N, D, W, kind};
+  CandParams p{q, cand, cand_stride, cand_step, C, labels, ent, g_ent, touched, dq, scores, loss, scale, margin, eps,
+               N, D, W, kind};
   const int threads = 256;
   long long blocks = (static_cast<long long>(N) * 32 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;

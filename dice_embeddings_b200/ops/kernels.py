@@ -80,10 +80,10 @@ def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.T
 
 
 def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: int, rel, coeff, dq, g_ent_table,
-                     g_rel, g_coeff, B: int, D: int) -> None:
+                     g_rel, g_coeff, B: int, D: int, touched_table: Optional[torch.Tensor] = None) -> None:
     rc = _lib.lib().dice_compose_backward(model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
                                           _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(g_ent_table), _ptr(g_rel),
-                                          _ptr(g_coeff), B, D, _stream())
+                                          _ptr(g_coeff), B, D, _ptr(touched_table), _stream())
     _check(rc, "dice_compose_backward")
 
 
@@ -148,11 +148,20 @@ def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
     _lib.lib().dice_kvsall_set_trace(_ptr(buffer))
 
 
-def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0) -> None:
-    """Fill ``out`` (int64) with uniform integers in ``[0, high)`` from the counter-based generator."""
-    _req(out, torch.int64, "out")
+def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0, step: Optional[torch.Tensor] = None) -> None:
+    """Fill ``out`` (int64; a contiguous tensor or a column block ``m[:, a:b]`` of a contiguous matrix) with uniform
+    integers in ``[0, high)`` from the counter-based generator.  ``step`` (device int64 scalar) is added to ``offset``
+    on the device, so a captured launch draws fresh numbers at every replay."""
+    if not out.is_cuda or out.dtype != torch.int64:
+        raise KernelError("out: expected a CUDA int64 tensor")
+    if out.is_contiguous():
+        stride, row_len = 0, 0
+    else:
+        assert out.dim() == 2 and out.stride(1) == 1, "only column blocks of a row-major matrix are supported"
+        stride, row_len = out.stride(0), out.shape[1]
     _check(_lib.lib().dice_uniform_int(_ptr(out), out.numel(), int(high), int(seed) & (2 ** 64 - 1),
-                                       int(offset) & (2 ** 64 - 1), _stream()), "dice_uniform_int")
+                                       int(offset) & (2 ** 64 - 1), _ptr(step), int(stride), int(row_len),
+                                       _stream()), "dice_uniform_int")
 
 
 def neg_sample(pos: torch.Tensor, k: int, num_entities: int, seed: int, offset: int, y: torch.Tensor,
@@ -186,7 +195,8 @@ def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_st
                   labels: Optional[torch.Tensor], ent_table: torch.Tensor, W: int,
                   g_ent_table: Optional[torch.Tensor] = None, dq: Optional[torch.Tensor] = None,
                   scores: Optional[torch.Tensor] = None, loss_acc: Optional[torch.Tensor] = None,
-                  scale: float = 1.0, kind: int = 0, margin: float = 0.0, eps: float = 0.0) -> None:
+                  scale: float = 1.0, kind: int = 0, margin: float = 0.0, eps: float = 0.0,
+                  touched_table: Optional[torch.Tensor] = None) -> None:
     """Scores of every query against its own candidate list, BCE loss and gradients (see ``dice_candidate_bce``)."""
     _req(q, torch.float32, "q")
     _req(cand, torch.int64, "cand")
@@ -200,7 +210,18 @@ def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_st
     _check(_lib.lib().dice_candidate_bce(_ptr(q), _ptr(cand), int(cand_stride), int(cand_step), int(C), _ptr(labels),
                                          _ptr(ent_table), _ptr(g_ent_table), _ptr(dq), _ptr(scores), _ptr(loss_acc),
                                          float(scale), int(kind), float(margin), float(eps), N, D, int(W),
-                                         _stream()), "dice_candidate_bce")
+                                         _ptr(touched_table), _stream()), "dice_candidate_bce")
+
+
+def sparse_rows_optimizer(kind: int, param, grad, m, v, shadow, touched: torch.Tensor, step, lr, beta1, beta2, eps,
+                          weight_decay) -> None:
+    """Update only the rows of ``param [rows, D]`` whose ``touched`` flag (uint8) is set; clears flag and gradient."""
+    _req(touched, torch.uint8, "touched")
+    rows, D = param.shape
+    _check(_lib.lib().dice_sparse_rows_optimizer(int(kind), _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow),
+                                                 _ptr(touched), int(rows), int(D), _ptr(step), float(lr),
+                                                 float(beta1), float(beta2), float(eps), float(weight_decay),
+                                                 _stream()), "dice_sparse_rows_optimizer")
 
 
 def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], target_idx: Optional[torch.Tensor],

@@ -127,3 +127,33 @@ def test_negsample_training_with_device_sampling_learns(umls_like_dir, tmp_path)
                             num_epochs=150, batch_size=1024, lr=0.1, gpus=0, kernel_backend="cuda",
                             trainer="torchCPUTrainer", eval_model="train_val_test")).start()
     assert rep["Train"]["MRR"] > 0.35, rep["Train"]
+
+
+@pytest.mark.parametrize("kind,name", [(0, "Adam"), (2, "SGD")])
+def test_sparse_rows_optimizer_updates_only_flagged_rows(kind, name):
+    torch.manual_seed(0)
+    rows, D = 1000, 128
+    p = torch.randn(rows, D, device=DEV)
+    g = torch.randn(rows, D, device=DEV)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    touched = (torch.rand(rows, device=DEV) < 0.3).to(torch.uint8)
+    step = torch.zeros(1, dtype=torch.int64, device=DEV)
+    ref = p.clone().requires_grad_(True)
+    opt = torch.optim.Adam([ref], lr=0.01) if kind == 0 else torch.optim.SGD([ref], lr=0.01)
+    ref.grad = g * touched[:, None].float()
+    opt.step()
+    p0, sel = p.clone(), touched.bool().clone()
+    K.sparse_rows_optimizer(kind, p, g, m, v, None, touched, step, 0.01, 0.9, 0.999, 1e-8, 0.0)
+    torch.cuda.synchronize()
+    assert torch.equal(p[~sel], p0[~sel])                       # untouched rows are not even read
+    assert torch.allclose(p[sel], ref.detach()[sel], atol=1e-5, rtol=1e-4)
+    assert int(touched.sum()) == 0 and float(g[sel].abs().sum()) == 0.0 and float(g[~sel].abs().sum()) > 0
+
+
+def test_uniform_int_into_column_block():
+    cand = torch.full((300, 9), -1, dtype=torch.int64, device=DEV)
+    K.uniform_int(cand[:, 1:], 50, seed=3)
+    assert (cand[:, 0] == -1).all() and cand[:, 1:].min() >= 0 and cand[:, 1:].max() < 50
+    flat = torch.empty(300 * 8, dtype=torch.int64, device=DEV)
+    K.uniform_int(flat, 50, seed=3)
+    assert torch.equal(flat.view(300, 8), cand[:, 1:])

@@ -31,3 +31,12 @@ def test_sharded_checkpoint_resume_and_sharded_ranking():
            "--master-addr", "127.0.0.1", "--master-port", "29613", os.path.join(HERE, "_sharded_eval_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0 and "SHARDED_EVAL_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def test_sharded_sampled_engine_matches_autograd_and_learns():
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29615", os.path.join(HERE, "_sharded_sampled_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0 and "SHARDED_SAMPLED_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
