@@ -116,8 +116,9 @@ struct CandParams {
   int N, D, W, kind;          // kind 0: dot product, 1: negative Euclidean distance
 };
 
-// One warp per query: the query stays in registers while its candidates stream through.
-template <int NV>  // float4 chunks per lane: D <= NV * 128
+// One warp per query: the query stays in registers while its candidates stream through, CH candidate rows in flight
+// at a time (their loads are all issued before the first dot product is reduced).
+template <int NV, int CH>  // float4 chunks per lane (D <= NV * 128), candidates in flight
 __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) {
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -131,67 +132,90 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
                       : make_float4(0.f, 0.f, 0.f, 0.f);
       dqv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int c = 0; c < p.C; ++c) {
-      const long long e = p.cand[n * p.cand_stride + c * p.cand_step];
-      const size_t row = static_cast<size_t>(e / p.W) * p.D;
-      const float* trow = p.ent[e % p.W] + row;
-      float4 tv[NV];
-      float acc = 0.f;
+    for (int c0 = 0; c0 < p.C; c0 += CH) {
+      long long ent_id[CH];
+      float4 tv[CH][NV];
+      float acc[CH];
 #pragma unroll
-      for (int v = 0; v < NV; ++v) {
-        const int d = (v * 32 + lane) * 4;
-        if (d < p.D) {
-          tv[v] = *reinterpret_cast<const float4*>(trow + d);
-          if (p.kind == 0) {
-            acc = fmaf(qv[v].x, tv[v].x, acc); acc = fmaf(qv[v].y, tv[v].y, acc);
-            acc = fmaf(qv[v].z, tv[v].z, acc); acc = fmaf(qv[v].w, tv[v].w, acc);
-          } else {
-            const float a = qv[v].x + p.eps - tv[v].x, b = qv[v].y + p.eps - tv[v].y;
-            const float cc = qv[v].z + p.eps - tv[v].z, dd = qv[v].w + p.eps - tv[v].w;
-            acc += a * a + b * b + cc * cc + dd * dd;
+      for (int j = 0; j < CH; ++j) {
+        const int c = c0 + j < p.C ? c0 + j : c0;   // the tail of the list repeats a valid candidate; results are dropped
+        ent_id[j] = p.cand[n * p.cand_stride + c * p.cand_step];
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const float* trow = p.ent[ent_id[j] % p.W] + static_cast<size_t>(ent_id[j] / p.W) * p.D;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int d = (v * 32 + lane) * 4;
+          tv[j][v] = d < p.D ? *reinterpret_cast<const float4*>(trow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        float a = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int d = (v * 32 + lane) * 4;
+          if (d < p.D) {
+            if (p.kind == 0) {
+              a = fmaf(qv[v].x, tv[j][v].x, a); a = fmaf(qv[v].y, tv[j][v].y, a);
+              a = fmaf(qv[v].z, tv[j][v].z, a); a = fmaf(qv[v].w, tv[j][v].w, a);
+            } else {
+              const float x0 = qv[v].x + p.eps - tv[j][v].x, x1 = qv[v].y + p.eps - tv[j][v].y;
+              const float x2 = qv[v].z + p.eps - tv[j][v].z, x3 = qv[v].w + p.eps - tv[j][v].w;
+              a += x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3;
+            }
+          }
+        }
+        acc[j] = a;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int c = c0 + j;
+        if (c >= p.C) continue;
+        float dist = 0.f;
+        float s = acc[j];
+        if (p.kind == 1) {
+          dist = sqrtf(acc[j]);
+          s = p.margin - dist;
+        }
+        const size_t flat = static_cast<size_t>(n) * p.C + c;
+        if (lane == 0 && p.scores != nullptr) p.scores[flat] = s;
+        if (p.labels == nullptr) continue;
+        const float y = p.labels[flat];
+        if (lane == 0) loss_local += static_cast<double>(fmaxf(s, 0.f) - s * y + log1pf(expf(-fabsf(s))));
+        if (p.dq == nullptr) continue;
+        float g = (1.f / (1.f + expf(-s)) - y) * p.scale;  // dL/ds
+        const long long e = ent_id[j];
+        float* grow = p.g_ent[e % p.W] + static_cast<size_t>(e / p.W) * p.D;
+        if (p.touched != nullptr && lane == 0) p.touched[e % p.W][e / p.W] = 1;
+        if (p.kind == 0) {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            const int d = (v * 32 + lane) * 4;
+            if (d < p.D) {
+              dqv[v].x = fmaf(g, tv[j][v].x, dqv[v].x); dqv[v].y = fmaf(g, tv[j][v].y, dqv[v].y);
+              dqv[v].z = fmaf(g, tv[j][v].z, dqv[v].z); dqv[v].w = fmaf(g, tv[j][v].w, dqv[v].w);
+              red_add_v4(grow + d, g * qv[v].x, g * qv[v].y, g * qv[v].z, g * qv[v].w);
+            }
           }
         } else {
-          tv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-      }
+          // s = margin - dist, d dist / d q = (q + eps - t) / dist
+          g = dist > 0.f ? -g / dist : 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      float dist = 0.f;
-      float s = acc;
-      if (p.kind == 1) {
-        dist = sqrtf(acc);
-        s = p.margin - dist;
-      }
-      const size_t flat = static_cast<size_t>(n) * p.C + c;
-      if (lane == 0 && p.scores != nullptr) p.scores[flat] = s;
-      if (p.labels == nullptr) continue;
-      const float y = p.labels[flat];
-      if (lane == 0) loss_local += static_cast<double>(fmaxf(s, 0.f) - s * y + log1pf(expf(-fabsf(s))));
-      if (p.dq == nullptr) continue;
-      float g = (1.f / (1.f + expf(-s)) - y) * p.scale;  // dL/ds
-      float* grow = p.g_ent[e % p.W] + row;
-      if (p.touched != nullptr && lane == 0) p.touched[e % p.W][e / p.W] = 1;
-      if (p.kind == 0) {
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          const int d = (v * 32 + lane) * 4;
-          if (d < p.D) {
-            dqv[v].x = fmaf(g, tv[v].x, dqv[v].x); dqv[v].y = fmaf(g, tv[v].y, dqv[v].y);
-            dqv[v].z = fmaf(g, tv[v].z, dqv[v].z); dqv[v].w = fmaf(g, tv[v].w, dqv[v].w);
-            red_add_v4(grow + d, g * qv[v].x, g * qv[v].y, g * qv[v].z, g * qv[v].w);
-          }
-        }
-      } else {
-        // s = margin - dist, d dist / d q = (q + eps - t) / dist
-        g = dist > 0.f ? -g / dist : 0.f;
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          const int d = (v * 32 + lane) * 4;
-          if (d < p.D) {
-            const float a = g * (qv[v].x + p.eps - tv[v].x), b = g * (qv[v].y + p.eps - tv[v].y);
-            const float cc = g * (qv[v].z + p.eps - tv[v].z), dd = g * (qv[v].w + p.eps - tv[v].w);
-            dqv[v].x += a; dqv[v].y += b; dqv[v].z += cc; dqv[v].w += dd;
-            red_add_v4(grow + d, -a, -b, -cc, -dd);
+          for (int v = 0; v < NV; ++v) {
+            const int d = (v * 32 + lane) * 4;
+            if (d < p.D) {
+              const float x0 = g * (qv[v].x + p.eps - tv[j][v].x), x1 = g * (qv[v].y + p.eps - tv[j][v].y);
+              const float x2 = g * (qv[v].z + p.eps - tv[j][v].z), x3 = g * (qv[v].w + p.eps - tv[j][v].w);
+              dqv[v].x += x0; dqv[v].y += x1; dqv[v].z += x2; dqv[v].w += x3;
+              red_add_v4(grow + d, -x0, -x1, -x2, -x3);
+            }
           }
         }
       }
@@ -208,16 +232,15 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
 }
 
 // ------------------------------------------------------------------------------------ row-wise sparse optimiser
-// One warp per group of 32 rows: the flags are read with one coalesced load, then the warp walks the flagged rows.
 // Only rows that received a gradient are touched: their moments decay lazily (as in torch.optim.SparseAdam), the
 // bias correction uses the global step.  The gradient row and the flag are cleared on the way out.
 struct SparseOptParams {
-  float* param;
-  float* grad;
-  float* m;
-  float* v;
-  __nv_bfloat16* shadow;      // optional bf16 copy of the parameters, refreshed for updated rows
-  unsigned char* touched;
+  float* __restrict__ param;
+  float* __restrict__ grad;
+  float* __restrict__ m;
+  float* __restrict__ v;
+  __nv_bfloat16* __restrict__ shadow;      // optional bf16 copy of the parameters, refreshed for updated rows
+  unsigned char* __restrict__ touched;
   long long rows;
   int D, kind;                // 0 Adam, 1 AdamW, 2 SGD
   const long long* step;      // completed steps (the update uses step + 1)
@@ -225,54 +248,88 @@ struct SparseOptParams {
 };
 
 __global__ void __launch_bounds__(256) sparse_rows_optimizer_kernel(const SparseOptParams p) {
-  const int lane = threadIdx.x & 31;
-  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  // A block takes 256 consecutive rows at a time: one flag per thread, the flagged rows are compacted into shared
+  // memory in row order and dealt to the 8 warps round-robin, so the warps of a block (and neighbouring blocks) work
+  // on neighbouring rows at the same moment and DRAM pages are used whole.
+  __shared__ unsigned char list[256];
+  __shared__ int warp_count[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float t = static_cast<float>(*p.step + 1);
-  const float bc1 = 1.f - exp2f(t * log2f(p.beta1)), bc2 = 1.f - exp2f(t * log2f(p.beta2));
-  for (long long base = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * 32; base < p.rows;
-       base += warps * 32) {
-    const long long mine = base + lane;
+  float inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
+  if (p.kind != 2) {
+    inv_bc1 = 1.f / (1.f - exp2f(t * log2f(p.beta1)));
+    inv_sqrt_bc2 = rsqrtf(1.f - exp2f(t * log2f(p.beta2)));
+  }
+  for (long long base = static_cast<long long>(blockIdx.x) * 256; base < p.rows;
+       base += static_cast<long long>(gridDim.x) * 256) {
+    const long long mine = base + threadIdx.x;
     const bool flag = mine < p.rows && p.touched[mine] != 0;
-    unsigned int todo = __ballot_sync(0xffffffffu, flag);
     if (flag) p.touched[mine] = 0;
-    while (todo) {
-      const int k = __ffs(todo) - 1;
-      todo &= todo - 1;
-      const size_t off = static_cast<size_t>(base + k) * p.D;
+    const unsigned int bits = __ballot_sync(0xffffffffu, flag);
+    if (lane == 0) warp_count[warp] = __popc(bits);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int c = warp_count[w];
+      if (w < warp) before += c;
+      total += c;
+    }
+    if (flag) list[before + __popc(bits & ((1u << lane) - 1u))] = static_cast<unsigned char>(threadIdx.x);
+    __syncthreads();
+    // four rows per warp are in flight at a time: all their loads are issued before the first store
+    constexpr int R = 4;
+    for (int i0 = warp; i0 < total; i0 += 8 * R) {
       for (int d = lane * 4; d < p.D; d += 128) {
-        const float4 g4 = *reinterpret_cast<const float4*>(p.grad + off + d);
-        const float4 w4 = *reinterpret_cast<const float4*>(p.param + off + d);
-        *reinterpret_cast<float4*>(p.grad + off + d) = make_float4(0.f, 0.f, 0.f, 0.f);
-        float gp[4] = {g4.x, g4.y, g4.z, g4.w};
-        float wp[4] = {w4.x, w4.y, w4.z, w4.w};
-        if (p.kind == 2) {
+        size_t off[R];
+        float4 g4[R], w4[R], m4[R], v4[R];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) wp[u] -= p.lr * (gp[u] + p.weight_decay * wp[u]);
-        } else {
-          const float4 m4 = *reinterpret_cast<const float4*>(p.m + off + d);
-          const float4 v4 = *reinterpret_cast<const float4*>(p.v + off + d);
-          float mp[4] = {m4.x, m4.y, m4.z, m4.w};
-          float vp[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float gu = gp[u];
-            if (p.kind == 0) gu += p.weight_decay * wp[u];
-            else wp[u] *= 1.f - p.lr * p.weight_decay;
-            mp[u] = p.beta1 * mp[u] + (1.f - p.beta1) * gu;
-            vp[u] = p.beta2 * vp[u] + (1.f - p.beta2) * gu * gu;
-            wp[u] -= p.lr * (mp[u] / bc1) / (sqrtf(vp[u] / bc2) + p.eps);
+        for (int j = 0; j < R; ++j) {
+          const int i = i0 + 8 * j;
+          off[j] = static_cast<size_t>(base + list[i < total ? i : i0]) * p.D + d;
+          g4[j] = *reinterpret_cast<const float4*>(p.grad + off[j]);
+          w4[j] = *reinterpret_cast<const float4*>(p.param + off[j]);
+          m4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          v4[j] = m4[j];
+          if (p.kind != 2) {
+            m4[j] = *reinterpret_cast<const float4*>(p.m + off[j]);
+            v4[j] = *reinterpret_cast<const float4*>(p.v + off[j]);
           }
-          *reinterpret_cast<float4*>(p.m + off + d) = make_float4(mp[0], mp[1], mp[2], mp[3]);
-          *reinterpret_cast<float4*>(p.v + off + d) = make_float4(vp[0], vp[1], vp[2], vp[3]);
         }
-        *reinterpret_cast<float4*>(p.param + off + d) = make_float4(wp[0], wp[1], wp[2], wp[3]);
-        if (p.shadow != nullptr) {
-          __nv_bfloat162 lo = __floats2bfloat162_rn(wp[0], wp[1]), hi = __floats2bfloat162_rn(wp[2], wp[3]);
-          uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-          *reinterpret_cast<uint2*>(p.shadow + off + d) = pk;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          if (i0 + 8 * j >= total) continue;
+          *reinterpret_cast<float4*>(p.grad + off[j]) = make_float4(0.f, 0.f, 0.f, 0.f);
+          float gp[4] = {g4[j].x, g4[j].y, g4[j].z, g4[j].w};
+          float wp[4] = {w4[j].x, w4[j].y, w4[j].z, w4[j].w};
+          if (p.kind == 2) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) wp[u] -= p.lr * fmaf(p.weight_decay, wp[u], gp[u]);
+          } else {
+            float mp[4] = {m4[j].x, m4[j].y, m4[j].z, m4[j].w};
+            float vp[4] = {v4[j].x, v4[j].y, v4[j].z, v4[j].w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              float gu = gp[u];
+              if (p.kind == 0) gu = fmaf(p.weight_decay, wp[u], gu);
+              else wp[u] *= 1.f - p.lr * p.weight_decay;
+              mp[u] = fmaf(p.beta1, mp[u], (1.f - p.beta1) * gu);
+              vp[u] = fmaf(p.beta2, vp[u], (1.f - p.beta2) * gu * gu);
+              wp[u] -= p.lr * inv_bc1 * mp[u] / (sqrtf(vp[u]) * inv_sqrt_bc2 + p.eps);
+            }
+            *reinterpret_cast<float4*>(p.m + off[j]) = make_float4(mp[0], mp[1], mp[2], mp[3]);
+            *reinterpret_cast<float4*>(p.v + off[j]) = make_float4(vp[0], vp[1], vp[2], vp[3]);
+          }
+          *reinterpret_cast<float4*>(p.param + off[j]) = make_float4(wp[0], wp[1], wp[2], wp[3]);
+          if (p.shadow != nullptr) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(wp[0], wp[1]), hi = __floats2bfloat162_rn(wp[2], wp[3]);
+            uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            *reinterpret_cast<uint2*>(p.shadow + off[j]) = pk;
+          }
         }
       }
     }
+    __syncthreads();  // the list is rebuilt for the next chunk
   }
 }
 
@@ -290,8 +347,8 @@ extern "C" int dice_sparse_rows_optimizer(int kind, float* param, float* grad, f
   if (D % 4 || kind < 0 || kind > 2) return -6;
   SparseOptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), touched, rows, D, kind, step, lr, beta1,
                     beta2, eps, weight_decay};
-  long long blocks = ((rows + 31) / 32 * 32 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  long long blocks = (rows + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   sparse_rows_optimizer_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -343,8 +400,8 @@ extern "C" int dice_candidate_bce(const float* q, const long long* cand, long lo
   long long blocks = (static_cast<long long>(N) * 32 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D <= 128) candidate_bce_kernel<1><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
-  else if (D <= 256) candidate_bce_kernel<2><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
-  else candidate_bce_kernel<4><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  if (D <= 128) candidate_bce_kernel<1, 4><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  else if (D <= 256) candidate_bce_kernel<2, 4><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
+  else candidate_bce_kernel<4, 2><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
