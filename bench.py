@@ -186,7 +186,7 @@ def run_ours(args) -> dict:
     ms_e2e = timed(lambda i: losses.append(engine.step_from_host(host_x[i], host_dp[i])), args.warmup, args.steps, 0)
     clocks = sampler.stop() if sampler is not None else None
     engine.sync_to_model()
-    if getattr(engine, "_phase_events", None):
+    if getattr(engine, "_phase_events", None) is not None:
         pt = engine.phase_times()
         if rank == 0:
             print("phase_ms " + json.dumps({k: round(v, 4) for k, v in pt.items()}), file=sys.stderr, flush=True)

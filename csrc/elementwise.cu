@@ -682,6 +682,18 @@ extern "C" int dice_finish_step(double* acc, float* loss_out, double inv_count, 
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// Writes the GPU's nanosecond timer into *slot: launched between the kernels of a (captured) step it gives per-phase
+// device times without host events.
+__global__ void timestamp_kernel(unsigned long long* slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *slot = t;
+}
+extern "C" int dice_timestamp(unsigned long long* slot, void* stream) {
+  timestamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(slot);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 // sig_table: device array of W pointers to each rank's unsigned[W] signal array; count: this rank's barrier counter.
 extern "C" int dice_p2p_barrier(unsigned int* const* sig_table, int rank, int W, unsigned int* count, int* status,
                                 unsigned int spin_limit, void* stream) {

@@ -178,6 +178,8 @@ def preprocess_args(args):
     if args.normalization == "None":
         args.normalization = None
     assert args.normalization in (None, "LayerNorm", "BatchNorm1d")
+    if args.model == "BytE" and getattr(args, "block_size", None) is None:
+        args.block_size = 8   # default of the command line (reference ``scripts/run.py:118``); the Python API leaves None
     if args.model == "BytE":
         args.byte_pair_encoding = True
     return args

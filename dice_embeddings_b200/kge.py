@@ -228,7 +228,9 @@ class KGE:
     def get_bpe_token_representation(self, x: StrOrList):
         if isinstance(x, list):
             return [self.get_bpe_token_representation(i) for i in x]
-        ids = list(self.enc.encode(x))
+        # padded to the training-time width; longer strings are cut there (the reference leaves that case open,
+        # ``dicee/abstracts.py:241-243``)
+        ids = list(self.enc.encode(x))[: self.max_length_subword_tokens]
         ids += [self.dummy_id] * max(0, self.max_length_subword_tokens - len(ids))
         return ids
 
@@ -615,7 +617,7 @@ class KGE:
             for x, y in loader:
                 opt.zero_grad()
                 loss = self.model.loss(self.model(x), y)
-                tot += float(loss)
+                tot += float(loss.detach())
                 loss.backward()
                 opt.step()
             print(f"Epoch={ep}\t Avg. Loss per epoch: {tot / n:.3f}")
@@ -668,7 +670,7 @@ class KGE:
                 loss = F.l1_loss(lit(bx[:, 0], bx[:, 1]), by)
                 loss.backward()
                 opt.step()
-                tot += float(loss)
+                tot += float(loss.detach())
                 nb += 1
             loss_log["lit_loss"].append(tot / max(nb, 1))
         lit.eval()

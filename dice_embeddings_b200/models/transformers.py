@@ -156,6 +156,8 @@ class BytE(BaseKGE):
             from ..data.bpe import get_tokenizer
             vocab = get_tokenizer().n_vocab
         n_head = 4 if self.embedding_dim % 4 == 0 else 1
+        if self.block_size is None:  # the Python API leaves it unset (reference ``config.py:157``); the CLI default is 8
+            self.block_size = 8
         self.config = GPTConfig(block_size=self.block_size, vocab_size=vocab, n_layer=4, n_head=n_head,
                                 n_embd=self.embedding_dim, dropout=0.0, bias=False)
         self.temperature = 0.5

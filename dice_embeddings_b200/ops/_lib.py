@@ -99,6 +99,7 @@ class _Sigs:
     dice_finish_step = [_p, _p, _d, _p, _p, _i, _p]
     dice_p2p_barrier = [_p, _i, _i, _p, _p, ctypes.c_uint, _p]
     dice_kvsall_set_trace = [_p]
+    dice_timestamp = [_p, _p]
     dice_uniform_int = [_p, _l, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _l, _l, _p]
     dice_neg_sample = [_p, _i, _i, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _i, _f, _f, _p, _p, _p, _p, _p, _p]
     dice_candidate_bce = [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p, _f, _i, _f, _f, _i, _i, _i, _p, _p]

@@ -139,6 +139,12 @@ def p2p_barrier(sig_table: torch.Tensor, rank: int, world: int, count: torch.Ten
                                        _stream()), "dice_p2p_barrier")
 
 
+def timestamp(slots: torch.Tensor, index: int) -> None:
+    """Write the GPU nanosecond timer into ``slots[index]`` (int64) in stream order; capturable in a CUDA graph."""
+    _req(slots, torch.int64, "slots")
+    _check(_lib.lib().dice_timestamp(slots.data_ptr() + 8 * int(index), _stream()), "dice_timestamp")
+
+
 def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
     """Register (or clear with ``None``) a ``[64, 8]`` int64 device buffer receiving per-tile clock stamps of CTA 0 of
     every following ``kvsall_fused`` launch (pipeline diagnostics; see ``profile_fused --trace``)."""

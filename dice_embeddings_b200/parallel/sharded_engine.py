@@ -160,6 +160,8 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._phase_events = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
+        self._phase_names = []
+        self._phase_slots = torch.zeros(32, dtype=torch.int64, device=dev)
         heap.host_barrier()
 
     # ------------------------------------------------------------------ the step, peer-memory flavour
@@ -185,23 +187,21 @@ class ShardedKvsAllEngine:
             K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=self.W)
 
     def _mark(self, name: str) -> None:
-        """Phase timing (enabled with ``DICE_B200_PHASE_TIMING=1`` together with ``DICE_B200_NO_GRAPH=1``): records a
-        CUDA event after each phase; :meth:`phase_times` returns the mean milliseconds per phase."""
+        """Phase timing (``DICE_B200_PHASE_TIMING=1``): a one-thread kernel stores the GPU timer after each phase, so
+        the times are device times also under graph replay; :meth:`phase_times` returns the microseconds per phase of
+        the last step."""
         if self._phase_events is not None:
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            self._phase_events.append((name, e))
+            if name not in self._phase_names:
+                self._phase_names.append(name)
+            K.timestamp(self._phase_slots, self._phase_names.index(name))
 
     def phase_times(self):
         torch.cuda.synchronize(self.device)
-        out, prev, last = {}, None, None
-        for name, e in self._phase_events or []:
-            if name == "start":
-                prev = e
-                continue
-            out.setdefault(name, []).append(prev.elapsed_time(e))
-            prev = e
-        return {k: sum(v) / len(v) for k, v in out.items()}
+        t = self._phase_slots.cpu().tolist()
+        out = {}
+        for i in range(1, len(self._phase_names)):
+            out[self._phase_names[i]] = (t[i] - t[i - 1]) / 1e6   # milliseconds
+        return out
 
     def _launch_p2p(self) -> None:
         W, B, D, n = self.W, self.B, self.D, self.W * self.B
