@@ -155,6 +155,12 @@ struct ComposeBwdParams {
   int B, D, W, norm_mode;
   int additive;
   unsigned char* const* touched;  // optional [W] per-row flags of the gradient shards: set where a row gets a gradient
+  // optional: dq of batch item i = sum over n_dq buffers (one per rank, peer pointers) of row dq_row_offset + i.
+  // This is the consumer side of a reduce-scatter: every rank keeps its partial query gradients for the whole batch
+  // locally and the owner of a batch slice sums the partials with coalesced peer loads while it applies the chain rule.
+  const float* const* dq_table;
+  int n_dq;
+  long long dq_row_offset;
 };
 
 template <int K, int VEC>
@@ -173,7 +179,22 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
     float hv[K][VEC], rv[K][VEC], rh[K][VEC], nrm[K][VEC], dq[K][VEC], dh[K][VEC], drh[K][VEC];
     load_blocks<K, VEC>(hrow, w, j0, hv);
     load_blocks<K, VEC>(rrow, w, j0, rv);
-    load_blocks<K, VEC>(p.dq + static_cast<long long>(i) * p.D, w, j0, dq);
+    if (p.dq_table == nullptr) {
+      load_blocks<K, VEC>(p.dq + static_cast<long long>(i) * p.D, w, j0, dq);
+    } else {
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) dq[a][u] = 0.f;
+      for (int k = 0; k < p.n_dq; ++k) {
+        float part[K][VEC];
+        load_blocks<K, VEC>(p.dq_table[k] + (p.dq_row_offset + i) * p.D, w, j0, part);
+#pragma unroll
+        for (int a = 0; a < K; ++a)
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) dq[a][u] += part[a][u];
+      }
+    }
     normalize_rel<K, VEC>(p.norm_mode, rv, rh, nrm);
     float c = 1.f;
     if (p.coeff != nullptr) {
@@ -603,9 +624,11 @@ extern "C" int dice_lookup_compose(int model, int normalize, const long long* id
 extern "C" int dice_compose_backward(int model, int normalize, const long long* idx_h, const long long* idx_r,
                                      const float* const* ent, int W, const float* rel, const float* coeff,
                                      const float* dq, float* const* g_ent, float* g_rel, float* g_coeff, int B, int D,
-                                     unsigned char* const* touched, void* stream) {
+                                     unsigned char* const* touched, const float* const* dq_table, int n_dq,
+                                     long long dq_row_offset, void* stream) {
   if (B <= 0) return 0;
-  ComposeBwdParams p{idx_h, idx_r, ent, rel, nullptr, dq, g_ent, g_rel, nullptr, B, D, W, NORM_NONE, 0, touched};
+  ComposeBwdParams p{idx_h, idx_r, ent, rel, nullptr, dq, g_ent, g_rel, nullptr, B, D, W, NORM_NONE, 0, touched,
+                     dq_table, n_dq, dq_row_offset};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (model) {
     case 0: return launch_bwd<1, 1>(p, s);

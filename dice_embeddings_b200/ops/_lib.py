@@ -91,7 +91,7 @@ class _Sigs:
     dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _p, _i, _f, _p]
     dice_build_label_masks = [_p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
     dice_lookup_compose = [_i, _i, _p, _p, _p, _i, _l, _p, _p, _p, _i, _l, _p, _i, _i, _p, _p, _p, _p]
-    dice_compose_backward = [_i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p]
+    dice_compose_backward = [_i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _i, _l, _p]
     dice_positive_scan = [_p, _p, _i, _p, _p]
     dice_positive_correction = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p, _i, _p]
     dice_optimizer_step = [_i, _p, _p, _p, _p, _p, _p, _l, _f, _f, _f, _f, _f, _p, _i, _p]

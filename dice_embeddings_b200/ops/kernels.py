@@ -80,10 +80,15 @@ def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.T
 
 
 def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: int, rel, coeff, dq, g_ent_table,
-                     g_rel, g_coeff, B: int, D: int, touched_table: Optional[torch.Tensor] = None) -> None:
+                     g_rel, g_coeff, B: int, D: int, touched_table: Optional[torch.Tensor] = None,
+                     dq_table: Optional[torch.Tensor] = None, n_dq: int = 0, dq_row_offset: int = 0) -> None:
+    """Chain rule of the composition.  With ``dq_table`` the query gradient of batch item ``i`` is the sum over the
+    ``n_dq`` buffers (one per rank) of their row ``dq_row_offset + i``: the reduce-scatter of the partial query
+    gradients happens here, by peer loads."""
     rc = _lib.lib().dice_compose_backward(model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
                                           _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(g_ent_table), _ptr(g_rel),
-                                          _ptr(g_coeff), B, D, _ptr(touched_table), _stream())
+                                          _ptr(g_coeff), B, D, _ptr(touched_table), _ptr(dq_table), int(n_dq),
+                                          int(dq_row_offset), _stream())
     _check(rc, "dice_compose_backward")
 
 

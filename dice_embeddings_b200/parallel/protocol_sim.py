@@ -11,7 +11,7 @@ the same sequence of reads, writes, reductions and barriers is replayed here on 
   peer, then wait until ``sig[rank][p] >= count`` for all ``p``, giving up after a bounded number of polls with
   status ``TIMEOUT_PEER``;
 * :func:`run_sharded_step` – the step itself (lookup by peer reads, query broadcast by peer writes, scoring of the
-  local shard, reduce-scatter of the query gradient by peer adds, scatter of row gradients to their owners,
+  local shard, reduce-scatter of the query gradient by peer loads at the consumer, scatter of row gradients to their owners,
   replicated update of the relation table from all ranks' gradient buffers) on a toy DistMult model, compared by the
   tests against a single-process computation; faults (a rank that never arrives, a dropped signal, a removed
   barrier) are injected on the host.
@@ -150,7 +150,7 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
     b = B // W
     rows = (NE + W - 1) // W
     heap = SimHeap(W)
-    for name, shape in (("E", (rows, D)), ("gE", (rows, D)), ("Q", (B, D)), ("dQ", (b, D)), ("gR", R.shape),
+    for name, shape in (("E", (rows, D)), ("gE", (rows, D)), ("Q", (B, D)), ("dQ", (B, D)), ("gR", R.shape),
                         ("loss", (1,))):
         heap.alloc(name, shape)
     Rrep = [R.copy() for _ in range(W)]
@@ -181,7 +181,6 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 for peer in range(W):
                     heap.write("Q", peer, rank, slice(lo, lo + b), q, region=("rows", lo))
                 heap.write("gR", rank, rank, slice(None), 0.0)
-                heap.write("dQ", rank, rank, slice(None), 0.0)
                 heap.write("loss", rank, rank, slice(None), 0.0)
                 barrier(rank, "S1")                            # all queries have landed, accumulators are clear
                 Eloc = heap.read("E", rank, rank)[:n_own]
@@ -192,11 +191,10 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 heap.add("loss", rank, rank, 0, np.sum(np.maximum(s, 0) - s * y + np.log1p(np.exp(-np.abs(s)))))
                 ds = (sig - y) / (B * NE)
                 heap.add("gE", rank, rank, np.arange(n_own), ds.T @ Q)
-                dQ_part = ds @ Eloc                            # partial over this shard: reduce-scatter to the owners
-                for peer in range(W):
-                    heap.add("dQ", peer, rank, np.arange(b), dQ_part[peer * b:(peer + 1) * b])
-                barrier(rank, "S2")                            # every partial of dQ has been added
-                dq = heap.read("dQ", rank, rank).copy()
+                heap.add("dQ", rank, rank, np.arange(B), ds @ Eloc)   # partial over this shard, kept locally
+                barrier(rank, "S2")                            # every rank's partial of dQ is complete
+                # reduce-scatter, consumer side: the owner of the batch slice sums all ranks' partial rows
+                dq = sum(heap.read("dQ", p, rank)[lo:lo + b] for p in range(W))
                 gh = dq * Rrep[rank][my_r]
                 for e, g in zip(my_h, gh):                     # row gradients go to the owners of the head rows
                     heap.add("gE", int(e) % W, rank, int(e) // W, g)
@@ -209,6 +207,7 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 Rrep[rank] = Rrep[rank] - lr * gR
                 heap.write("E", rank, rank, slice(None), heap.bufs["E"][rank] - lr * g_own)
                 heap.write("gE", rank, rank, slice(None), 0.0)
+                heap.write("dQ", rank, rank, slice(None), 0.0)
                 losses[rank] = loss
         except BaseException as exc:  # noqa: BLE001 - reported to the caller
             errors[rank] = exc

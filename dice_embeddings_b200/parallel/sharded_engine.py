@@ -14,10 +14,11 @@ S0    ``p2p_barrier``                                        flags
 S1    ``p2p_barrier``
 2     ``build_label_masks`` + ``kvsall_fused`` (entity-       none (local shard × all queries)
       stationary): loss and dense ``dE`` of the local shard
-3     ``kvsall_fused`` (query-stationary): ``dQ`` tiles are   peer ``red.add`` into the owner of each query block
-      reduced straight into the owning rank's buffer           (GEMM → reduce-scatter in one kernel)
+3     ``kvsall_fused`` (query-stationary): partial ``dQ``      none (the partials of the whole batch stay local)
+      of the local shard for all queries
 S2    ``p2p_barrier``
-4     ``compose_backward``: chain rule, row gradients          peer ``red.add`` into the owner's gradient shard
+4     ``compose_backward``: the owner of a batch slice sums    peer loads (the reduce-scatter of dQ, consumer side);
+      all ranks' partial ``dQ`` rows, chain rule, row grads    peer ``red.add`` into the owner's gradient shard
 S3    ``p2p_barrier``
 5     ``optimizer_step``: local shard; relations read every    peer loads (all-reduce folded into the update)
       rank's gradient buffer; ``finish_step`` sums the losses
@@ -98,7 +99,7 @@ class ShardedKvsAllEngine:
         heap.plan("gR", (self.NR, D), torch.float32)
         heap.plan("gC", (4,), torch.float32)
         heap.plan("Q", (W * B, D), torch.bfloat16)
-        heap.plan("dQ", (B, D), torch.float32)
+        heap.plan("dQ", (W * B, D), torch.float32)   # this rank's partial query gradients for the whole batch
         heap.plan("dp", (W * B,), torch.int64)
         heap.plan("loss", (2,), torch.float64)
         heap.plan("sig", (64,), torch.int32)
@@ -229,23 +230,24 @@ class ShardedKvsAllEngine:
                        mask=self.mask_e, pos_delta=self.pos_weight)
         self._mark("fused_E")
         K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
-                       out_table=self.tab.dQ, out_block_rows=B, mask=self.mask_q, pos_delta=self.pos_weight)
+                       mask=self.mask_q, pos_delta=self.pos_weight)
         self._mark("fused_Q+rs")
         if not masks:
             # label term of the positives whose tail lives in this shard: loss, dE rows here, dQ rows at their owners
             K.positive_scan(self.dp_all, self.offsets, n, self.first)
             K.positive_correction(self.dp_all, self.offsets, self.values, self.first, self.Q, self.E_bf16, self.dQ,
-                                  self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, W, self.rank,
-                                  dq_table=self.tab.dQ, dq_block_rows=B)
+                                  self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, W, self.rank)
             self._mark("positives")
         self._barrier()                                   # S2: every rank's dQ block is complete
         self._mark("S2")
-        K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, self.dQ,
-                           self.tab.gE, self.gR, self.gC if self.coeff_trainable else None, B, D)
-        self.dQ.zero_()
+        # the owner of a batch slice sums all ranks' partial query gradients by peer loads (the reduce-scatter)
+        K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, None,
+                           self.tab.gE, self.gR, self.gC if self.coeff_trainable else None, B, D,
+                           dq_table=self.tab.dQ, n_dq=W, dq_row_offset=self.rank * B)
         self._mark("compose_bwd")
-        self._barrier()                                   # S3: all row gradients reached their owners
+        self._barrier()                                   # S3: all row gradients reached their owners, all pulls done
         self._mark("S3")
+        self.dQ.zero_()
         self._optimizers_and_finish(scale, reduced=False)
         self._mark("optim")
 
