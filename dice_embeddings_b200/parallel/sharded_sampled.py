@@ -195,6 +195,7 @@ class ShardedSampledEngine:
         Every rank must call with the same shapes.  Returns the global mean loss (device scalar)."""
         if self.st == "NegSample":
             pos = batch[0]
+            assert len(batch) == 1 or batch[1] is None, "pass the positives only (dataset.defer_sampling = True)"
             assert pos.shape[1] == 3, "the sharded NegSample step takes the positives; it draws the corruptions itself"
             B = pos.shape[0]
             key = (B, 1 + self.k, B) if self.layout == "tails" else (B * (1 + self.k), 1, B)

@@ -40,3 +40,24 @@ def test_sharded_sampled_engine_matches_autograd_and_learns():
            "--master-addr", "127.0.0.1", "--master-port", "29615", os.path.join(HERE, "_sharded_sampled_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0 and "SHARDED_SAMPLED_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+@pytest.mark.parametrize("st,extra", [("NegSample", ["--neg_ratio", "16"]), ("KvsAll", [])])
+def test_sharded_trainer_through_the_command_line(tmp_path, st, extra):
+    """``--trainer Sharded`` end to end on two ranks: training, gathering the shards, evaluation, stored run."""
+    import json
+    sys.path.insert(0, os.path.dirname(HERE))
+    from dice_embeddings_b200.data.synthetic import make_planted_kg
+    kg = make_planted_kg(str(tmp_path / "kg"), num_entities=300, num_relations=10, seed=1)
+    out = tmp_path / "run"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(HERE))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29617", "-m", "dice_embeddings_b200", "--dataset_dir", kg, "--model", "ComplEx",
+           "--scoring_technique", st, "--trainer", "Sharded", "--embedding_dim", "64", "--num_epochs", "60",
+           "--batch_size", "256", "--lr", "0.05", "--optim", "Adam", "--eval_model", "train_val_test",
+           "--path_to_store_single_run", str(out)] + extra
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    rep = json.load(open(out / "eval_report.json"))
+    assert rep["Train"]["MRR"] > (0.5 if st == "KvsAll" else 0.3), rep
+    assert os.path.isfile(out / "model.pt")
