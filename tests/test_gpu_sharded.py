@@ -53,8 +53,8 @@ def test_sharded_trainer_through_the_command_line(tmp_path, st, extra):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=os.path.dirname(HERE))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29617", "-m", "dice_embeddings_b200", "--dataset_dir", kg, "--model", "ComplEx",
-           "--scoring_technique", st, "--trainer", "Sharded", "--embedding_dim", "64", "--num_epochs", "60",
-           "--batch_size", "256", "--lr", "0.05", "--optim", "Adam", "--eval_model", "train_val_test",
+           "--scoring_technique", st, "--trainer", "Sharded", "--embedding_dim", "64", "--num_epochs", "150",
+           "--batch_size", "256", "--lr", "0.1", "--optim", "Adam", "--eval_model", "train_val_test",
            "--path_to_store_single_run", str(out)] + extra
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
