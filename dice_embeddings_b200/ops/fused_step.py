@@ -125,6 +125,8 @@ class FusedKvsAllEngine:
         # the sparse correction kernels
         mask_bytes = 2 * self.B * self.NE / 8
         self.label_mode = label_mode or ("mask" if mask_bytes <= (1 << 30) else "sparse")
+        # which of the two scoring passes also accumulates the loss (its epilogue is the longer one)
+        self.loss_in_query_pass = os.environ.get("DICE_B200_LOSS_PASS", "entity") == "query"
         self._bufs = {}
         self._graphs = {}
 
@@ -156,9 +158,10 @@ class FusedKvsAllEngine:
             b.mask_q.zero_()
             b.mask_e.zero_()
             K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e)
-            K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True,
-                           mask=b.mask_e, pos_delta=self.pos_weight)
-            K.kvsall_fused(b.Q, self.E_bf16, b.dQ, None, self.status, self.base, scale, False,
+            lq = self.loss_in_query_pass
+            K.kvsall_fused(self.E_bf16, b.Q, self.gE, None if lq else self.loss_acc, self.status, self.base, scale,
+                           not lq, mask=b.mask_e, pos_delta=self.pos_weight)
+            K.kvsall_fused(b.Q, self.E_bf16, b.dQ, self.loss_acc if lq else None, self.status, self.base, scale, lq,
                            mask=b.mask_q, pos_delta=self.pos_weight)
         else:
             K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True)
