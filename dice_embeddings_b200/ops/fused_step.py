@@ -250,6 +250,41 @@ class FusedKvsAllEngine:
         self._run(b, n)
         return float(self.loss_out.item())
 
+    def step_from_host_pipelined(self, x_pinned: torch.Tensor, dp_pinned: torch.Tensor) -> Optional[float]:
+        """Like :meth:`step_from_host` but without stalling the host on the step it has just queued: the loss is
+        copied to pinned host memory in stream order and the call returns the loss of the *previous* step (``None``
+        on the first call; :meth:`last_loss` waits for the newest one).  Every step still carries its own host→device
+        input copy and device→host loss copy; the host merely runs one step ahead of the GPU."""
+        n = x_pinned.shape[0]
+        b = self._buffers(n)
+        if not hasattr(b, "x_in"):
+            b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=self.device)
+        if not hasattr(self, "_loss_host"):
+            self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._loss_event = [torch.cuda.Event(), torch.cuda.Event()]
+            self._loss_slot, self._loss_pending = 0, False
+        prev = None
+        if self._loss_pending:
+            self._loss_event[self._loss_slot].synchronize()
+            prev = float(self._loss_host[self._loss_slot][0])
+        b.x_in.copy_(x_pinned, non_blocking=True)
+        b.dp.copy_(dp_pinned, non_blocking=True)
+        b.h.copy_(b.x_in[:, 0])
+        b.r.copy_(b.x_in[:, 1])
+        self._run(b, n)
+        self._loss_slot ^= 1
+        self._loss_host[self._loss_slot].copy_(self.loss_out, non_blocking=True)
+        self._loss_event[self._loss_slot].record()
+        self._loss_pending = True
+        return prev
+
+    def last_loss(self) -> Optional[float]:
+        """Loss of the newest pipelined step (waits for it)."""
+        if not getattr(self, "_loss_pending", False):
+            return None
+        self._loss_event[self._loss_slot].synchronize()
+        return float(self._loss_host[self._loss_slot][0])
+
     def sync_to_model(self) -> None:
         """Parameters are updated in place; only kernel failures need surfacing."""
         K.check_status(self.status, "in fused training step")

@@ -343,6 +343,35 @@ class ShardedKvsAllEngine:
         self._run()
         return float(self.loss_out.item())
 
+    def step_from_host_pipelined(self, x_pinned: torch.Tensor, dp_pinned: torch.Tensor) -> Optional[float]:
+        """:meth:`step_from_host` without stalling the host on the step it has just queued: returns the loss of the
+        previous step (``None`` first); :meth:`last_loss` waits for the newest.  Each step still has its own
+        host→device input copy and device→host loss copy."""
+        if not hasattr(self, "_loss_host"):
+            self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._loss_event = [torch.cuda.Event(), torch.cuda.Event()]
+            self._loss_slot, self._loss_pending = 0, False
+        prev = None
+        if self._loss_pending:
+            self._loss_event[self._loss_slot].synchronize()
+            prev = float(self._loss_host[self._loss_slot][0])
+        self.x_in.copy_(x_pinned, non_blocking=True)
+        self.dp.copy_(dp_pinned, non_blocking=True)
+        self.h.copy_(self.x_in[:, 0])
+        self.r.copy_(self.x_in[:, 1])
+        self._run()
+        self._loss_slot ^= 1
+        self._loss_host[self._loss_slot].copy_(self.loss_out, non_blocking=True)
+        self._loss_event[self._loss_slot].record()
+        self._loss_pending = True
+        return prev
+
+    def last_loss(self) -> Optional[float]:
+        if not getattr(self, "_loss_pending", False):
+            return None
+        self._loss_event[self._loss_slot].synchronize()
+        return float(self._loss_host[self._loss_slot][0])
+
     def check(self) -> None:
         K.check_status(self.status, f"on rank {self.rank} of the sharded step")
 

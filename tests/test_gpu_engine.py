@@ -106,3 +106,20 @@ def test_trainer_uses_fused_engine(tmp_path):
     assert rep["Train"]["MRR"] > 0.9
     k = KGE(path=str(tmp_path / "run"))
     assert len(k.predict_topk(h=[next(iter(k.entity_to_idx))], r=[next(iter(k.relation_to_idx))], topk=3)[0]) == 3
+
+
+def test_pipelined_host_steps_return_the_same_losses():
+    ds, m1, m2 = _make("ComplEx", 64, "Adam", 0.05)
+    B = 256
+    e1 = FusedKvsAllEngine(m1, ds, batch_size=B, lr=0.05, device=DEV)
+    e2 = FusedKvsAllEngine(m2, ds, batch_size=B, lr=0.05, device=DEV)
+    g = torch.Generator().manual_seed(3)
+    pairs = ds.train_data.cpu()
+    a, b = [], []
+    for _ in range(6):
+        idx = torch.randperm(len(ds), generator=g)[:B]
+        x, dp = pairs[idx].contiguous().pin_memory(), idx.contiguous().pin_memory()
+        a.append(e1.step_from_host(x, dp))
+        b.append(e2.step_from_host_pipelined(x, dp))
+    b = b[1:] + [e2.last_loss()]
+    assert all(abs(u - v) < 1e-6 * max(1.0, abs(u)) for u, v in zip(a, b)), (a, b)
