@@ -43,6 +43,13 @@ struct EvalParams {
   float* cand_score;       // [x_rows, cand_cap], pre-filled with -inf
   int* cand_idx;           // [x_rows, cand_cap], pre-filled with -1
   int* cand_count;         // [x_rows], zero-initialised
+  // band mode (BAND variants): scores within +-margin[row] of the target are not decided here; their (row, entity)
+  // pairs are appended to a list for an exact second pass, only scores above target + margin are counted
+  const float* margin;     // [x_rows]
+  int* band_rows;          // [band_cap]
+  int* band_cols;          // [band_cap] global entity ids
+  unsigned long long* band_count;
+  long long band_cap;
 };
 
 template <int D>
@@ -53,11 +60,13 @@ struct Cfg {
   static constexpr int SMEM_BYTES = TILE_BYTES * (1 + NSTAGE) + 1024 + 512;
 };
 
-template <int D, bool TOPK>
+template <int D, int MODE>  // 0 count, 1 count + top-k, 2 count with an undecided band
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
                  const EvalParams p) {
   using C = Cfg<D>;
+  constexpr bool TOPK = MODE == 1;
+  constexpr bool BAND = MODE == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sX = smem;
@@ -204,6 +213,12 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (rel_id >= 0 && rel_id % p.y_stride == 0) tgt_col = rel_id / p.y_stride;
       }
       int cnt = 0;
+      float hi = tgt, lo = tgt;
+      if constexpr (BAND) {
+        const float mg = valid_x ? p.margin[x_global] : 0.f;
+        hi = tgt + mg;
+        lo = tgt - mg;
+      }
       float thr = valid_x ? -CUDART_INF_F : CUDART_INF_F;
       int minpos = 0;
       if constexpr (TOPK) {
@@ -224,12 +239,14 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           tmem_ld32(s_addr + col0, r);
           tc_wait_ld();
           const int rel = tgt_col - (tile_col0 + col0);  // position of the true entity inside this chunk, if any
+          uint32_t band = 0u;
           const bool plain = (col0 + 32 <= y_valid) && (p.col_bias == nullptr);
           if (plain) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float s = __uint_as_float(r[i]);
-              cnt += (s > tgt && i != rel) ? 1 : 0;
+              cnt += (s > hi && i != rel) ? 1 : 0;
+              if constexpr (BAND) band |= ((s > lo && s <= hi && i != rel) ? 1u : 0u) << i;
               if constexpr (TOPK) {
                 if (s > thr) {
                   top_s[minpos] = s;
@@ -248,7 +265,8 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
               float s = __uint_as_float(r[i]);
               if (p.col_bias != nullptr && in) s += p.col_bias[tile_col0 + col0 + i];
               if (!in) s = -CUDART_INF_F;
-              cnt += (s > tgt && i != rel) ? 1 : 0;
+              cnt += (s > hi && i != rel) ? 1 : 0;
+              if constexpr (BAND) band |= ((s > lo && s <= hi && i != rel) ? 1u : 0u) << i;
               if constexpr (TOPK) {
                 if (s > thr) {
                   top_s[minpos] = s;
@@ -258,6 +276,24 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                   for (int j = 1; j < p.k; ++j)
                     if (top_s[j] < thr) { thr = top_s[j]; minpos = j; }
                 }
+              }
+            }
+          }
+          if constexpr (BAND) {
+            if (band != 0u) {  // undecided pairs of this thread's 32 columns go to the list of the exact pass
+              const int nb = __popc(band);
+              const unsigned long long base = atomicAdd(p.band_count, static_cast<unsigned long long>(nb));
+              if (static_cast<long long>(base) + nb <= p.band_cap) {
+                unsigned long long at = base;
+                while (band) {
+                  const int i = __ffs(band) - 1;
+                  band &= band - 1;
+                  p.band_rows[at] = x_global;
+                  p.band_cols[at] = p.y_offset + (tile_col0 + col0 + i) * p.y_stride;
+                  ++at;
+                }
+              } else {
+                atomicCAS(p.status, 0, ST_INBOX_OVERFLOW);
               }
             }
           }
@@ -294,10 +330,10 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
 }
 
-template <int D, bool TOPK>
+template <int D, int MODE>
 static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const EvalParams& p, int num_ctas,
                   cudaStream_t stream) {
-  auto kern = eval_rank_kernel<D, TOPK>;
+  auto kern = eval_rank_kernel<D, MODE>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES) != cudaSuccess)
@@ -314,7 +350,13 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const EvalParams
 // Local row c of y is entity y_offset + c * y_stride; entities of other shards are skipped (the caller sums over
 // shards).  With target_in != null the target scores are taken from it instead (second phase of the sharded
 // protocol, after the owners' scores have been exchanged).
-__global__ void eval_sparse_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ y, int n,
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+
+template <typename T>
+__global__ void eval_sparse_kernel(const T* __restrict__ q, const T* __restrict__ y, int n,
                                    int D, int y_rows, int y_offset, int y_stride, const int* __restrict__ target,
                                    const float* __restrict__ col_bias, const float* __restrict__ target_in,
                                    const long long* __restrict__ filt_ptr, const int* __restrict__ filt_cols,
@@ -322,13 +364,13 @@ __global__ void eval_sparse_kernel(const __nv_bfloat16* __restrict__ q, const __
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= n) return;
-  const __nv_bfloat16* qi = q + static_cast<size_t>(warp) * D;
+  const T* qi = q + static_cast<size_t>(warp) * D;
   auto dot = [&](int col) -> float {
-    const __nv_bfloat16* yj = y + static_cast<size_t>(col) * D;
+    const T* yj = y + static_cast<size_t>(col) * D;
     float acc = 0.f;
     for (int d = lane * 2; d < D; d += 64) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qi + d));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(yj + d));
+      const float2 a = load2(qi + d);
+      const float2 b = load2(yj + d);
       acc = fmaf(a.x, b.x, acc);
       acc = fmaf(a.y, b.y, acc);
     }
@@ -364,6 +406,35 @@ __global__ void eval_sparse_kernel(const __nv_bfloat16* __restrict__ q, const __
   if (lane == 0) filtered_greater[warp] = cnt;
 }
 
+// Exact second pass of the band mode: one warp per undecided (query, entity) pair, fp32 operands; the pair counts
+// when its exact score beats the exact target score of the query.
+__global__ void eval_band_exact_kernel(const float* __restrict__ q, const float* __restrict__ y, int D, int y_rows,
+                                       int y_offset, int y_stride, const float* __restrict__ col_bias,
+                                       const int* __restrict__ band_rows, const int* __restrict__ band_cols,
+                                       const unsigned long long* __restrict__ band_count, long long band_cap,
+                                       const float* __restrict__ target, int* __restrict__ greater) {
+  const long long total = min(static_cast<long long>(*band_count), band_cap);
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
+    const int row = band_rows[i];
+    const int c = (band_cols[i] - y_offset) / y_stride;
+    const float* qi = q + static_cast<size_t>(row) * D;
+    const float* yj = y + static_cast<size_t>(c) * D;
+    float acc = 0.f;
+    for (int d = lane * 2; d < D; d += 64) {
+      const float2 a = *reinterpret_cast<const float2*>(qi + d);
+      const float2 b = *reinterpret_cast<const float2*>(yj + d);
+      acc = fmaf(a.x, b.x, acc);
+      acc = fmaf(a.y, b.y, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (col_bias != nullptr) acc += col_bias[c];
+    if (lane == 0 && acc > target[row]) atomicAdd(greater + row, 1);
+  }
+}
+
 }  // namespace evalk
 }  // namespace dice
 
@@ -375,7 +446,8 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
                               const int* target_idx, const float* col_bias, int y_offset, int y_stride, int* greater,
                               int k,
                               int cand_cap, float* cand_score, int* cand_idx, int* cand_count, int* status,
-                              int num_ctas, void* stream) {
+                              int num_ctas, const float* margin, int* band_rows, int* band_cols,
+                              unsigned long long* band_count, long long band_cap, void* stream) {
   using namespace dice;
   using namespace dice::evalk;
   if (x_rows <= 0 || y_rows <= 0) return 0;
@@ -405,6 +477,12 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   p.cand_score = cand_score;
   p.cand_idx = cand_idx;
   p.cand_count = cand_count;
+  p.margin = margin;
+  p.band_rows = band_rows;
+  p.band_cols = band_cols;
+  p.band_count = band_count;
+  p.band_cap = band_cap;
+  if (margin != nullptr && (k > 0 || band_rows == nullptr || band_cols == nullptr || band_count == nullptr)) return -7;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -414,10 +492,16 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   const long long total = static_cast<long long>(p.nx_tiles) * p.ny_tiles;
   if (num_ctas > total) num_ctas = static_cast<int>(total);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int mode = k > 0 ? 1 : (margin != nullptr ? 2 : 0);
+#define DICE_EVAL_DISPATCH(DD)                                              \
+  case DD:                                                                  \
+    if (mode == 1) return launch<DD, 1>(tx, ty, p, num_ctas, s);            \
+    if (mode == 2) return launch<DD, 2>(tx, ty, p, num_ctas, s);            \
+    return launch<DD, 0>(tx, ty, p, num_ctas, s);
   switch (D) {
-    case 256: return k > 0 ? launch<256, true>(tx, ty, p, num_ctas, s) : launch<256, false>(tx, ty, p, num_ctas, s);
-    case 128: return k > 0 ? launch<128, true>(tx, ty, p, num_ctas, s) : launch<128, false>(tx, ty, p, num_ctas, s);
-    case 64: return k > 0 ? launch<64, true>(tx, ty, p, num_ctas, s) : launch<64, false>(tx, ty, p, num_ctas, s);
+    DICE_EVAL_DISPATCH(256)
+    DICE_EVAL_DISPATCH(128)
+    DICE_EVAL_DISPATCH(64)
     default: return -6;
   }
 }
@@ -457,14 +541,32 @@ extern "C" int dice_eval_rank_cand_cap(int x_rows, int y_rows, int D, int k, int
 extern "C" int dice_eval_sparse(const void* q, const void* y, int n, int D, int y_rows, int y_offset, int y_stride,
                                 const int* target, const float* col_bias, const float* target_in,
                                 const long long* filt_ptr, const int* filt_cols, float* target_score,
-                                int* filtered_greater, void* stream) {
+                                int* filtered_greater, int fp32_operands, void* stream) {
   using namespace dice::evalk;
   if (n <= 0) return 0;
   if (D % 2) return -6;
   const int threads = 256;
   const int blocks = (n * 32 + threads - 1) / threads;
-  eval_sparse_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(y), n, D, y_rows, y_offset,
-      y_stride > 0 ? y_stride : 1, target, col_bias, target_in, filt_ptr, filt_cols, target_score, filtered_greater);
+  if (fp32_operands)
+    eval_sparse_kernel<float><<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float*>(q), static_cast<const float*>(y), n, D, y_rows, y_offset,
+        y_stride > 0 ? y_stride : 1, target, col_bias, target_in, filt_ptr, filt_cols, target_score, filtered_greater);
+  else
+    eval_sparse_kernel<__nv_bfloat16><<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(y), n, D, y_rows, y_offset,
+        y_stride > 0 ? y_stride : 1, target, col_bias, target_in, filt_ptr, filt_cols, target_score, filtered_greater);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Exact pass over the pairs that dice_eval_rank left undecided (band mode): q and y are the fp32 operands.
+extern "C" int dice_eval_band_exact(const float* q, const float* y, int D, int y_rows, int y_offset, int y_stride,
+                                    const float* col_bias, const int* band_rows, const int* band_cols,
+                                    const unsigned long long* band_count, long long band_cap, const float* target,
+                                    int* greater, void* stream) {
+  using namespace dice::evalk;
+  if (D % 2) return -6;
+  eval_band_exact_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      q, y, D, y_rows, y_offset, y_stride > 0 ? y_stride : 1, col_bias, band_rows, band_cols, band_count, band_cap,
+      target, greater);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -90,9 +90,12 @@ def _use_fused(model, fused: Optional[bool]) -> bool:
 
 @torch.no_grad()
 def fused_tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 4096, ranker=None) -> torch.Tensor:
-    """:func:`tail_ranks` through the tcgen05 ranking kernel: no ``[B, |E|]`` score matrix, no sort.  Operands are
-    rounded to bf16 (fp32 accumulation), so ranks of near-tied entities can differ from the fp32 path."""
+    """:func:`tail_ranks` through the tcgen05 ranking kernel: no ``[B, |E|]`` score matrix, no sort.  The tensor
+    cores score bf16-rounded operands; entities whose score falls within the rounding margin of the target are
+    re-scored in fp32, so the ranks are those of an fp32 evaluation.  Should the list of such entities overflow
+    (targets ranked in the middle of a very large table), the batch is ranked from the bf16 scores alone."""
     from ..ops import eval_rank
+    from ..ops.kernels import KernelError
     ranker = ranker or eval_rank.ranker_for_model(model)
     dev = ranker.device
     out = []
@@ -100,7 +103,17 @@ def fused_tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 4
         b = triples[i:i + batch_size].to(dev)
         q, _ = eval_rank.model_queries(model, b[:, :2])
         ptr, cols = filter_csr(er_vocab, b[:, 0], b[:, 1])
-        out.append(ranker.ranks(q, b[:, 2], ptr, cols).cpu())
+        try:
+            r = ranker.ranks(q, b[:, 2], ptr, cols)
+        except KernelError:
+            if not ranker.exact:
+                raise
+            ranker.exact = False
+            try:
+                r = ranker.ranks(q, b[:, 2], ptr, cols)
+            finally:
+                ranker.exact = True
+        out.append(r.cpu())
     return torch.cat(out) if out else torch.zeros(0, dtype=torch.long)
 
 

@@ -307,7 +307,7 @@ class KGE:
         from .ops import eval_rank
         if not eval_rank.supports(self.model):
             return None
-        ranker = eval_rank.ranker_for_model(self.model)  # rebuilt per call: the weights may have been trained since
+        ranker = eval_rank.ranker_for_model(self.model, exact=False)  # rebuilt per call: the weights may have been trained since
         dev = self.model.device
         scores, indices = [], []
         for i in range(0, pairs.shape[0], batch_size):

@@ -44,13 +44,27 @@ class FusedRanker:
     """
 
     def __init__(self, table: torch.Tensor, col_bias: Optional[torch.Tensor] = None, y_offset: int = 0,
-                 y_stride: int = 1, group=None):
+                 y_stride: int = 1, group=None, exact: bool = False, band_capacity: int = 1 << 24):
+        """``exact``: ranks equal those of an fp32 scoring of the same operands.  The tensor cores still do the bulk
+        of the work on bf16-rounded operands; a score can differ from its fp32 value by at most
+        ``2^-8 · ‖q‖ · ‖e‖``, so only entities whose bf16 score lies within that margin of the target are undecided,
+        and exactly those (typically a fraction of a percent) are re-scored in fp32 by a second, sparse pass."""
         assert table.is_cuda, "the fused ranker runs on a CUDA device"
         self.d = table.shape[1]
         self.d_pad = pad_dim(self.d)
         if self.d_pad is None:
             raise ValueError(f"embedding width {self.d} exceeds the kernel's limit of {SUPPORTED_D[-1]}")
         self.table = to_kernel_operand(table, self.d_pad)
+        self.exact = bool(exact)
+        if self.exact:
+            t32 = table.detach().float()
+            if self.d != self.d_pad:
+                t32 = torch.nn.functional.pad(t32, (0, self.d_pad - self.d))
+            self.table_f32 = t32.contiguous()
+            self.row_norm_max = float(self.table_f32.norm(dim=1).max()) if table.shape[0] else 0.0
+            self.band_rows = torch.empty(band_capacity, dtype=torch.int32, device=table.device)
+            self.band_cols = torch.empty(band_capacity, dtype=torch.int32, device=table.device)
+            self.band_count = torch.zeros(1, dtype=torch.int64, device=table.device)
         self.col_bias = None if col_bias is None else col_bias.detach().float().contiguous()
         self.y_offset, self.y_stride, self.group = int(y_offset), int(y_stride), group
         self.device = table.device
@@ -76,6 +90,8 @@ class FusedRanker:
         if filt_ptr is not None:
             filt_ptr = filt_ptr.to(torch.int64).contiguous()
             filt_cols = filt_cols.to(torch.int32).contiguous()
+        if self.exact:
+            return self._ranks_exact(q, qk, tgt_idx, tgt_score, greater, filtered, filt_ptr, filt_cols)
         sharded = self.group is not None
         if sharded:  # phase 1: owners score their targets, phase 2: everybody counts against the merged scores
             kernels.eval_sparse(qk, self.table, tgt_idx, tgt_score, None, col_bias=self.col_bias,
@@ -93,6 +109,37 @@ class FusedRanker:
         if sharded:
             self._all_reduce(greater, filtered)
         kernels.check_status(self.status, "in dice_eval_rank")
+        return (1 + greater - filtered).long()
+
+    def _ranks_exact(self, q, qk, tgt_idx, tgt_score, greater, filtered, filt_ptr, filt_cols) -> torch.Tensor:
+        q32 = q.detach().float()
+        if self.d != self.d_pad:
+            q32 = torch.nn.functional.pad(q32, (0, self.d_pad - self.d))
+        q32 = q32.contiguous()
+        kw = dict(col_bias=self.col_bias, y_offset=self.y_offset, y_stride=self.y_stride)
+        sharded = self.group is not None
+        # exact target scores and exact filtered counts from the fp32 operands
+        kernels.eval_sparse(q32, self.table_f32, tgt_idx, tgt_score, None if sharded else
+                            (filtered if filt_ptr is not None else None), None if sharded else filt_ptr,
+                            None if sharded else filt_cols, **kw)
+        emax = torch.tensor([self.row_norm_max], device=self.device)
+        if sharded:
+            import torch.distributed as dist
+            self._all_reduce(tgt_score)
+            dist.all_reduce(emax, op=dist.ReduceOp.MAX, group=self.group)
+            if filt_ptr is not None:
+                kernels.eval_sparse(q32, self.table_f32, tgt_idx, None, filtered, filt_ptr, filt_cols,
+                                    target_in=tgt_score, **kw)
+        # |bf16 score - fp32 score| <= 2^-8 (1 + 2^-9) |q| |e|; a little head room for the fp32 accumulation orders
+        margin = (q32.norm(dim=1) * emax * (2.0 ** -8 * 1.01) + 1e-30).contiguous()
+        self.band_count.zero_()
+        kernels.eval_rank(qk, self.table, tgt_score, tgt_idx, greater, self.status, margin=margin,
+                          band_rows=self.band_rows, band_cols=self.band_cols, band_count=self.band_count, **kw)
+        kernels.eval_band_exact(q32, self.table_f32, self.band_rows, self.band_cols, self.band_count, tgt_score,
+                                greater, **kw)
+        if sharded:
+            self._all_reduce(greater, filtered)
+        kernels.check_status(self.status, "in dice_eval_rank (band list full: raise band_capacity or use smaller batches)")
         return (1 + greater - filtered).long()
 
     @torch.no_grad()
@@ -142,8 +189,9 @@ def supports(model) -> bool:
         and kernels._lib.available()
 
 
-def ranker_for_model(model) -> FusedRanker:
-    return FusedRanker(model.entity_embeddings.weight)
+def ranker_for_model(model, exact: bool = True) -> FusedRanker:
+    """Ranker over the model's entity table; ``exact`` (default) gives the ranks of an fp32 evaluation."""
+    return FusedRanker(model.entity_embeddings.weight, exact=exact)
 
 
 @torch.no_grad()

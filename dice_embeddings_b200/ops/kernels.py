@@ -239,10 +239,13 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
               greater: Optional[torch.Tensor], status: torch.Tensor, col_bias: Optional[torch.Tensor] = None,
               y_offset: int = 0, y_stride: int = 1, k: int = 0, cand_score: Optional[torch.Tensor] = None,
               cand_idx: Optional[torch.Tensor] = None, cand_count: Optional[torch.Tensor] = None,
-              num_ctas: int = 0) -> None:
+              num_ctas: int = 0, margin: Optional[torch.Tensor] = None, band_rows: Optional[torch.Tensor] = None,
+              band_cols: Optional[torch.Tensor] = None, band_count: Optional[torch.Tensor] = None) -> None:
     """``greater[i] += #{c : (x_i · y_c + col_bias[c]) > target[i], c != column of target_idx[i]}`` on the tcgen05
     path, plus per-segment top-``k`` candidates appended to ``cand_*`` when ``k > 0``.  Nothing of the score matrix
-    is written to memory."""
+    is written to memory.  With ``margin`` (band mode) only scores above ``target + margin`` are counted and the
+    pairs within ``±margin`` of the target are appended to ``band_rows / band_cols`` (``band_count``: int64 scalar)
+    for :func:`eval_band_exact`."""
     _req(x, torch.bfloat16, "x")
     _req(y, torch.bfloat16, "y")
     assert x.shape[1] == y.shape[1]
@@ -263,8 +266,25 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
     rc = _lib.lib().dice_eval_rank(_ptr(x), x.shape[0], _ptr(y), y.shape[0], x.shape[1], _ptr(target),
                                    _ptr(target_idx), _ptr(col_bias), int(y_offset), int(y_stride), _ptr(greater),
                                    int(k), int(cap), _ptr(cand_score), _ptr(cand_idx), _ptr(cand_count),
-                                   _ptr(status), int(num_ctas), _stream())
+                                   _ptr(status), int(num_ctas), _ptr(margin), _ptr(band_rows), _ptr(band_cols),
+                                   _ptr(band_count), 0 if band_rows is None else band_rows.numel(), _stream())
     _check(rc, "dice_eval_rank")
+
+
+def eval_band_exact(q: torch.Tensor, y: torch.Tensor, band_rows: torch.Tensor, band_cols: torch.Tensor,
+                    band_count: torch.Tensor, target: torch.Tensor, greater: torch.Tensor,
+                    col_bias: Optional[torch.Tensor] = None, y_offset: int = 0, y_stride: int = 1) -> None:
+    """Exact fp32 decision for the pairs the band mode of :func:`eval_rank` left open."""
+    _req(q, torch.float32, "q")
+    _req(y, torch.float32, "y")
+    _req(band_rows, torch.int32, "band_rows")
+    _req(band_cols, torch.int32, "band_cols")
+    _req(band_count, torch.int64, "band_count")
+    _req(greater, torch.int32, "greater")
+    _check(_lib.lib().dice_eval_band_exact(_ptr(q), _ptr(y), q.shape[1], y.shape[0], int(y_offset), int(y_stride),
+                                           _ptr(col_bias), _ptr(band_rows), _ptr(band_cols), _ptr(band_count),
+                                           band_rows.numel(), _ptr(target), _ptr(greater), _stream()),
+           "dice_eval_band_exact")
 
 
 def eval_rank_cand_cap(x_rows: int, y_rows: int, D: int, k: int, num_ctas: int = 0) -> int:
@@ -278,8 +298,9 @@ def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, targ
                 target_in: Optional[torch.Tensor] = None, y_offset: int = 0, y_stride: int = 1) -> None:
     """Gather-dots of the ranking protocol: the target score of each query and the number of filtered entities (CSR
     ``filt_ptr`` int64 / ``filt_cols`` int32) that beat it."""
-    _req(q, torch.bfloat16, "q")
-    _req(y, torch.bfloat16, "y")
+    fp32 = q.dtype == torch.float32
+    _req(q, torch.float32 if fp32 else torch.bfloat16, "q")
+    _req(y, q.dtype, "y")
     _req(target_idx, torch.int32, "target_idx")
     if filt_ptr is not None:
         _req(filt_ptr, torch.int64, "filt_ptr")
@@ -287,7 +308,7 @@ def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, targ
     rc = _lib.lib().dice_eval_sparse(_ptr(q), _ptr(y), q.shape[0], q.shape[1], y.shape[0], int(y_offset),
                                      int(y_stride), _ptr(target_idx), _ptr(col_bias), _ptr(target_in),
                                      _ptr(filt_ptr), _ptr(filt_cols), _ptr(target_score), _ptr(filtered_greater),
-                                     _stream())
+                                     int(fp32), _stream())
     _check(rc, "dice_eval_sparse")
 
 
