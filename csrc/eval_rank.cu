@@ -43,6 +43,8 @@ struct EvalParams {
   float* cand_score;       // [x_rows, cand_cap], pre-filled with -inf
   int* cand_idx;           // [x_rows, cand_cap], pre-filled with -1
   int* cand_count;         // [x_rows], zero-initialised
+  float* row_floor;        // [x_rows], pre-filled with -inf: best known lower bound of each row's k-th best score,
+                           // published by finished segments so that later segments start with a tight threshold
   // band mode (BAND variants): scores within +-margin[row] of the target are not decided here; their (row, entity)
   // pairs are appended to a list for an exact second pass, only scores above target + margin are counted
   const float* margin;     // [x_rows]
@@ -60,13 +62,19 @@ struct Cfg {
   static constexpr int SMEM_BYTES = TILE_BYTES * (1 + NSTAGE) + 1024 + 512;
 };
 
-template <int D, int MODE>  // 0 count, 1 count + top-k, 2 count with an undecided band
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+template <int D, int MODE>  // 0 count, 1 count + running top-k, 2 count with an undecided band, 3 collect above floor
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
                  const EvalParams p) {
   using C = Cfg<D>;
   constexpr bool TOPK = MODE == 1;
   constexpr bool BAND = MODE == 2;
+  constexpr bool COLLECT = MODE == 3;  // every score >= row_floor[row] is appended to the row's candidate list
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sX = smem;
@@ -219,7 +227,13 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         hi = tgt + mg;
         lo = tgt - mg;
       }
-      float thr = valid_x ? -CUDART_INF_F : CUDART_INF_F;
+      // scores at or below `floor_s` cannot be among the row's k best: some finished segment already holds k better
+      float floor_s = -CUDART_INF_F;
+      if constexpr (TOPK) {
+        if (valid_x && p.row_floor != nullptr) floor_s = p.row_floor[x_global];
+      }
+      if constexpr (COLLECT) floor_s = valid_x ? p.row_floor[x_global] : CUDART_INF_F;
+      float thr = valid_x ? floor_s : CUDART_INF_F;
       int minpos = 0;
       if constexpr (TOPK) {
         for (int j = 0; j < p.k; ++j) { top_s[j] = -CUDART_INF_F; top_i[j] = -1; }
@@ -247,6 +261,7 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
               const float s = __uint_as_float(r[i]);
               cnt += (s > hi && i != rel) ? 1 : 0;
               if constexpr (BAND) band |= ((s > lo && s <= hi && i != rel) ? 1u : 0u) << i;
+              if constexpr (COLLECT) band |= (s >= floor_s ? 1u : 0u) << i;
               if constexpr (TOPK) {
                 if (s > thr) {
                   top_s[minpos] = s;
@@ -255,6 +270,7 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                   minpos = 0;
                   for (int j = 1; j < p.k; ++j)
                     if (top_s[j] < thr) { thr = top_s[j]; minpos = j; }
+                  thr = fmaxf(thr, floor_s);
                 }
               }
             }
@@ -267,6 +283,7 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
               if (!in) s = -CUDART_INF_F;
               cnt += (s > hi && i != rel) ? 1 : 0;
               if constexpr (BAND) band |= ((s > lo && s <= hi && i != rel) ? 1u : 0u) << i;
+              if constexpr (COLLECT) band |= (s >= floor_s ? 1u : 0u) << i;
               if constexpr (TOPK) {
                 if (s > thr) {
                   top_s[minpos] = s;
@@ -275,7 +292,24 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                   minpos = 0;
                   for (int j = 1; j < p.k; ++j)
                     if (top_s[j] < thr) { thr = top_s[j]; minpos = j; }
+                  thr = fmaxf(thr, floor_s);
                 }
+              }
+            }
+          }
+          if constexpr (COLLECT) {
+            while (band) {  // rare: the floor is the k-th best score of a sample of the table
+              const int i = __ffs(band) - 1;
+              band &= band - 1;
+              const int pos = atomicAdd(p.cand_count + x_global, 1);
+              if (pos < p.cand_cap) {
+                float s = __uint_as_float(r[0]);
+#pragma unroll
+                for (int u = 1; u < 32; ++u) s = (u == i) ? __uint_as_float(r[u]) : s;
+                if (p.col_bias != nullptr) s += p.col_bias[tile_col0 + col0 + i];
+                p.cand_score[static_cast<size_t>(x_global) * p.cand_cap + pos] = s;
+                p.cand_idx[static_cast<size_t>(x_global) * p.cand_cap + pos] =
+                    p.y_offset + (tile_col0 + col0 + i) * p.y_stride;
               }
             }
           }
@@ -306,6 +340,7 @@ eval_rank_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       if (valid_x) {
         if (p.greater != nullptr && cnt != 0) atomicAdd(p.greater + x_global, cnt);
         if constexpr (TOPK) {
+          if (p.row_floor != nullptr && thr > floor_s) atomic_max_float(p.row_floor + x_global, thr);
           const int pos = atomicAdd(p.cand_count + x_global, p.k);
           if (pos + p.k <= p.cand_cap) {
             float* cs = p.cand_score + static_cast<size_t>(x_global) * p.cand_cap + pos;
@@ -447,13 +482,14 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
                               int k,
                               int cand_cap, float* cand_score, int* cand_idx, int* cand_count, int* status,
                               int num_ctas, const float* margin, int* band_rows, int* band_cols,
-                              unsigned long long* band_count, long long band_cap, void* stream) {
+                              unsigned long long* band_count, long long band_cap, float* row_floor, void* stream) {
   using namespace dice;
   using namespace dice::evalk;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15)) return -5;
-  if (k < 0 || k > KMAX) return -7;
-  if (k > 0 && (cand_score == nullptr || cand_idx == nullptr || cand_count == nullptr || cand_cap < k)) return -7;
+  if (k < -1 || k > KMAX) return -7;   // k == -1: collect mode (every score >= row_floor goes to the candidate lists)
+  if (k != 0 && (cand_score == nullptr || cand_idx == nullptr || cand_count == nullptr || cand_cap < k)) return -7;
+  if (k == -1 && row_floor == nullptr) return -7;
   CUtensorMap tx, ty;
   int rc = make_tmap_bf16(&tx, x, x_rows, D);
   if (rc) return rc;
@@ -477,6 +513,7 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   p.cand_score = cand_score;
   p.cand_idx = cand_idx;
   p.cand_count = cand_count;
+  p.row_floor = row_floor;
   p.margin = margin;
   p.band_rows = band_rows;
   p.band_cols = band_cols;
@@ -492,11 +529,12 @@ extern "C" int dice_eval_rank(const void* x, int x_rows, const void* y, int y_ro
   const long long total = static_cast<long long>(p.nx_tiles) * p.ny_tiles;
   if (num_ctas > total) num_ctas = static_cast<int>(total);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int mode = k > 0 ? 1 : (margin != nullptr ? 2 : 0);
+  const int mode = k > 0 ? 1 : (k == -1 ? 3 : (margin != nullptr ? 2 : 0));
 #define DICE_EVAL_DISPATCH(DD)                                              \
   case DD:                                                                  \
     if (mode == 1) return launch<DD, 1>(tx, ty, p, num_ctas, s);            \
     if (mode == 2) return launch<DD, 2>(tx, ty, p, num_ctas, s);            \
+    if (mode == 3) return launch<DD, 3>(tx, ty, p, num_ctas, s);            \
     return launch<DD, 0>(tx, ty, p, num_ctas, s);
   switch (D) {
     DICE_EVAL_DISPATCH(256)

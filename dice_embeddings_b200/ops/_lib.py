@@ -104,7 +104,7 @@ class _Sigs:
     dice_neg_sample = [_p, _i, _i, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _i, _f, _f, _p, _p, _p, _p, _p, _p]
     dice_candidate_bce = [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p, _f, _i, _f, _f, _i, _i, _i, _p, _p]
     dice_sparse_rows_optimizer = [_i, _p, _p, _p, _p, _p, _p, _l, _i, _p, _f, _f, _f, _f, _f, _p]
-    dice_eval_rank = [_p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _p]
+    dice_eval_rank = [_p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _p, _p]
     dice_eval_rank_cand_cap = [_i, _i, _i, _i, _i]
     dice_eval_sparse = [_p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p]
     dice_eval_band_exact = [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _l, _p, _p, _p]

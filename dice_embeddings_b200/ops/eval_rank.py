@@ -111,6 +111,52 @@ class FusedRanker:
         kernels.check_status(self.status, "in dice_eval_rank")
         return (1 + greater - filtered).long()
 
+    #: tables with more rows than this are searched in two stages (threshold from a prefix, then one collecting pass)
+    TWO_STAGE_ROWS = 131072
+    SAMPLE_ROWS = 32768
+
+    def _running_topk(self, qk: torch.Tensor, table: torch.Tensor, kk: int, col_bias):
+        """Per-segment running top-k lists in the kernel + merge: right for small tables (every thread keeps its own
+        list, which costs a warm-up per segment)."""
+        B = qk.shape[0]
+        cap = kernels.eval_rank_cand_cap(B, table.shape[0], self.d_pad, kk)
+        cs = torch.full((B, cap), float("-inf"), dtype=torch.float32, device=self.device)
+        ci = torch.full((B, cap), -1, dtype=torch.int32, device=self.device)
+        cc = torch.zeros(B, dtype=torch.int32, device=self.device)
+        floor = torch.full((B,), float("-inf"), dtype=torch.float32, device=self.device)
+        kernels.eval_rank(qk, table, None, None, None, self.status, col_bias=col_bias, y_offset=self.y_offset,
+                          y_stride=self.y_stride, k=kk, cand_score=cs, cand_idx=ci, cand_count=cc, row_floor=floor)
+        kernels.check_status(self.status, "in dice_eval_rank (top-k)")
+        sc, pos = torch.topk(cs, kk, dim=1)
+        return sc, torch.gather(ci, 1, pos).long()
+
+    def _topk_local(self, qk: torch.Tensor, kk: int):
+        n_local = self.table.shape[0]
+        if n_local <= self.TWO_STAGE_ROWS:
+            return self._running_topk(qk, self.table, kk, self.col_bias)
+        # stage 1: the k-th best score over a prefix of the table is a lower bound of the k-th best overall
+        S = self.SAMPLE_ROWS
+        bias_s = None if self.col_bias is None else self.col_bias[:S].contiguous()
+        sc_s, _ = self._running_topk(qk, self.table[:S], kk, bias_s)
+        floor = sc_s[:, kk - 1].contiguous()
+        # stage 2: one pass over the whole table that appends every score >= floor (few per row) to the row's list
+        B = qk.shape[0]
+        cap = int(4 * kk * (n_local / S) + 64)
+        for attempt in range(2):
+            cs = torch.full((B, cap), float("-inf"), dtype=torch.float32, device=self.device)
+            ci = torch.full((B, cap), -1, dtype=torch.int32, device=self.device)
+            cc = torch.zeros(B, dtype=torch.int32, device=self.device)
+            kernels.eval_rank(qk, self.table, None, None, None, self.status, col_bias=self.col_bias,
+                              y_offset=self.y_offset, y_stride=self.y_stride, k=-1, cand_score=cs, cand_idx=ci,
+                              cand_count=cc, row_floor=floor)
+            kernels.check_status(self.status, "in dice_eval_rank (collect)")
+            worst = int(cc.max())
+            if worst <= cap:
+                sc, pos = torch.topk(cs, kk, dim=1)
+                return sc, torch.gather(ci, 1, pos).long()
+            cap = worst + 64   # the prefix was not representative of the table (e.g. rows sorted by norm): exact size
+        return self._running_topk(qk, self.table, kk, self.col_bias)
+
     def _ranks_exact(self, q, qk, tgt_idx, tgt_score, greater, filtered, filt_ptr, filt_cols) -> torch.Tensor:
         q32 = q.detach().float()
         if self.d != self.d_pad:
@@ -156,16 +202,7 @@ class FusedRanker:
             ix = ix * self.y_stride + self.y_offset
         else:
             kk = min(k, n_local)
-            cap = kernels.eval_rank_cand_cap(B, n_local, self.d_pad, kk)
-            cs = torch.full((B, cap), float("-inf"), dtype=torch.float32, device=self.device)
-            ci = torch.full((B, cap), -1, dtype=torch.int32, device=self.device)
-            cc = torch.zeros(B, dtype=torch.int32, device=self.device)
-            kernels.eval_rank(qk, self.table, None, None, None, self.status, col_bias=self.col_bias,
-                              y_offset=self.y_offset, y_stride=self.y_stride, k=kk, cand_score=cs, cand_idx=ci,
-                              cand_count=cc)
-            kernels.check_status(self.status, "in dice_eval_rank (top-k)")
-            sc, pos = torch.topk(cs, kk, dim=1)
-            ix = torch.gather(ci, 1, pos).long()
+            sc, ix = self._topk_local(qk, kk)
         if self.group is not None:
             import torch.distributed as dist
             W = dist.get_world_size(self.group)

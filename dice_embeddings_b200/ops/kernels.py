@@ -240,13 +240,17 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
               y_offset: int = 0, y_stride: int = 1, k: int = 0, cand_score: Optional[torch.Tensor] = None,
               cand_idx: Optional[torch.Tensor] = None, cand_count: Optional[torch.Tensor] = None,
               num_ctas: int = 0, margin: Optional[torch.Tensor] = None, band_rows: Optional[torch.Tensor] = None,
-              band_cols: Optional[torch.Tensor] = None, band_count: Optional[torch.Tensor] = None) -> None:
+              band_cols: Optional[torch.Tensor] = None, band_count: Optional[torch.Tensor] = None,
+              row_floor: Optional[torch.Tensor] = None) -> None:
     """``greater[i] += #{c : (x_i · y_c + col_bias[c]) > target[i], c != column of target_idx[i]}`` on the tcgen05
     path, plus per-segment top-``k`` candidates appended to ``cand_*`` when ``k > 0``.  Nothing of the score matrix
     is written to memory.  With ``margin`` (band mode) only scores above ``target + margin`` are counted and the
     pairs within ``±margin`` of the target are appended to ``band_rows / band_cols`` (``band_count``: int64 scalar)
-    for :func:`eval_band_exact`."""
+    for :func:`eval_band_exact`.  ``row_floor`` (top-k mode; fp32 ``[x_rows]`` filled with ``-inf``) lets finished
+    segments publish their k-th best score so that later segments of the same row start with a tight threshold."""
     _req(x, torch.bfloat16, "x")
+    if row_floor is not None:
+        _req(row_floor, torch.float32, "row_floor")
     _req(y, torch.bfloat16, "y")
     assert x.shape[1] == y.shape[1]
     if target is not None:
@@ -258,7 +262,7 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
     if col_bias is not None:
         _req(col_bias, torch.float32, "col_bias")
     cap = 0
-    if k > 0:
+    if k != 0:   # k > 0: running top-k per segment; k == -1: collect every score >= row_floor[row]
         _req(cand_score, torch.float32, "cand_score")
         _req(cand_idx, torch.int32, "cand_idx")
         _req(cand_count, torch.int32, "cand_count")
@@ -267,7 +271,8 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
                                    _ptr(target_idx), _ptr(col_bias), int(y_offset), int(y_stride), _ptr(greater),
                                    int(k), int(cap), _ptr(cand_score), _ptr(cand_idx), _ptr(cand_count),
                                    _ptr(status), int(num_ctas), _ptr(margin), _ptr(band_rows), _ptr(band_cols),
-                                   _ptr(band_count), 0 if band_rows is None else band_rows.numel(), _stream())
+                                   _ptr(band_count), 0 if band_rows is None else band_rows.numel(),
+                                   _ptr(row_floor), _stream())
     _check(rc, "dice_eval_rank")
 
 

@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--topk", type=int, default=0, help="also time top-k mode with this k on the first 256 queries")
+    ap.add_argument("--topk_queries", type=int, default=256)
     ap.add_argument("--compare", action="store_true")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
@@ -59,9 +60,25 @@ def main():
           f"{tf / pk['bf16_tflops']:.2f} of {pk['source']} ({pk['bf16_tflops']:.0f})")
     if a.topk:
         r = FusedRanker(y)
-        n = min(256, a.queries)
+        n = min(a.topk_queries, a.queries)
         ms = timed(lambda: r.topk(q[:n], a.topk), max(a.iters // 2, 1))
-        print(f"top-{a.topk} of {n} queries over {a.entities} entities: {ms * 1e3:9.1f} us")
+        print(f"top-{a.topk} of {n} queries over {a.entities} entities: {ms * 1e3:9.1f} us (with candidate merge)")
+        cap = K.eval_rank_cand_cap(n, a.entities, a.d, a.topk)
+        cs = torch.full((n, cap), float("-inf"), device=dev)
+        ci = torch.full((n, cap), -1, dtype=torch.int32, device=dev)
+        cc = torch.zeros(n, dtype=torch.int32, device=dev)
+        qn = q[:n].contiguous()
+
+        fl = torch.empty(n, device=dev)
+
+        def kernel_only():
+            cc.zero_()
+            fl.fill_(float("-inf"))
+            K.eval_rank(qn, y, None, None, None, status, k=a.topk, cand_score=cs, cand_idx=ci, cand_count=cc,
+                        row_floor=fl)
+        ms = timed(kernel_only, max(a.iters // 2, 1))
+        tfk = 2.0 * n * a.entities * a.d / (ms * 1e-3) / 1e12
+        print(f"   kernel alone: {ms * 1e3:9.1f} us  {tfk:7.1f} TFLOP/s  (candidate capacity {cap} per row)")
     if a.compare:
         def torch_counts():
             out = []

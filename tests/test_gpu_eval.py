@@ -160,3 +160,20 @@ def test_exact_mode_reproduces_fp32_ranks(nx, ny, D):
     rough = FusedRanker(y, exact=False).ranks(x, tgt, ptr, cols)
     assert (exact == ref).float().mean() > 0.998 and (exact - ref).abs().max() <= 1   # fp32 vs fp64 ties only
     assert (rough == ref).float().mean() < (exact == ref).float().mean()            # the band pass is what fixes them
+
+
+@pytest.mark.parametrize("adversarial", [False, True])
+def test_two_stage_topk_over_a_large_table(adversarial):
+    """Tables above the two-stage limit: threshold from a prefix, one collecting pass; with rows sorted by norm the
+    prefix is not representative, the candidate lists overflow and the pass is repeated with the exact size."""
+    nx, ny, D, k = 70, 300000, 128, 10
+    x, y = _operands(nx, ny, D, 9)
+    if adversarial:
+        scale = torch.linspace(0.05, 3.0, ny, device=DEV)[:, None]
+        y = (y.float() * scale).to(torch.bfloat16)
+    r = FusedRanker(y)
+    assert ny > r.TWO_STAGE_ROWS
+    sc, ix = r.topk(x, k)
+    ref_s, ref_i = torch.topk(x.float() @ y.float().t(), k, dim=1)
+    assert torch.allclose(sc, ref_s, atol=5e-3, rtol=2e-3)
+    assert (ix == ref_i).float().mean() > 0.97
