@@ -20,7 +20,7 @@ from typing import Dict, Optional
 import numpy as np
 import torch
 
-from ..data.vocab import PairCSR, ee_csr, er_csr, re_csr
+from ..data.vocab import ee_csr, er_csr, re_csr
 from .link_prediction import evaluate_bpe_lp, evaluate_lp_bpe_k_vs_all
 from .ranking import head_and_tail_ranks, metrics_from_ranks, relation_ranks, tail_ranks
 

@@ -10,7 +10,6 @@ long, so attention goes through PyTorch's fused SDPA; no custom kernel is warran
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch

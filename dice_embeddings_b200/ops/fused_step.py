@@ -125,8 +125,8 @@ class FusedKvsAllEngine:
         # the sparse correction kernels
         mask_bytes = 2 * self.B * self.NE / 8
         self.label_mode = label_mode or ("mask" if mask_bytes <= (1 << 30) else "sparse")
-        # which of the two scoring passes also accumulates the loss (its epilogue is the longer one)
-        self.loss_in_query_pass = os.environ.get("DICE_B200_LOSS_PASS", "entity") == "query"
+        # which of the two scoring passes also accumulates the loss; measured equal either way, the entity pass keeps it
+        self.loss_in_query_pass = False
         self._bufs = {}
         self._graphs = {}
 

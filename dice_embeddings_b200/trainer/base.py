@@ -6,7 +6,6 @@ reference ``dicee/abstracts.py:18-150, 474-581``) so user callbacks written agai
 """
 from __future__ import annotations
 
-import time
 from typing import Iterator, List, Optional
 
 import torch

@@ -26,7 +26,7 @@ import torch
 
 from ..data.datasets import construct_dataset
 from ..data.kg import KG
-from ..io.checkpoint import read_index_csv, select_model
+from ..io.checkpoint import select_model
 from ..models import EnsembleKGE
 from .base import BatchLoader
 from .torch_trainer import TorchTrainer

@@ -13,8 +13,6 @@ gradients are only *zeroed* every ``k`` batches while the optimiser still steps 
 from __future__ import annotations
 
 import time
-from typing import Optional
-
 import torch
 
 from .base import AbstractTrainer, BatchLoader
