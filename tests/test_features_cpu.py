@@ -121,3 +121,39 @@ def test_ensemble_of_runs_is_evaluated(umls_like_dir, tmp_path):
                                                          weighted_averaging=False)
     for o in (out, plain):
         assert 0 < o["MRR"] <= 1 and o["H@10"] >= o["H@1"]
+
+
+def test_online_learning_moves_scores(umls_like_dir, tmp_path):
+    """A stored model is fine-tuned on single triples and on one (h, r) pair (reference tests/test_online_learning.py)."""
+    rep = Execute(_args(umls_like_dir, tmp_path / "r", model="AConEx", scoring_technique="1vsSample", neg_ratio=1,
+                        num_epochs=0, num_of_output_channels=2)).start()
+    assert os.path.isdir(rep["path_experiment_folder"])
+    k = KGE(path=rep["path_experiment_folder"])
+    tr = np.load(tmp_path / "r" / "train_set.npy")
+    h, r, t = k.idx_to_entity[int(tr[0, 0])], k.idx_to_relations[int(tr[0, 1])], k.idx_to_entity[int(tr[0, 2])]
+    first = float(k.triple_score(h=[h], r=[r], t=[h]))
+    k.train_triples(h=[h], r=[r], t=[h], labels=[0.0], iteration=3,
+                    optimizer=torch.optim.Adam(params=k.parameters(), lr=0.01))
+    assert float(k.triple_score(h=[h], r=[r], t=[h])) < first
+    before = float(k.triple_score(h=[h], r=[r], t=[t]))
+    k.train_k_vs_all(h=[h], r=[r], iteration=5, lr=0.01)
+    assert float(k.triple_score(h=[h], r=[r], t=[t])) > before
+    k.save()                                     # the fine-tuned weights can be stored next to the original run
+
+
+@pytest.mark.parametrize("backend", ["pandas", "polars", "rdflib"])
+def test_reading_backends(umls_like_dir, tmp_path, backend):
+    """``polars`` falls back to the pandas reader when the package is absent; ``rdflib`` needs the package."""
+    kw = {}
+    if backend == "rdflib":
+        pytest.importorskip("rdflib")
+        import pandas as pd
+        df = pd.read_csv(os.path.join(umls_like_dir, "train.txt"), sep=r"\\s+", header=None)
+        nt = tmp_path / "kg.nt"
+        with open(nt, "w") as f:
+            for s, p, o in df.head(300).itertuples(index=False):
+                f.write(f"<http://x/{s}> <http://x/{p}> <http://x/{o}> .\\n")
+        kw = dict(dataset_dir=None, path_single_kg=str(nt))
+    rep = Execute(_args(kw.pop("dataset_dir", umls_like_dir), tmp_path / "r", backend=backend, num_epochs=3,
+                        **kw)).start()
+    assert rep["num_train_triples"] > 0 and np.isfinite(rep["Train"]["MRR"])
