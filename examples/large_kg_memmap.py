@@ -3,6 +3,10 @@ directory, so a second start skips reading and indexing and maps ``memory_map_tr
 
     python examples/large_kg_memmap.py --path_single_kg big.tsv --out Experiments/big
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 import argparse
 
 from dice_embeddings_b200 import Execute, Namespace

@@ -4,6 +4,10 @@
 
 The literal files hold one ``entity<TAB>attribute<TAB>value`` row per line.
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 import argparse
 
 from dice_embeddings_b200 import KGE

@@ -2,6 +2,10 @@
 
     python examples/multi_hop_queries.py --dataset_dir KGs/UMLS --run Experiments/<run>
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 import argparse
 
 from dice_embeddings_b200 import KGE, QueryGenerator, evaluate

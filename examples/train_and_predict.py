@@ -2,6 +2,10 @@
 
     python examples/train_and_predict.py --dataset_dir KGs/UMLS --model Keci
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 import argparse
 
 from dice_embeddings_b200 import Execute, KGE, Namespace

@@ -42,9 +42,12 @@ def test_sharded_sampled_engine_matches_autograd_and_learns():
     assert res.returncode == 0 and "SHARDED_SAMPLED_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
 
-@pytest.mark.parametrize("st,extra", [("NegSample", ["--neg_ratio", "16"]), ("KvsAll", [])])
+@pytest.mark.parametrize("st,extra", [("NegSample", ["--neg_ratio", "16"]), ("KvsAll", []),
+                                      ("KvsAll", ["--trainer", "torchDDP", "--model", "ConEx", "--num_of_output_channels", "2",
+                                                  "--embedding_dim", "32", "--lr", "0.02"])])
 def test_sharded_trainer_through_the_command_line(tmp_path, st, extra):
-    """``--trainer Sharded`` end to end on two ranks: training, gathering the shards, evaluation, stored run."""
+    """``--trainer Sharded`` end to end on two ranks: training, gathering the shards, evaluation, stored run; the
+    last case is a model outside the fused kernels on ``torchDDP`` (replicated model, gradient all-reduce)."""
     import json
     sys.path.insert(0, os.path.dirname(HERE))
     from dice_embeddings_b200.data.synthetic import make_planted_kg
@@ -59,5 +62,5 @@ def test_sharded_trainer_through_the_command_line(tmp_path, st, extra):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     rep = json.load(open(out / "eval_report.json"))
-    assert rep["Train"]["MRR"] > (0.5 if st == "KvsAll" else 0.3), rep
+    assert rep["Train"]["MRR"] > (0.3 if (st != "KvsAll" or "ConEx" in extra) else 0.5), rep
     assert os.path.isfile(out / "model.pt")
