@@ -161,26 +161,16 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
   }
 }
 
-// SPLIT (D = 256 only): the two GEMMs of a tile read Y from two separate slab rings.  Ring A (6 slabs of 16 KB) feeds
-// S = X · Yᵀ and frees every slab as soon as its four MMAs are done; ring B (4 slabs) is filled a second time from
-// L2 for out += dS · Y.  A slab therefore is no longer held from the first GEMM through the epilogue to the second,
-// which with whole-tile stages limited the pipeline to two tiles and left the tensor pipe waiting for refills.
-constexpr int RING_A = 6;
-constexpr int RING_B = 4;
-
-template <int D, bool LOSS, bool MASK, bool SPLIT>
+template <int D, bool LOSS, bool MASK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
                     const KvsAllParams p) {
   using C = Cfg<D>;
-  static_assert(!SPLIT || D == 256, "the split rings are laid out for D = 256");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sX = smem;
   uint8_t* sY = smem + C::TILE_BYTES;
-  uint8_t* sB = sY + RING_A * SLAB_BYTES;  // SPLIT: ring B behind ring A
-  uint64_t* bars = reinterpret_cast<uint64_t*>(
-      smem + (SPLIT ? C::TILE_BYTES + (RING_A + RING_B) * SLAB_BYTES : C::TILE_BYTES * (1 + C::NSTAGE)));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::TILE_BYTES * (1 + C::NSTAGE));
   uint64_t* x_full = bars + 0;
   uint64_t* x_empty = bars + 1;
   uint64_t* dx_full = bars + 2;
@@ -189,10 +179,6 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   uint64_t* ds_full = bars + 6;      // [2]
   uint64_t* y_empty = bars + 8;      // [NSTAGE]
   uint64_t* y_full = bars + 12;      // [NSTAGE][4]: one per 64-column slab, so the S GEMM starts on the first slab
-  uint64_t* a_full = bars + 8;       // SPLIT: [RING_A]
-  uint64_t* a_empty = bars + 14;     // SPLIT: [RING_A]
-  uint64_t* b_full = bars + 20;      // SPLIT: [RING_B]
-  uint64_t* b_empty = bars + 24;     // SPLIT: [RING_B]
   uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 28);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 29);
 
@@ -213,14 +199,9 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(s_full + i, 1);
       mbar_init(ds_full + i, NUM_EPI_WARPS);
     }
-    if constexpr (SPLIT) {
-      for (int i = 0; i < RING_A; ++i) { mbar_init(a_full + i, 1); mbar_init(a_empty + i, 1); }
-      for (int i = 0; i < RING_B; ++i) { mbar_init(b_full + i, 1); mbar_init(b_empty + i, 1); }
-    } else {
-      for (int i = 0; i < C::NSTAGE; ++i) {
-        mbar_init(y_empty + i, 1);
-        for (int sl = 0; sl < C::NSLAB; ++sl) mbar_init(y_full + i * 4 + sl, 1);
-      }
+    for (int i = 0; i < C::NSTAGE; ++i) {
+      mbar_init(y_empty + i, 1);
+      for (int sl = 0; sl < C::NSLAB; ++sl) mbar_init(y_full + i * 4 + sl, 1);
     }
     *reinterpret_cast<volatile uint64_t*>(bars + 29) = 0;  // abort flag and an always-zero word next to it
     fence_barrier_init();
@@ -251,64 +232,7 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   if (warp == 0) {
     // =========================================================================== TMA producer
-    if (lane == 0 && SPLIT) {
-      // two independent slab streams over the same tile sequence; whichever ring has a free slot is served
-      TileCursor ca, cb;
-      ca.start(w_begin, w_end, p.map);
-      cb.start(w_begin, w_end, p.map);
-      uint32_t na = 0, nb = 0, x_loads = 0, idle = 0;
-      bool ok = true;
-      while ((!ca.done() || !cb.done()) && ok && !*s_abort) {
-        bool progressed = false;
-        if (!ca.done() && mbar_try_wait(a_empty + na % RING_A, ((na / RING_A) & 1) ^ 1)) {
-          const int sl = na & 3;
-          bool go = true;
-          if (sl == 0 && ca.first()) {  // first slab of a segment: the X tile goes first
-            go = mbar_try_wait(x_empty, (ca.seg & 1) ^ 1);
-            if (go) {
-              mbar_arrive_expect_tx(x_full, C::TILE_BYTES);
-              for (int s2 = 0; s2 < C::NSLAB; ++s2)
-                tma_load_2d(sX + s2 * SLAB_BYTES, &tmap_x, s2 * 64, ca.x * BLOCK_X, x_full);
-              ++x_loads;
-            }
-          }
-          if (go) {
-            if (sl == 0) stamp(na >> 2, 0);
-            const uint32_t slot = na % RING_A;
-            mbar_arrive_expect_tx(a_full + slot, SLAB_BYTES);
-            tma_load_2d(sY + slot * SLAB_BYTES, &tmap_y, sl * 64, (ca.y0 + ca.t) * BLOCK_Y, a_full + slot);
-            ++na;
-            if ((na & 3) == 0) ca.advance();
-            progressed = true;
-          }
-        }
-        if (!cb.done() && mbar_try_wait(b_empty + nb % RING_B, ((nb / RING_B) & 1) ^ 1)) {
-          const uint32_t slot = nb % RING_B;
-          mbar_arrive_expect_tx(b_full + slot, SLAB_BYTES);
-          tma_load_2d(sB + slot * SLAB_BYTES, &tmap_y, (nb & 3) * 64, (cb.y0 + cb.t) * BLOCK_Y, b_full + slot);
-          ++nb;
-          if ((nb & 3) == 0) cb.advance();
-          progressed = true;
-        }
-        if (progressed) idle = 0;
-        else if (++idle > DICE_WAIT_LIMIT) ok = false;
-        else if (idle > 256) __nanosleep(32);
-      }
-      if (!ok) fail(ST_TIMEOUT_PRODUCER);
-      if (*s_abort) {  // every copy issued by this thread must land before the CTA may exit
-        bool drained = true;
-        if (x_loads > 0) drained &= mbar_wait_bounded(x_full, (x_loads - 1) & 1, s_abort + 1, 1u << 20);
-        for (uint32_t i = 0; i < RING_A && i < na; ++i) {
-          const uint32_t last = na - 1 - i;
-          drained &= mbar_wait_bounded(a_full + last % RING_A, (last / RING_A) & 1, s_abort + 1, 1u << 20);
-        }
-        for (uint32_t i = 0; i < RING_B && i < nb; ++i) {
-          const uint32_t last = nb - 1 - i;
-          drained &= mbar_wait_bounded(b_full + last % RING_B, (last / RING_B) & 1, s_abort + 1, 1u << 20);
-        }
-        if (!drained) atomicExch(p.status, ST_TIMEOUT_DRAIN);
-      }
-    } else if (lane == 0) {
+    if (lane == 0) {
       uint32_t ycount = 0, seg = 0;
       uint32_t x_loads = 0;
       for (long long w = w_begin; w < w_end && !*s_abort;) {
@@ -360,36 +284,13 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const uint64_t ydesc_g1 = make_sw128_desc(smem_u32(sY), 16, 1024);
       const uint64_t ydesc_g2 = make_sw128_desc(smem_u32(sY), SLAB_BYTES, 1024);
 
-      const uint64_t bdesc_g2 = make_sw128_desc(smem_u32(sB), SLAB_BYTES, 1024);
-      constexpr uint32_t IDESC_G2_HALF = make_idesc_bf16(BLOCK_X, 128, 0, 1);  // SPLIT: out[:, 128 h ..] += dS · Y
-
       auto issue_g1 = [&](uint32_t gi) -> bool {
-        stamp(gi, 1);
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_s0 + (gi & 1) * BLOCK_Y;
-        if constexpr (SPLIT) {
-#pragma unroll
-          for (int sl = 0; sl < 4; ++sl) {
-            const uint32_t a = gi * 4 + sl, slot = a % RING_A;
-            if (sl > 0) {  // slab 0 was probed by the caller
-              if (!mbar_wait_bounded(a_full + slot, (a / RING_A) & 1, s_abort)) return false;
-              tc_fence_after();
-            }
-            const uint64_t yd = ydesc_g1 + slot * (SLAB_BYTES >> 4);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t xd = xdesc + sl * (SLAB_BYTES >> 4) + kk * 2;
-              if (sl == 0 && kk == 0) mma_ss(d_tmem, xd, yd + kk * 2, IDESC_G1, 0u);
-              else mma_ss(d_tmem, xd, yd + kk * 2, IDESC_G1, 1u);
-            }
-            tc_commit(a_empty + slot);  // this slab may be refilled as soon as its four MMAs are done
-          }
-          tc_commit(s_full + (gi & 1));
-          return true;
-        } else {
         const uint32_t st = gi % C::NSTAGE;
         const uint32_t par = (gi / C::NSTAGE) & 1;
+        stamp(gi, 1);
+        tc_fence_after();
         const uint64_t yd = ydesc_g1 + st * (C::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_s0 + (gi & 1) * BLOCK_Y;
 #pragma unroll
         for (int sl = 0; sl < C::NSLAB; ++sl) {
           if (sl > 0) {  // slab 0 was probed by the caller
@@ -405,34 +306,13 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         tc_commit(s_full + (gi & 1));
         return true;
-        }
       };
-      auto issue_g2 = [&](uint32_t gi, bool first, bool last) -> bool {
+      auto issue_g2 = [&](uint32_t gi, bool first, bool last) {
+        const uint32_t st = gi % C::NSTAGE;
         stamp(gi, 2);
         tc_fence_after();
-        const uint32_t a_base = tmem_s0 + (gi & 1) * BLOCK_Y;
-        if constexpr (SPLIT) {
-#pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {  // two halves of the 256 output columns, two slabs of ring B each
-            const uint32_t b0 = gi * 4 + hc * 2, slot = b0 % RING_B;
-            if (!mbar_wait_bounded(b_full + slot, (b0 / RING_B) & 1, s_abort)) return false;
-            if (!mbar_wait_bounded(b_full + slot + 1, ((b0 + 1) / RING_B) & 1, s_abort)) return false;
-            tc_fence_after();
-            const uint64_t yd = bdesc_g2 + slot * (SLAB_BYTES >> 4);
-#pragma unroll
-            for (int k = 0; k < BLOCK_Y / 16; ++k) {
-              const uint32_t a_tmem = a_base + 32 * (k >> 1) + 8 * (k & 1);
-              if (k == 0) mma_ts(tmem_out + 128 * hc, a_tmem, yd, IDESC_G2_HALF, first ? 0u : 1u);
-              else mma_ts(tmem_out + 128 * hc, a_tmem, yd + k * 128, IDESC_G2_HALF, 1u);
-            }
-            tc_commit(b_empty + slot);
-            tc_commit(b_empty + slot + 1);
-          }
-          if (last) tc_commit(dx_full);
-          return true;
-        } else {
-        const uint32_t st = gi % C::NSTAGE;
         const uint64_t yd = ydesc_g2 + st * (C::TILE_BYTES >> 4);
+        const uint32_t a_base = tmem_s0 + (gi & 1) * BLOCK_Y;
 #pragma unroll
         for (int k = 0; k < BLOCK_Y / 16; ++k) {
           // dS: the 32 K elements of column group c are packed into columns [32 c, 32 c + 16) of the S buffer
@@ -444,8 +324,6 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         tc_commit(y_empty + st);
         if (last) tc_commit(dx_full);
-        return true;
-        }
       };
 
       TileCursor c1, c2;
@@ -457,14 +335,13 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         bool progressed = false;
         if (g2 < g1 && mbar_try_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
             (!c2.first() || mbar_try_wait(dx_empty, (c2.seg & 1) ^ 1))) {
-          if (!issue_g2(g2, c2.first(), c2.last())) { ok = false; break; }
+          issue_g2(g2, c2.first(), c2.last());
           ++g2;
           c2.advance();
           progressed = true;
         }
         if (!progressed && !c1.done() && g1 - g2 < 2 && (!c1.first() || mbar_try_wait(x_full, c1.seg & 1)) &&
-            (SPLIT ? mbar_try_wait(a_full + (g1 * 4) % RING_A, ((g1 * 4) / RING_A) & 1)
-                   : mbar_try_wait(y_full + (g1 % C::NSTAGE) * 4, (g1 / C::NSTAGE) & 1))) {
+            mbar_try_wait(y_full + (g1 % C::NSTAGE) * 4, (g1 / C::NSTAGE) & 1)) {
           if (!issue_g1(g1)) { ok = false; break; }
           if (c1.last()) tc_commit(x_empty);  // last S GEMM of the segment: the X buffer may be refilled
           ++g1;
@@ -601,19 +478,17 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int D, bool LOSS, bool MASK, bool SPLIT = false>
+template <int D, bool LOSS, bool MASK>
 static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllParams& p, int num_ctas,
                   cudaStream_t stream) {
-  auto kern = kvsall_fused_kernel<D, LOSS, MASK, SPLIT>;
-  constexpr int smem_bytes =
-      SPLIT ? Cfg<D>::TILE_BYTES + (RING_A + RING_B) * SLAB_BYTES + 1024 + 512 : Cfg<D>::SMEM_BYTES;
+  auto kern = kvsall_fused_kernel<D, LOSS, MASK>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES) != cudaSuccess)
       return -3;
     configured = true;
   }
-  kern<<<num_ctas, NUM_THREADS, smem_bytes, stream>>>(tx, ty, p);
+  kern<<<num_ctas, NUM_THREADS, Cfg<D>::SMEM_BYTES, stream>>>(tx, ty, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -623,11 +498,6 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 // writes clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
 // 4 epilogue wrote dS, 5 out tile drained).  Pass null to switch it off again.
 static long long* g_trace_buffer = nullptr;
-static int g_split_rings = 0;  // D = 256: 0 = whole-tile stages, 1 = split slab rings
-extern "C" int dice_kvsall_set_split_rings(int on) {
-  g_split_rings = on;
-  return 0;
-}
 extern "C" int dice_kvsall_set_trace(long long* buffer) {
   g_trace_buffer = buffer;
   return 0;
@@ -680,10 +550,6 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool wl = with_loss != 0;
   const bool mk = mask != nullptr;
-  if (D == 256 && g_split_rings) {
-    if (wl) return mk ? launch<256, true, true, true>(tx, ty, p, num_ctas, s) : launch<256, true, false, true>(tx, ty, p, num_ctas, s);
-    return mk ? launch<256, false, true, true>(tx, ty, p, num_ctas, s) : launch<256, false, false, true>(tx, ty, p, num_ctas, s);
-  }
 #define DICE_DISPATCH(DD)                                                                        \
   case DD:                                                                                       \
     if (wl) return mk ? launch<DD, true, true>(tx, ty, p, num_ctas, s) : launch<DD, true, false>(tx, ty, p, num_ctas, s); \

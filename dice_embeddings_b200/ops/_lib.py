@@ -77,8 +77,6 @@ def lib() -> ctypes.CDLL:
                 fn = getattr(_lib, name)
                 fn.restype = ctypes.c_int
                 fn.argtypes = getattr(_Sigs, name)
-        if os.environ.get("DICE_B200_SPLIT_RINGS") is not None:
-            _lib.dice_kvsall_set_split_rings(int(os.environ["DICE_B200_SPLIT_RINGS"] == "1"))
     return _lib
 
 
@@ -101,7 +99,6 @@ class _Sigs:
     dice_finish_step = [_p, _p, _d, _p, _p, _i, _p]
     dice_p2p_barrier = [_p, _i, _i, _p, _p, ctypes.c_uint, _p]
     dice_kvsall_set_trace = [_p]
-    dice_kvsall_set_split_rings = [_i]
     dice_timestamp = [_p, _p]
     dice_uniform_int = [_p, _l, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _l, _l, _p]
     dice_neg_sample = [_p, _i, _i, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _i, _f, _f, _p, _p, _p, _p, _p, _p]

@@ -150,12 +150,6 @@ def timestamp(slots: torch.Tensor, index: int) -> None:
     _check(_lib.lib().dice_timestamp(slots.data_ptr() + 8 * int(index), _stream()), "dice_timestamp")
 
 
-def kvsall_set_split_rings(on: bool) -> None:
-    """D = 256 only: choose between whole-tile Y stages (``False``) and the split slab rings (``True``) of
-    ``kvsall_fused``; the environment variable ``DICE_B200_SPLIT_RINGS`` sets the initial choice."""
-    _lib.lib().dice_kvsall_set_split_rings(int(bool(on)))
-
-
 def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
     """Register (or clear with ``None``) a ``[64, 8]`` int64 device buffer receiving per-tile clock stamps of CTA 0 of
     every following ``kvsall_fused`` launch (pipeline diagnostics; see ``profile_fused --trace``)."""

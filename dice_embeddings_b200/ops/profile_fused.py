@@ -25,11 +25,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mask", action="store_true")
     ap.add_argument("--trace", action="store_true", help="print per-tile pipeline stamps of CTA 0 (cycles)")
-    ap.add_argument("--split", type=int, default=None, help="D=256: 1 = split slab rings, 0 = whole-tile stages")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
-    if a.split is not None:
-        K.kvsall_set_split_rings(bool(a.split))
     torch.manual_seed(0)
     x = (torch.randn(a.nx, a.d, device=dev) * 0.1).to(torch.bfloat16)
     y = (torch.randn(a.ny, a.d, device=dev) * 0.1).to(torch.bfloat16)
