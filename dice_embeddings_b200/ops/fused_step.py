@@ -135,6 +135,7 @@ class FusedKvsAllEngine:
         if n not in self._bufs:
             dev = self.device
             b = SimpleNamespace()
+            b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=dev)   # the batch's (h, r) pairs as they arrive
             b.h = torch.zeros(n, dtype=torch.int64, device=dev)
             b.r = torch.zeros(n, dtype=torch.int64, device=dev)
             b.dp = torch.zeros(n, dtype=torch.int64, device=dev)
@@ -152,6 +153,8 @@ class FusedKvsAllEngine:
 
     def _launch_all(self, b, n: int) -> None:
         scale = 1.0 / (float(n) * float(self.NE))
+        b.h.copy_(b.x_in[:, 0])   # inside the captured sequence: callers only fill x_in and dp
+        b.r.copy_(b.x_in[:, 1])
         K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,
                          None, n, self.D, self.status)
         if self.label_mode == "mask":
@@ -184,7 +187,7 @@ class FusedKvsAllEngine:
 
     #: number of kernels of this library launched per step (for launch accounting)
     def launches_per_step(self) -> int:
-        return (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
+        return (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)   # kernels of this library
 
     def _run(self, b, n: int) -> None:
         key = (n, self.lr)
@@ -230,8 +233,7 @@ class FusedKvsAllEngine:
         x, dp = batch[0], batch[1]
         n = x.shape[0]
         b = self._buffers(n)
-        b.h.copy_(x[:, 0])
-        b.r.copy_(x[:, 1])
+        b.x_in.copy_(x)
         b.dp.copy_(dp)
         self._run(b, n)
         return self.loss_out[0]
@@ -241,12 +243,8 @@ class FusedKvsAllEngine:
         device→host read of the loss."""
         n = x_pinned.shape[0]
         b = self._buffers(n)
-        if not hasattr(b, "x_in"):
-            b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=self.device)
         b.x_in.copy_(x_pinned, non_blocking=True)
         b.dp.copy_(dp_pinned, non_blocking=True)
-        b.h.copy_(b.x_in[:, 0])
-        b.r.copy_(b.x_in[:, 1])
         self._run(b, n)
         return float(self.loss_out.item())
 
@@ -257,8 +255,6 @@ class FusedKvsAllEngine:
         input copy and device→host loss copy; the host merely runs one step ahead of the GPU."""
         n = x_pinned.shape[0]
         b = self._buffers(n)
-        if not hasattr(b, "x_in"):
-            b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=self.device)
         if not hasattr(self, "_loss_host"):
             self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
             self._loss_event = [torch.cuda.Event(), torch.cuda.Event()]
@@ -269,8 +265,6 @@ class FusedKvsAllEngine:
             prev = float(self._loss_host[self._loss_slot][0])
         b.x_in.copy_(x_pinned, non_blocking=True)
         b.dp.copy_(dp_pinned, non_blocking=True)
-        b.h.copy_(b.x_in[:, 0])
-        b.r.copy_(b.x_in[:, 1])
         self._run(b, n)
         self._loss_slot ^= 1
         self._loss_host[self._loss_slot].copy_(self.loss_out, non_blocking=True)

@@ -210,6 +210,8 @@ class ShardedKvsAllEngine:
         self._mark("start")
         self._barrier()                                   # S0: everyone finished the previous step
         self._mark("S0")
+        self.h.copy_(self.x_in[:, 0])                     # callers only fill x_in and dp
+        self.r.copy_(self.x_in[:, 1])
         self.gR.zero_()
         self.gC.zero_()
         self.loss_acc.zero_()
@@ -277,6 +279,8 @@ class ShardedKvsAllEngine:
     def _launch_nccl(self) -> None:
         W, B, D, n, g = self.W, self.B, self.D, self.W * self.B, self.group
         scale = 1.0 / (float(n) * float(self.NE))
+        self.h.copy_(self.x_in[:, 0])
+        self.r.copy_(self.x_in[:, 1])
         # lookup: all-gather the head ids, every owner contributes its rows, reduce-scatter back
         dist.all_gather_into_tensor(self.n_h_all, self.h, group=g)
         dist.all_gather_into_tensor(self.n_dp_all, self.dp, group=g)
@@ -329,8 +333,7 @@ class ShardedKvsAllEngine:
         """``batch = (x [B, 2], data-point ids [B])`` of *this rank* on the device; returns the global mean loss."""
         x, dp = batch[0], batch[1]
         assert x.shape[0] == self.B, "the sharded step needs full batches of the configured size on every rank"
-        self.h.copy_(x[:, 0])
-        self.r.copy_(x[:, 1])
+        self.x_in.copy_(x)
         self.dp.copy_(dp)
         self._run()
         return self.loss_out[0]
@@ -338,8 +341,6 @@ class ShardedKvsAllEngine:
     def step_from_host(self, x_pinned: torch.Tensor, dp_pinned: torch.Tensor) -> float:
         self.x_in.copy_(x_pinned, non_blocking=True)
         self.dp.copy_(dp_pinned, non_blocking=True)
-        self.h.copy_(self.x_in[:, 0])
-        self.r.copy_(self.x_in[:, 1])
         self._run()
         return float(self.loss_out.item())
 
@@ -357,8 +358,6 @@ class ShardedKvsAllEngine:
             prev = float(self._loss_host[self._loss_slot][0])
         self.x_in.copy_(x_pinned, non_blocking=True)
         self.dp.copy_(dp_pinned, non_blocking=True)
-        self.h.copy_(self.x_in[:, 0])
-        self.r.copy_(self.x_in[:, 1])
         self._run()
         self._loss_slot ^= 1
         self._loss_host[self._loss_slot].copy_(self.loss_out, non_blocking=True)
