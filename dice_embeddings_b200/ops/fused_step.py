@@ -129,6 +129,7 @@ class FusedKvsAllEngine:
         self.loss_in_query_pass = False
         self._bufs = {}
         self._graphs = {}
+        self._side = torch.cuda.Stream(device=dev)
 
     # ------------------------------------------------------------------ buffers per batch size
     def _buffers(self, n: int):
@@ -153,14 +154,21 @@ class FusedKvsAllEngine:
 
     def _launch_all(self, b, n: int) -> None:
         scale = 1.0 / (float(n) * float(self.NE))
+        main = torch.cuda.current_stream(self.device)
+        if self.label_mode == "mask":
+            # the label masks depend on the data-point ids only: they are built on a side stream (a parallel branch
+            # of the captured graph) while the main stream gathers and composes the queries
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                b.mask_q.zero_()
+                b.mask_e.zero_()
+                K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e)
         b.h.copy_(b.x_in[:, 0])   # inside the captured sequence: callers only fill x_in and dp
         b.r.copy_(b.x_in[:, 1])
         K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,
                          None, n, self.D, self.status)
         if self.label_mode == "mask":
-            b.mask_q.zero_()
-            b.mask_e.zero_()
-            K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e)
+            main.wait_stream(self._side)
             lq = self.loss_in_query_pass
             K.kvsall_fused(self.E_bf16, b.Q, self.gE, None if lq else self.loss_acc, self.status, self.base, scale,
                            not lq, mask=b.mask_e, pos_delta=self.pos_weight)
