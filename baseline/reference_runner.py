@@ -32,7 +32,7 @@ class _StopBench(Exception):
 
 def reference_available():
     if not os.path.isdir(os.path.join(REF, "dicee")):
-        return False, "baseline/_ref/dicee is missing (offline pip install of /root/reference was not done on this machine)"
+        return False, "baseline/_ref/dicee is missing (the offline pip install of the reference sources was not done on this machine)"
     return True, ""
 
 

@@ -4,7 +4,9 @@ import re
 
 import pytest
 
-REF = "/root/reference/dicee"
+# the reference sources: the in-tree install used by the benchmark's reference arm, or a checkout named by DICEE_SRC
+_HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("DICEE_SRC") or os.path.join(os.path.dirname(_HERE), "baseline", "_ref", "dicee")
 
 
 def _reference_flags():
