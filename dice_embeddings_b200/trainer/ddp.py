@@ -60,6 +60,27 @@ class TorchDDPTrainer(AbstractTrainer):
                 raise
             return None
 
+    def _maybe_peer_optimizer(self, model):
+        """Replicated model on B200s: the gradient all-reduce is folded into the optimiser kernel (peer loads)."""
+        backend = getattr(self.attributes, "kernel_backend", "auto")
+        if backend == "torch" or getattr(self.attributes, "comm", "p2p") != "p2p" or self.world_size < 2 \
+                or self.device.type != "cuda" or torch.cuda.get_device_capability(self.device)[0] != 10:
+            return None
+        try:
+            from ..ops import kernels as K
+            from ..parallel.peer_allreduce_optimizer import PeerAllReduceOptimizer
+            if getattr(model, "optimizer_name", None) not in K.OPT_CODE:
+                return None
+            if any(p.dtype != torch.float32 for p in model.parameters() if p.requires_grad):
+                return None
+            return PeerAllReduceOptimizer(model, lr=self.attributes.lr,
+                                          weight_decay=getattr(self.attributes, "weight_decay", 0.0) or 0.0,
+                                          device=self.device)
+        except (ImportError, RuntimeError, OSError):
+            if backend == "cuda":
+                raise
+            return None
+
     def _allreduce_grads(self, params) -> None:
         grads = [p.grad for p in params if p.grad is not None]
         if not grads or self.world_size == 1:
@@ -84,7 +105,12 @@ class TorchDDPTrainer(AbstractTrainer):
         self.engine = self._maybe_sharded_engine(model, loader)
         if self.engine is not None:
             loader.drop_last = True
-        self.optimizer = self.engine.optimizer_view() if self.engine is not None else model.configure_optimizers()
+        self.peer_optimizer = None
+        if self.engine is not None:
+            self.optimizer = self.engine.optimizer_view()
+        else:
+            self.peer_optimizer = self._maybe_peer_optimizer(model)
+            self.optimizer = self.peer_optimizer if self.peer_optimizer is not None else model.configure_optimizers()
         params = [p for p in model.parameters() if p.requires_grad]
         use_bf16 = getattr(self.attributes, "compute_dtype", "fp32") == "bf16" and self.device.type == "cuda"
         if self.is_global_zero:
@@ -106,8 +132,9 @@ class TorchDDPTrainer(AbstractTrainer):
                     with torch.autocast("cuda", dtype=torch.bfloat16, enabled=use_bf16):
                         loss = model.training_step(batch)
                     loss.backward()
-                    self._allreduce_grads(params)
-                    self.optimizer.step()
+                    if self.peer_optimizer is None:
+                        self._allreduce_grads(params)
+                    self.optimizer.step()   # the peer optimiser sums all ranks' gradients inside its update kernel
                 total += loss.detach()
                 nb += 1
             if self.engine is None and self.world_size > 1:
@@ -115,6 +142,8 @@ class TorchDDPTrainer(AbstractTrainer):
                 total /= self.world_size
             if self.engine is not None:
                 self.engine.sync_to_model()
+            if self.peer_optimizer is not None:
+                self.peer_optimizer.check()
             epoch_loss = float(total) / max(nb, 1)
             model.loss_history.append(epoch_loss)
             if self.is_global_zero:

@@ -64,3 +64,11 @@ def test_sharded_trainer_through_the_command_line(tmp_path, st, extra):
     rep = json.load(open(out / "eval_report.json"))
     assert rep["Train"]["MRR"] > (0.3 if (st != "KvsAll" or "ConEx" in extra) else 0.5), rep
     assert os.path.isfile(out / "model.pt")
+
+
+def test_peer_allreduce_optimizer_matches_single_process_training():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29619", os.path.join(HERE, "_peer_optimizer_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0 and "PEER_OPT_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
