@@ -482,12 +482,24 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const bool aligned = ((reinterpret_cast<uintptr_t>(param) | reinterpret_cast<uintptr_t>(grad) |
                          reinterpret_cast<uintptr_t>(pm) | reinterpret_cast<uintptr_t>(pv)) & 15) == 0 &&
-                       (reinterpret_cast<uintptr_t>(shadow) & 7) == 0 && p.grad_table == nullptr;
+                       (reinterpret_cast<uintptr_t>(shadow) & 7) == 0;
+  bool table_aligned = true;  // gradient buffers of the ranks (symmetric-heap regions) are 16-byte aligned as a rule
+  if (p.grad_table != nullptr)
+    for (int k = 0; k < p.n_grad; ++k) table_aligned &= (reinterpret_cast<uintptr_t>(p.grad_table[k]) & 15) == 0;
   long long done = 0;
-  if (aligned) {
+  if (aligned && table_aligned) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
       float4 w = reinterpret_cast<float4*>(param)[i];
-      float4 g = reinterpret_cast<float4*>(grad)[i];
+      float4 g;
+      if (p.grad_table != nullptr) {  // sum of all ranks' buffers (peer loads): the all-reduce happens here
+        g = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < p.n_grad; ++k) {
+          const float4 t = reinterpret_cast<const float4*>(p.grad_table[k])[i];
+          g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        }
+      } else {
+        g = reinterpret_cast<float4*>(grad)[i];
+      }
       float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
       if (p.kind != 2) {
         m = reinterpret_cast<float4*>(pm)[i];
@@ -498,7 +510,7 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
       w.z = opt_update(p.kind, w.z, g.z, m.z, v.z, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
       w.w = opt_update(p.kind, w.w, g.w, m.w, v.w, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
       reinterpret_cast<float4*>(param)[i] = w;
-      reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.grad_table == nullptr) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (p.kind != 2) {
         reinterpret_cast<float4*>(pm)[i] = m;
         reinterpret_cast<float4*>(pv)[i] = v;
