@@ -182,15 +182,19 @@ class FusedKvsAllEngine:
                                   self.loss_acc, self.pos_weight, scale, n, self.D, 1, 0)
         K.compose_backward(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.R, self.coeff, b.dQ, b.gent_tab,
                            self.gR, self.gC if self.coeff_trainable else None, n, self.D)
-        b.dQ.zero_()
         b1, b2 = self.betas
+        # the small updates (relations, coefficient, clearing dQ) run beside the sweep over the entity table
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            b.dQ.zero_()
+            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, self.lr, b1, b2,
+                             self.eps, self.weight_decay)
+            if self.coeff_trainable:
+                K.optimizer_step(self.opt_kind, self.coeff, self.gC, self.mC, self.vC, None, self.step_count, self.lr,
+                                 b1, b2, self.eps, self.weight_decay)
         K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, self.lr, b1,
                          b2, self.eps, self.weight_decay)
-        K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, self.lr, b1, b2,
-                         self.eps, self.weight_decay)
-        if self.coeff_trainable:
-            K.optimizer_step(self.opt_kind, self.coeff, self.gC, self.mC, self.vC, None, self.step_count, self.lr, b1,
-                             b2, self.eps, self.weight_decay)
+        main.wait_stream(self._side)
         K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
 
     #: number of kernels of this library launched per step (for launch accounting)
