@@ -419,6 +419,32 @@ __global__ void build_label_masks_kernel(const long long* __restrict__ dp_idx, c
   }
 }
 
+// Same result as build_label_masks_kernel, one thread per positive label: `first` holds the prefix sums of the
+// positives per data point (positive_scan_kernel), a binary search finds the data point of a positive.  A few data
+// points of a Zipf-shaped graph have thousands of known tails; with one warp per data point those few warps set the
+// kernel's duration.
+__global__ void build_label_masks_flat_kernel(const long long* __restrict__ dp_idx,
+                                              const long long* __restrict__ offsets,
+                                              const long long* __restrict__ values, const int* __restrict__ first,
+                                              int n, int W, int rank, unsigned int* __restrict__ mask_q, int stride_q,
+                                              unsigned int* __restrict__ mask_e, int stride_e) {
+  const int total = first[n];
+  const int stride = gridDim.x * blockDim.x;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    int lo = 0, hi = n - 1;  // largest i with first[i] <= t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (first[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    const int i = lo;
+    const long long j = values[offsets[dp_idx[i]] + (t - first[i])];
+    if (j % W != rank) continue;
+    const long long jl = j / W;
+    atomicOr(mask_q + static_cast<long long>(i) * stride_q + (jl >> 5), 1u << (jl & 31));
+    atomicOr(mask_e + jl * stride_e + (i >> 5), 1u << (i & 31));
+  }
+}
+
 // ------------------------------------------------------------------------------------ optimisers
 struct OptParams {
   float* param;
@@ -661,6 +687,18 @@ extern "C" int dice_build_label_masks(const long long* dp_idx, const long long* 
   const long long blocks = (static_cast<long long>(n) * 32 + threads - 1) / threads;
   build_label_masks_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       dp_idx, offsets, values, n, W, rank, mask_q, stride_q, mask_e, stride_e);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// first: int[n + 1] scratch for the prefix sums of positives per data point.
+extern "C" int dice_build_label_masks_flat(const long long* dp_idx, const long long* offsets, const long long* values,
+                                           int* first, int n, int W, int rank, unsigned int* mask_q, int stride_q,
+                                           unsigned int* mask_e, int stride_e, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  positive_scan_kernel<<<1, 1024, 0, s>>>(dp_idx, offsets, n, first);
+  build_label_masks_flat_kernel<<<148 * 4, 256, 0, s>>>(dp_idx, offsets, values, first, n, W, rank, mask_q, stride_q,
+                                                        mask_e, stride_e);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

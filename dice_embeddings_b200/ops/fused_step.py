@@ -162,7 +162,7 @@ class FusedKvsAllEngine:
             with torch.cuda.stream(self._side):
                 b.mask_q.zero_()
                 b.mask_e.zero_()
-                K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e)
+                K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e, first=b.first)
         b.h.copy_(b.x_in[:, 0])   # inside the captured sequence: callers only fill x_in and dp
         b.r.copy_(b.x_in[:, 1])
         K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,

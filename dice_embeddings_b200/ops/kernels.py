@@ -98,10 +98,20 @@ def mask_stride(n_bits: int) -> int:
 
 
 def build_label_masks(dp_idx, offsets, values, n: int, W: int, rank: int, mask_q: torch.Tensor,
-                      mask_e: torch.Tensor) -> None:
-    """Set the positive-label bits of a batch in both mask orientations (masks must be zeroed by the caller)."""
+                      mask_e: torch.Tensor, first: Optional[torch.Tensor] = None) -> None:
+    """Set the positive-label bits of a batch in both mask orientations (masks must be zeroed by the caller).
+    With ``first`` (int32 ``[n + 1]`` scratch) the work is spread one thread per positive label instead of one warp
+    per data point, which is faster when a few data points own most of the positives."""
     _req(mask_q, torch.int32, "mask_q")
     _req(mask_e, torch.int32, "mask_e")
+    if first is not None:
+        _req(first, torch.int32, "first")
+        assert first.numel() >= n + 1
+        rc = _lib.lib().dice_build_label_masks_flat(_ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), n, W,
+                                                    rank, _ptr(mask_q), mask_q.shape[1], _ptr(mask_e),
+                                                    mask_e.shape[1], _stream())
+        _check(rc, "dice_build_label_masks_flat")
+        return
     rc = _lib.lib().dice_build_label_masks(_ptr(dp_idx), _ptr(offsets), _ptr(values), n, W, rank, _ptr(mask_q),
                                            mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], _stream())
     _check(rc, "dice_build_label_masks")

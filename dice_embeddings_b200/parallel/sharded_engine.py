@@ -155,7 +155,7 @@ class ShardedKvsAllEngine:
         else:
             assert comm == "p2p", "the sparse label path is implemented for the peer-memory flavour"
             self.mask_q = self.mask_e = None
-            self.first = torch.zeros(W * B + 1, dtype=torch.int32, device=dev)
+        self.first = torch.zeros(W * B + 1, dtype=torch.int32, device=dev)
         if comm == "nccl":
             self._init_nccl_buffers()
         self._graph = None
@@ -225,7 +225,8 @@ class ShardedKvsAllEngine:
         self._barrier()                                   # S1: all query rows have landed everywhere
         self._mark("S1")
         if masks:
-            K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e)
+            K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e,
+                                first=self.first)
             self._mark("masks")
         e_loc = self.E_bf16[: self.rows]
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,

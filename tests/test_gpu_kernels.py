@@ -183,3 +183,25 @@ def test_p2p_barrier_wait_is_bounded():
     torch.cuda.synchronize()
     K.check_status(status)
     assert (torch.ones(4, device=DEV) * 2).sum().item() == 8.0
+
+
+def test_label_mask_kernels_agree():
+    """One warp per data point and one thread per positive label build the same masks (two shards)."""
+    from dice_embeddings_b200.data.datasets import KvsAll
+    from dice_embeddings_b200.data.synthetic import zipf_kg
+    NE, NR = 900, 9
+    ds = KvsAll(zipf_kg(NE, NR, 20000, seed=4), NE, NR).to(DEV)
+    offsets, values = ds.offsets.to(DEV).contiguous(), ds.values.to(DEV).contiguous()
+    n = 700
+    dp = torch.randperm(len(ds), device=DEV)[:n].contiguous()
+    for W, rank in ((1, 0), (2, 1)):
+        rows = (NE - rank + W - 1) // W
+        masks = []
+        for flat in (False, True):
+            mq = torch.zeros(n, K.mask_stride(rows), dtype=torch.int32, device=DEV)
+            me = torch.zeros(rows, K.mask_stride(n), dtype=torch.int32, device=DEV)
+            first = torch.zeros(n + 1, dtype=torch.int32, device=DEV) if flat else None
+            K.build_label_masks(dp, offsets, values, n, W, rank, mq, me, first=first)
+            masks.append((mq, me))
+        assert torch.equal(masks[0][0], masks[1][0]) and torch.equal(masks[0][1], masks[1][1])
+        assert int(masks[0][0].ne(0).sum()) > 0
