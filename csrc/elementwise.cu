@@ -275,42 +275,40 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
 // first[i] = number of positive labels of batch items 0..i-1; first[n] = total.
 __global__ void positive_scan_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
                                      int n, int* __restrict__ first) {
+  // one block, one pass: every thread owns a run of consecutive batch items, the block scans the run totals
   __shared__ int warp_sums[32];
-  __shared__ int carry;
-  if (threadIdx.x == 0) carry = 0;
+  const int per = (n + blockDim.x - 1) / blockDim.x;
+  const int lo = min(n, static_cast<int>(threadIdx.x) * per), hi = min(n, lo + per);
+  int total = 0;
+  for (int i = lo; i < hi; ++i) {
+    const long long d = dp_idx[i];
+    total += static_cast<int>(offsets[d + 1] - offsets[d]);
+  }
+  int v = total;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) >= o) v += t;
+  }
+  if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
   __syncthreads();
-  for (int base = 0; base < n; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    int c = 0;
-    if (i < n) {
-      const long long d = dp_idx[i];
-      c = static_cast<int>(offsets[d + 1] - offsets[d]);
-    }
-    int v = c;
+  if (threadIdx.x < 32) {
+    int s2 = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, v, o);
-      if ((threadIdx.x & 31) >= o) v += t;
+      const int t = __shfl_up_sync(0xffffffffu, s2, o);
+      if (threadIdx.x >= o) s2 += t;
     }
-    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      int s = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, s, o);
-        if (threadIdx.x >= o) s += t;
-      }
-      warp_sums[threadIdx.x] = s;
-    }
-    __syncthreads();
-    const int prefix = carry + ((threadIdx.x >> 5) > 0 ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - c;
-    if (i < n) first[i] = prefix;
-    __syncthreads();
-    if (threadIdx.x == blockDim.x - 1) carry = prefix + c;
-    __syncthreads();
+    warp_sums[threadIdx.x] = s2;
   }
-  if (threadIdx.x == 0) first[n] = carry;
+  __syncthreads();
+  int run = ((threadIdx.x >> 5) > 0 ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - total;  // exclusive prefix
+  for (int i = lo; i < hi; ++i) {
+    first[i] = run;
+    const long long d = dp_idx[i];
+    run += static_cast<int>(offsets[d + 1] - offsets[d]);
+  }
+  if (threadIdx.x == blockDim.x - 1) first[n] = run;
 }
 
 struct PositiveParams {
