@@ -27,6 +27,16 @@ int dice_positive_correction_noalloc(const long long* dp_idx, const long long* o
                                      const void* q, const void* e, float* dq, float* de, double* loss, float weight,
                                      float scale, int n, int D, int W, int rank, void* stream);
 
+// Convolutional gate (3x3 convolution with one input channel, batch normalisation, ReLU) of the ConEx / ConvQ /
+// ConvO model families.  dice_conv_gate_supported returns 1 when the shape is covered.
+int dice_conv_gate_supported(int B, int H, int W, int C);
+int dice_conv_gate_forward(int B, int H, int W, int C, int training, const float* X, const float* w,
+                           const float* bias, const float* gamma, const float* beta, float* run_mean, float* run_var,
+                           float momentum, float eps, double* stats, float* fold, float* F, void* stream);
+int dice_conv_gate_backward(int B, int H, int W, int C, int training, const float* X, const float* w,
+                            const float* bias, const float* fold, const float* dF, double* bstats, float* dX,
+                            double* dwb, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,7 @@ class _ConvGate(BaseKGE):
     _bn_conv_name = "bn_conv2d"
     _norm_fc_name = "norm_fc1"
     _recreate_embeddings = False
+    fused_conv_gate = True   # on a B200: conv + batch norm + ReLU in the kernels of ops/conv_gate.py
 
     def __init__(self, args):
         super().__init__(args)
@@ -55,10 +56,18 @@ class _ConvGate(BaseKGE):
     def residual_convolution(self, C_1: Tuple[torch.Tensor, ...], C_2: Tuple[torch.Tensor, ...]):
         """Gate vectors from the blocks of head (``C_1``) and relation (``C_2``)."""
         w = self.embedding_dim // self._k
-        x = torch.cat([p.reshape(-1, 1, 1, w) for p in (*C_1, *C_2)], dim=2)
-        x = torch.relu(getattr(self, self._bn_conv_name)(self.conv2d(x)))
-        x = self.feature_map_dropout(x)
-        x = x.reshape(x.shape[0], -1)
+        bn = getattr(self, self._bn_conv_name)
+        x = None
+        if C_1[0].is_cuda and self.fused_conv_gate and not (self.training and self.feature_map_dropout_rate):
+            from ..ops import conv_gate
+            image = torch.cat((*C_1, *C_2), dim=1)   # [B, 2k * w]: row i of the image is block i
+            if conv_gate.supported(image, self.conv2d, bn, 2 * self._k, w):
+                x = conv_gate.conv_gate_features(image, self.conv2d, bn, 2 * self._k, w)
+        if x is None:
+            x = torch.cat([p.reshape(-1, 1, 1, w) for p in (*C_1, *C_2)], dim=2)
+            x = torch.relu(bn(self.conv2d(x)))
+            x = self.feature_map_dropout(x)
+            x = x.reshape(x.shape[0], -1)
         x = torch.relu(getattr(self, self._norm_fc_name)(self.fc1(x)))
         return torch.chunk(x, self._gate_chunks, dim=1)
 

@@ -107,5 +107,8 @@ class _Sigs:
     dice_sparse_rows_optimizer = [_i, _p, _p, _p, _p, _p, _p, _l, _i, _p, _f, _f, _f, _f, _f, _p]
     dice_eval_rank = [_p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _p, _p]
     dice_eval_rank_cand_cap = [_i, _i, _i, _i, _i]
+    dice_conv_gate_supported = [_i, _i, _i, _i]
+    dice_conv_gate_forward = [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _f, _f, _p, _p, _p, _p]
+    dice_conv_gate_backward = [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]
     dice_eval_sparse = [_p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p]
     dice_eval_band_exact = [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _l, _p, _p, _p]
