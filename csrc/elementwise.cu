@@ -274,16 +274,22 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
 // ------------------------------------------------------------------------------------ positives
 // first[i] = number of positive labels of batch items 0..i-1; first[n] = total.
 __global__ void positive_scan_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
-                                     int n, int* __restrict__ first) {
-  // one block, one pass: every thread owns a run of consecutive batch items, the block scans the run totals
+                                     int n, int* first) {
+  // One block.  Pass 1: the number of positives of every batch item, with strided (coalesced, independent) loads so
+  // that the two dependent reads per item overlap across items; the counts are parked in first[].  Pass 2: every
+  // thread owns a run of consecutive items, the block scans the run totals, the run is rewritten as exclusive prefixes.
   __shared__ int warp_sums[32];
+#pragma unroll 4
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const long long d = dp_idx[i];
+    first[i] = static_cast<int>(offsets[d + 1] - offsets[d]);
+  }
+  __syncthreads();
   const int per = (n + blockDim.x - 1) / blockDim.x;
   const int lo = min(n, static_cast<int>(threadIdx.x) * per), hi = min(n, lo + per);
   int total = 0;
-  for (int i = lo; i < hi; ++i) {
-    const long long d = dp_idx[i];
-    total += static_cast<int>(offsets[d + 1] - offsets[d]);
-  }
+#pragma unroll 4
+  for (int i = lo; i < hi; ++i) total += first[i];
   int v = total;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -304,9 +310,9 @@ __global__ void positive_scan_kernel(const long long* __restrict__ dp_idx, const
   __syncthreads();
   int run = ((threadIdx.x >> 5) > 0 ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - total;  // exclusive prefix
   for (int i = lo; i < hi; ++i) {
+    const int c = first[i];
     first[i] = run;
-    const long long d = dp_idx[i];
-    run += static_cast<int>(offsets[d + 1] - offsets[d]);
+    run += c;
   }
   if (threadIdx.x == blockDim.x - 1) first[n] = run;
 }
