@@ -272,19 +272,21 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
 }
 
 // ------------------------------------------------------------------------------------ positives
-// first[i] = number of positive labels of batch items 0..i-1; first[n] = total.
-__global__ void positive_scan_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
-                                     int n, int* first) {
-  // One block.  Pass 1: the number of positives of every batch item, with strided (coalesced, independent) loads so
-  // that the two dependent reads per item overlap across items; the counts are parked in first[].  Pass 2: every
-  // thread owns a run of consecutive items, the block scans the run totals, the run is rewritten as exclusive prefixes.
+// first[i] = number of positive labels of batch items 0..i-1; first[n] = total.  Two launches: the counts (two
+// dependent random reads per item; spread over many SMs because one SM sustains too few outstanding misses for a
+// large batch) and a one-block scan over the counts parked in first[].
+__global__ void positive_count_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
+                                      int n, int* __restrict__ first) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long d = dp_idx[i];
+  first[i] = static_cast<int>(offsets[d + 1] - offsets[d]);
+}
+
+__global__ void positive_scan_kernel(int n, int* first) {
+  // every thread owns a run of consecutive items, the block scans the run totals, the run is rewritten as
+  // exclusive prefixes
   __shared__ int warp_sums[32];
-#pragma unroll 4
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const long long d = dp_idx[i];
-    first[i] = static_cast<int>(offsets[d + 1] - offsets[d]);
-  }
-  __syncthreads();
   const int per = (n + blockDim.x - 1) / blockDim.x;
   const int lo = min(n, static_cast<int>(threadIdx.x) * per), hi = min(n, lo + per);
   int total = 0;
@@ -700,14 +702,16 @@ extern "C" int dice_build_label_masks_flat(const long long* dp_idx, const long l
                                            unsigned int* mask_e, int stride_e, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  positive_scan_kernel<<<1, 1024, 0, s>>>(dp_idx, offsets, n, first);
+  positive_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(dp_idx, offsets, n, first);
+  positive_scan_kernel<<<1, 1024, 0, s>>>(n, first);
   build_label_masks_flat_kernel<<<148 * 4, 256, 0, s>>>(dp_idx, offsets, values, first, n, W, rank, mask_q, stride_q,
                                                         mask_e, stride_e);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int dice_positive_scan(const long long* dp_idx, const long long* offsets, int n, int* first, void* stream) {
-  positive_scan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first);
+  positive_count_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first);
+  positive_scan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(n, first);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

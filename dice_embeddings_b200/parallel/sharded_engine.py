@@ -160,6 +160,7 @@ class ShardedKvsAllEngine:
             self._init_nccl_buffers()
         self._graph = None
         self._graph_lr = None
+        self._side = torch.cuda.Stream(device=dev)
         self._phase_events = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
         self._phase_names = []
         self._phase_slots = torch.zeros(32, dtype=torch.int64, device=dev)
@@ -216,15 +217,19 @@ class ShardedKvsAllEngine:
         self.gC.zero_()
         self.loss_acc.zero_()
         masks = self.label_mode == "mask"
-        if masks:
-            self.mask_q.zero_()
-            self.mask_e.zero_()
+        if masks:   # cleared on a parallel branch; joined before the masks are built
+            main = torch.cuda.current_stream(self.device)
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                self.mask_q.zero_()
+                self.mask_e.zero_()
         K.lookup_compose(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.NE, self.R, self.coeff,
                          self.tab.Q, W, self.rank * B, None, B, D, self.status, dp_src=self.dp, dp_dst_table=self.tab.dp)
         self._mark("zero+lookup")
         self._barrier()                                   # S1: all query rows have landed everywhere
         self._mark("S1")
         if masks:
+            main.wait_stream(self._side)
             K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e,
                                 first=self.first)
             self._mark("masks")
