@@ -284,39 +284,53 @@ __global__ void positive_count_kernel(const long long* __restrict__ dp_idx, cons
 }
 
 __global__ void positive_scan_kernel(int n, int* first) {
-  // every thread owns a run of consecutive items, the block scans the run totals, the run is rewritten as
-  // exclusive prefixes
-  __shared__ int warp_sums[32];
-  const int per = (n + blockDim.x - 1) / blockDim.x;
-  const int lo = min(n, static_cast<int>(threadIdx.x) * per), hi = min(n, lo + per);
-  int total = 0;
-#pragma unroll 4
-  for (int i = lo; i < hi; ++i) total += first[i];
-  int v = total;
+  // 32 warps; warp w owns the items [w * chunk, (w + 1) * chunk).  All reads and writes are coalesced 128-byte rows and
+  // the reads of one group of eight rows are independent, so the single block is not bound by load latency.
+  __shared__ int warp_tot[32];
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = ((n + 1023) / 1024) * 32;
+  const int lo = min(n, warp * chunk), hi = min(n, lo + chunk);
+  int tot = 0;
+#pragma unroll 8
+  for (int i = lo + lane; i < hi; i += 32) tot += first[i];
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, v, o);
-    if ((threadIdx.x & 31) >= o) v += t;
-  }
-  if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
+  for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(full, tot, o);
+  if (lane == 0) warp_tot[warp] = tot;
   __syncthreads();
-  if (threadIdx.x < 32) {
-    int s2 = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0;
+  if (warp == 0) {
+    const int own = warp_tot[lane];
+    int v = own;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, s2, o);
-      if (threadIdx.x >= o) s2 += t;
+      const int t = __shfl_up_sync(full, v, o);
+      if (lane >= o) v += t;
     }
-    warp_sums[threadIdx.x] = s2;
+    warp_tot[lane] = v - own;   // exclusive prefix of the warp totals
   }
   __syncthreads();
-  int run = ((threadIdx.x >> 5) > 0 ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - total;  // exclusive prefix
-  for (int i = lo; i < hi; ++i) {
-    const int c = first[i];
-    first[i] = run;
-    run += c;
+  int carry = warp_tot[warp];
+  for (int base = lo; base < hi; base += 256) {
+    int c[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = base + k * 32 + lane;
+      c[k] = i < hi ? first[i] : 0;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = base + k * 32 + lane;
+      int v = c[k];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(full, v, o);
+        if (lane >= o) v += t;
+      }
+      if (i < hi) first[i] = carry + v - c[k];
+      carry += __shfl_sync(full, v, 31);
+    }
   }
-  if (threadIdx.x == blockDim.x - 1) first[n] = run;
+  if (warp == 31 && lane == 0) first[n] = carry;   // warps past the end have empty ranges: their carry is the total
 }
 
 struct PositiveParams {

@@ -205,3 +205,17 @@ def test_label_mask_kernels_agree():
             masks.append((mq, me))
         assert torch.equal(masks[0][0], masks[1][0]) and torch.equal(masks[0][1], masks[1][1])
         assert int(masks[0][0].ne(0).sum()) > 0
+
+
+@pytest.mark.parametrize("n", [1, 31, 700, 4096, 5000, 32768, 65536])
+def test_positive_scan_equals_cumsum(n):
+    torch.manual_seed(n)
+    n_dp = 5000
+    counts = torch.randint(0, 9, (n_dp,), device=DEV)
+    counts[::97] = 400                                         # a few data points own many positives
+    offsets = torch.cat((torch.zeros(1, dtype=torch.int64, device=DEV), counts.cumsum(0))).contiguous()
+    dp = torch.randint(0, n_dp, (n,), device=DEV)
+    first = torch.full((n + 1,), -1, dtype=torch.int32, device=DEV)
+    K.positive_scan(dp, offsets, n, first)
+    want = torch.cat((torch.zeros(1, dtype=torch.int64, device=DEV), counts[dp].cumsum(0)))
+    assert torch.equal(first.long(), want)
