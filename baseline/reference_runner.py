@@ -83,7 +83,7 @@ def write_config_kg(config: int, path: str, seed: int = 0) -> str:
     return syn.make_fb15k237_like(path, seed)
 
 
-def run(config: int, gpus: int, steps: int, warmup: int) -> dict:
+def run(config: int, gpus: int, steps: int, warmup: int, num_core: int = 0) -> dict:
     import torch
     prepare_imports()
     import dicee  # noqa: F401  (the reference)
@@ -124,7 +124,7 @@ def run(config: int, gpus: int, steps: int, warmup: int) -> dict:
     args.label_smoothing_rate = cfg["label_smoothing_rate"]
     args.num_epochs = 10 ** 6          # the hook below ends the run after warmup + steps
     args.eval_model = "None"           # no evaluation; with this setting the reference adds no reciprocal triples
-    args.num_core = 0
+    args.num_core = int(num_core)      # the reference's own flag (DataLoader workers); 0 is its default
     args.random_seed = 0
     args.p, args.q = cfg.get("p", 0), cfg.get("q", 1)
 
@@ -183,6 +183,7 @@ def run(config: int, gpus: int, steps: int, warmup: int) -> dict:
     num_triples = int(train.shape[0])
     num_pairs = int(np.unique(train[:, 0].astype(np.int64) * (int(train[:, 1].max()) + 1) + train[:, 1]).shape[0])
     num_entities = int(max(train[:, 0].max(), train[:, 2].max())) + 1
+    num_relations = int(train[:, 1].max()) + 1
     B = cfg["batch_size"]
     triples_per_step = B * world * num_triples / num_pairs
     if torch.distributed.is_initialized():
@@ -192,5 +193,5 @@ def run(config: int, gpus: int, steps: int, warmup: int) -> dict:
             pass
     return {"ms_total": ms, "steps": steps, "warmup": warmup, "world": world, "rank": rank,
             "triples_per_step": triples_per_step, "num_pairs": num_pairs, "num_triples": num_triples,
-            "num_entities": num_entities, "batch_size": B,
+            "num_entities": num_entities, "num_relations": num_relations, "batch_size": B, "num_core": int(num_core),
             "h2d_bytes_per_step": B * 2 * 8 + B * num_entities * 4, "d2h_bytes_per_step": 4, "config": cfg}

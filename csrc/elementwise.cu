@@ -7,41 +7,10 @@
 // Entity rows are distributed cyclically: global row e lives on rank e % W at local row e / W.  All kernels take
 // arrays of per-rank base pointers, so with W == 1 they act on one table and with W > 1 they read / write peer
 // memory directly (plain ld/st/red over NVLink; no multicast loads).
+#include "algebra.cuh"
 #include "ptx_sm100.cuh"
 
 namespace dice {
-
-// ------------------------------------------------------------------------------------ algebra tables
-// q_k = sum_a SGN[k][a] * h_a * r_{IDX[k][a]}   for K blocks of width D / K (block layout).
-template <int K> struct Alg;
-template <> struct Alg<1> {
-  static __device__ __forceinline__ int idx(int k, int a) { return 0; }
-  static __device__ __forceinline__ float sgn(int k, int a) { return 1.f; }
-};
-template <> struct Alg<2> {  // complex product
-  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
-  static __device__ __forceinline__ float sgn(int k, int a) { return (k == 0 && a == 1) ? -1.f : 1.f; }
-};
-template <> struct Alg<4> {  // Hamilton product
-  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
-  static __device__ __forceinline__ float sgn(int k, int a) {
-    // rows k, columns a; entries are the sign of h_a * r_{k^a} in component k
-    constexpr int S[4][4] = {{1, -1, -1, -1}, {1, 1, 1, -1}, {1, -1, 1, 1}, {1, 1, -1, 1}};
-    return static_cast<float>(S[k][a]);
-  }
-};
-template <> struct Alg<8> {  // octonion product
-  static __device__ __forceinline__ int idx(int k, int a) { return k ^ a; }
-  static __device__ __forceinline__ float sgn(int k, int a) {
-    constexpr int S[8][8] = {{1, -1, -1, -1, -1, -1, -1, -1}, {1, 1, 1, -1, 1, -1, -1, 1},
-                             {1, -1, 1, 1, 1, 1, -1, -1},     {1, 1, -1, 1, 1, -1, 1, -1},
-                             {1, -1, -1, -1, 1, 1, 1, 1},     {1, 1, -1, 1, -1, 1, -1, 1},
-                             {1, 1, 1, -1, -1, 1, 1, -1},     {1, -1, 1, 1, -1, -1, 1, 1}};
-    return static_cast<float>(S[k][a]);
-  }
-};
-
-enum NormMode : int { NORM_NONE = 0, NORM_ACROSS_BLOCKS = 1, NORM_CONSECUTIVE4 = 2 };
 
 // Loads the K x VEC elements of row `row` that one thread owns (positions j0..j0+VEC-1 of every block).
 template <int K, int VEC>
@@ -110,7 +79,7 @@ __global__ void lookup_compose_kernel(const LookupParams p) {
   const int j0 = static_cast<int>(tid % per_row) * VEC;
   const long long h = p.idx_h[i];
   const long long r_id = p.idx_r[i];
-  if (h < 0 || h >= p.num_entities) { atomicCAS(p.status, 0, ST_BAD_INDEX); return; }
+  if (h < 0 || h >= p.num_entities || r_id < 0) { atomicCAS(p.status, 0, ST_BAD_INDEX); return; }
   const float* hrow = p.ent[h % p.W] + (h / p.W) * p.D;
   const float* rrow = p.rel + r_id * p.D;
   if (j0 == 0 && p.dp_src != nullptr) {
@@ -276,10 +245,15 @@ __global__ void compose_backward_kernel(const ComposeBwdParams p) {
 // dependent random reads per item; spread over many SMs because one SM sustains too few outstanding misses for a
 // large batch) and a one-block scan over the counts parked in first[].
 __global__ void positive_count_kernel(const long long* __restrict__ dp_idx, const long long* __restrict__ offsets,
-                                      int n, int* __restrict__ first) {
+                                      int n, int* __restrict__ first, long long num_data_points, int* status) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long d = dp_idx[i];
+  if (num_data_points > 0 && (d < 0 || d >= num_data_points)) {   // reported; the item then has no positives
+    if (status != nullptr) atomicCAS(status, 0, ST_BAD_INDEX);
+    first[i] = 0;
+    return;
+  }
   first[i] = static_cast<int>(offsets[d + 1] - offsets[d]);
 }
 
@@ -447,7 +421,8 @@ __global__ void build_label_masks_flat_kernel(const long long* __restrict__ dp_i
                                               const long long* __restrict__ offsets,
                                               const long long* __restrict__ values, const int* __restrict__ first,
                                               int n, int W, int rank, unsigned int* __restrict__ mask_q, int stride_q,
-                                              unsigned int* __restrict__ mask_e, int stride_e) {
+                                              unsigned int* __restrict__ mask_e, int stride_e,
+                                              long long num_local_rows, int* status) {
   const int total = first[n];
   const int stride = gridDim.x * blockDim.x;
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -460,6 +435,10 @@ __global__ void build_label_masks_flat_kernel(const long long* __restrict__ dp_i
     const long long j = values[offsets[dp_idx[i]] + (t - first[i])];
     if (j % W != rank) continue;
     const long long jl = j / W;
+    if (num_local_rows > 0 && (j < 0 || jl >= num_local_rows)) {   // a CSR value outside the local shard
+      if (status != nullptr) atomicCAS(status, 0, ST_BAD_INDEX);
+      continue;
+    }
     atomicOr(mask_q + static_cast<long long>(i) * stride_q + (jl >> 5), 1u << (jl & 31));
     atomicOr(mask_e + jl * stride_e + (i >> 5), 1u << (i & 31));
   }
@@ -478,7 +457,24 @@ struct OptParams {
   int kind;                  // 0 Adam, 1 AdamW, 2 SGD, 3 ADOPT
   const float* const* grad_table;  // optional: gradient = sum over n_grad buffers (one per rank, peer pointers):
   int n_grad;                      // the all-reduce of replicated parameters folded into their update
+  const float* grad_mc;            // optional: multicast address of the gradient buffer; the sum over all bound GPUs
+                                   // is then formed inside the switch by multimem.ld_reduce (replaces grad_table)
+  const int* status;               // optional: the sweep is skipped when this word already holds an error
 };
+
+__device__ __forceinline__ float4 opt_multimem_sum4(const float* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ float opt_multimem_sum1(const float* mc_addr) {
+  float r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(r) : "l"(mc_addr) : "memory");
+  return r;
+}
 
 // One parameter element: returns the updated weight; m / v are updated in place (registers).
 __device__ __forceinline__ float opt_update(int kind, float w, float g, float& m, float& v, float lr, float beta1,
@@ -511,6 +507,7 @@ __device__ __forceinline__ float opt_update(int kind, float w, float g, float& m
 }
 
 __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
+  if (p.status != nullptr && *p.status != 0) return;
   const long long t = *p.step + 1;
   float inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
   if (p.kind <= 1) {
@@ -530,14 +527,18 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
                          reinterpret_cast<uintptr_t>(pm) | reinterpret_cast<uintptr_t>(pv)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(shadow) & 7) == 0;
   bool table_aligned = true;  // gradient buffers of the ranks (symmetric-heap regions) are 16-byte aligned as a rule
-  if (p.grad_table != nullptr)
+  const bool remote = p.grad_table != nullptr || p.grad_mc != nullptr;   // gradient summed over ranks; owners clear later
+  if (p.grad_mc != nullptr) table_aligned = (reinterpret_cast<uintptr_t>(p.grad_mc) & 15) == 0;
+  else if (p.grad_table != nullptr)
     for (int k = 0; k < p.n_grad; ++k) table_aligned &= (reinterpret_cast<uintptr_t>(p.grad_table[k]) & 15) == 0;
   long long done = 0;
   if (aligned && table_aligned) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
       float4 w = reinterpret_cast<float4*>(param)[i];
       float4 g;
-      if (p.grad_table != nullptr) {  // sum of all ranks' buffers (peer loads): the all-reduce happens here
+      if (p.grad_mc != nullptr) {     // sum of all ranks' buffers formed inside the switch
+        g = opt_multimem_sum4(p.grad_mc + (i << 2));
+      } else if (p.grad_table != nullptr) {  // sum of all ranks' buffers (peer loads): the all-reduce happens here
         g = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int k = 0; k < p.n_grad; ++k) {
           const float4 t = reinterpret_cast<const float4*>(p.grad_table[k])[i];
@@ -556,7 +557,7 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
       w.z = opt_update(p.kind, w.z, g.z, m.z, v.z, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
       w.w = opt_update(p.kind, w.w, g.w, m.w, v.w, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
       reinterpret_cast<float4*>(param)[i] = w;
-      if (p.grad_table == nullptr) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!remote) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (p.kind != 2) {
         reinterpret_cast<float4*>(pm)[i] = m;
         reinterpret_cast<float4*>(pv)[i] = v;
@@ -574,7 +575,9 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
   for (long long i = done + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n; i += stride) {
     float w = param[i];
     float g;
-    if (p.grad_table != nullptr) {
+    if (p.grad_mc != nullptr) {
+      g = opt_multimem_sum1(p.grad_mc + i);
+    } else if (p.grad_table != nullptr) {
       g = 0.f;
       for (int k = 0; k < p.n_grad; ++k) g += p.grad_table[k][i];  // owners clear their buffer after the next barrier
     } else {
@@ -599,7 +602,8 @@ __global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* _
 // loss_out = acc * inv_count; acc = 0; step += 1   (one thread)
 // With acc_table the loss is the sum of every rank's accumulator (peer reads); each owner clears its own later.
 __global__ void finish_step_kernel(double* acc, float* loss_out, double inv_count, long long* step,
-                                   const double* const* acc_table, int n_acc) {
+                                   const double* const* acc_table, int n_acc, const int* status) {
+  if (status != nullptr && *status != 0) return;
   if (acc_table != nullptr) {
     double s = 0.0;
     for (int k = 0; k < n_acc; ++k) s += *acc_table[k];
@@ -614,17 +618,20 @@ __global__ void finish_step_kernel(double* acc, float* loss_out, double inv_coun
 // Barrier across W ranks (one process per GPU) on per-rank signal arrays in peer-accessible memory.
 // Rank r adds 1 to slot r of every peer's array, then waits until every slot of its own array reaches the
 // number of barriers passed so far.  The wait is bounded; on a time-out the status word is set and the kernel
-// returns, so the host sees an error instead of a hang.
+// returns, so the host sees an error instead of a hang.  Once the status word holds an error the barrier neither
+// signals nor waits, and the kernels behind it that touch peer memory return at once.
 __global__ void p2p_barrier_kernel(unsigned int* const* sig_table, int rank, int W, unsigned int* count, int* status,
                                    unsigned int spin_limit) {
   __shared__ unsigned int target;
+  __shared__ int failed;
   if (threadIdx.x == 0) {
     target = *count + 1;
     *count = target;
+    failed = *status;   // after a failure nothing is signalled any more: the peers' waits run out as well
   }
   __syncthreads();
   const int peer = threadIdx.x;
-  if (peer < W) {
+  if (peer < W && failed == 0) {
     __threadfence_system();
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(sig_table[peer] + rank) : "memory");
     const unsigned int* mine = sig_table[rank] + peer;
@@ -711,20 +718,24 @@ extern "C" int dice_build_label_masks(const long long* dp_idx, const long long* 
 }
 
 // first: int[n + 1] scratch for the prefix sums of positives per data point.
+// num_data_points / num_local_rows > 0 (with status) switch on range checks of the data-point ids and of the CSR
+// values; offending entries are reported through *status and skipped.
 extern "C" int dice_build_label_masks_flat(const long long* dp_idx, const long long* offsets, const long long* values,
                                            int* first, int n, int W, int rank, unsigned int* mask_q, int stride_q,
-                                           unsigned int* mask_e, int stride_e, void* stream) {
+                                           unsigned int* mask_e, int stride_e, long long num_data_points,
+                                           long long num_local_rows, int* status, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  positive_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(dp_idx, offsets, n, first);
+  positive_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(dp_idx, offsets, n, first, num_data_points, status);
   positive_scan_kernel<<<1, 1024, 0, s>>>(n, first);
   build_label_masks_flat_kernel<<<148 * 4, 256, 0, s>>>(dp_idx, offsets, values, first, n, W, rank, mask_q, stride_q,
-                                                        mask_e, stride_e);
+                                                        mask_e, stride_e, num_local_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int dice_positive_scan(const long long* dp_idx, const long long* offsets, int n, int* first, void* stream) {
-  positive_count_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first);
+  positive_count_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(dp_idx, offsets, n, first, 0,
+                                                                                          nullptr);
   positive_scan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(n, first);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -751,10 +762,11 @@ extern "C" int dice_positive_correction(const long long* dp_idx, const long long
 
 extern "C" int dice_optimizer_step(int kind, float* param, float* grad, float* m, float* v, void* shadow,
                                    const long long* step, long long n, float lr, float beta1, float beta2, float eps,
-                                   float weight_decay, const float* const* grad_table, int n_grad, void* stream) {
+                                   float weight_decay, const float* const* grad_table, int n_grad,
+                                   const float* grad_mc, const int* status, void* stream) {
   if (n <= 0) return 0;
   OptParams p{param, grad, m, v, static_cast<__nv_bfloat16*>(shadow), step, n, lr, beta1, beta2, eps, weight_decay, kind,
-              grad_table, n_grad};
+              grad_table, n_grad, grad_mc, status};
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -772,8 +784,9 @@ extern "C" int dice_cast_bf16(const float* src, void* dst, long long n, void* st
 }
 
 extern "C" int dice_finish_step(double* acc, float* loss_out, double inv_count, long long* step,
-                                const double* const* acc_table, int n_acc, void* stream) {
-  finish_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(acc, loss_out, inv_count, step, acc_table, n_acc);
+                                const double* const* acc_table, int n_acc, const int* status, void* stream) {
+  finish_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(acc, loss_out, inv_count, step, acc_table, n_acc,
+                                                                      status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -369,11 +369,13 @@ template <int D, int MODE>
 static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const EvalParams& p, int num_ctas,
                   cudaStream_t stream) {
   auto kern = eval_rank_kernel<D, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};   // the attribute is per device: one flag per device ordinal
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES) != cudaSuccess)
       return -3;
-    configured = true;
+    configured[dev] = true;
   }
   kern<<<num_ctas, NUM_THREADS, Cfg<D>::SMEM_BYTES, stream>>>(tx, ty, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

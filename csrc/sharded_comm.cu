@@ -1,0 +1,415 @@
+// Vectorised lookup / composition and its backward, with the collectives of the row-sharded step issued from inside
+// the kernels:
+//
+//   lookup_compose_vec     each thread owns 8 consecutive columns of every algebra block of one query: it pulls the
+//                          head row from its owner (peer loads over NVLink), composes the query and publishes the
+//                          bf16 result with ONE 16-byte `multimem.st` through the NVSwitch multicast mapping of the
+//                          query buffer (the all-gather of Q), or with one 16-byte store per destination rank when
+//                          no multicast mapping exists.  The (h, r, data point) indices travel with the row.
+//   compose_backward_owner the rank that owns a head row handles that query's backward: the query gradient is the
+//                          sum of every rank's partial, fetched with `multimem.ld_reduce.add` (reduced inside the
+//                          switch: the reduce-scatter of dQ) or by summing peer loads; chain rule; the row gradient
+//                          is added to the local gradient shard, so no row gradient crosses the fabric.
+//
+// Entity row e lives on rank e % W at local row e / W.  Both kernels leave at once when the status word already
+// holds an error (a timed-out barrier, a bad index), so that a rank whose peers are gone stops touching their memory.
+// The reference has no counterpart: its lookups are `nn.Embedding` gathers on one device and its only collective is
+// DDP's gradient all-reduce (dicee/models/base_model.py:371-383, dicee/trainer/torch_trainer_ddp.py:88).
+#include "algebra.cuh"
+#include "ptx_sm100.cuh"
+
+namespace dice {
+
+// One 16-byte store to every GPU bound to the multicast object.
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+// Sum over all GPUs bound to the multicast object of four consecutive floats (added inside the switch).
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+
+template <int K>
+__device__ __forceinline__ void load_blocks8(const float* row, int w, int j0, float (&v)[K][8]) {
+#pragma unroll
+  for (int a = 0; a < K; ++a) {
+    const float4 lo = *reinterpret_cast<const float4*>(row + a * w + j0);
+    const float4 hi = *reinterpret_cast<const float4*>(row + a * w + j0 + 4);
+    v[a][0] = lo.x; v[a][1] = lo.y; v[a][2] = lo.z; v[a][3] = lo.w;
+    v[a][4] = hi.x; v[a][5] = hi.y; v[a][6] = hi.z; v[a][7] = hi.w;
+  }
+}
+
+// rh = normalised relation, nrm = the norm every element was divided by.
+template <int K>
+__device__ __forceinline__ void normalize_rel8(int mode, const float (&r)[K][8], float (&rh)[K][8],
+                                               float (&nrm)[K][8]) {
+#pragma unroll
+  for (int a = 0; a < K; ++a)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { rh[a][u] = r[a][u]; nrm[a][u] = 1.f; }
+  if (mode == NORM_ACROSS_BLOCKS) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float s = 0.f;
+#pragma unroll
+      for (int a = 0; a < K; ++a) s += r[a][u] * r[a][u];
+      const float n = sqrtf(s);
+#pragma unroll
+      for (int a = 0; a < K; ++a) { rh[a][u] = r[a][u] / n; nrm[a][u] = n; }
+    }
+  } else if (mode == NORM_CONSECUTIVE4) {   // groups of four consecutive columns of the row
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int g = 0; g < 8; g += 4) {
+        float s = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s += r[a][g + u] * r[a][g + u];
+        const float n = fmaxf(sqrtf(s), 1e-12f);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { rh[a][g + u] = r[a][g + u] / n; nrm[a][g + u] = n; }
+      }
+  }
+}
+
+struct LookupVecParams {
+  const long long* idx_h;        // [B] global entity ids of this rank's queries
+  const long long* idx_r;        // [B]
+  const long long* dp_src;       // [B] data-point ids (optional)
+  const float* const* ent;       // [W] fp32 shard bases (peer pointers allowed)
+  const float* rel;              // [R, D] replicated
+  const float* coeff;            // Keci coefficient or null
+  __nv_bfloat16* const* q_dst;   // [n_dst] unicast destinations of the bf16 query rows
+  __nv_bfloat16* q_mc;           // multicast address of the query buffer, or null
+  float* q_f32;                  // optional local fp32 copy [B, D]
+  long long* const* ids_dst;     // [n_dst] index buffers laid out as h[ids_stride] | r[ids_stride] | dp[ids_stride]
+  long long ids_stride;
+  long long q_row_offset;        // first destination row of this rank's batch
+  long long num_entities;
+  int num_relations;
+  int n_dst, B, D, W, norm_mode, additive;
+  int* status;
+};
+
+template <int K>
+__global__ void __launch_bounds__(256) lookup_compose_vec_kernel(const LookupVecParams p) {
+  if (*p.status != 0) return;
+  const int w = p.D / K;
+  const int per_row = w >> 3;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (tid >= static_cast<long long>(p.B) * per_row) return;
+  const int i = static_cast<int>(tid / per_row);
+  const int j0 = static_cast<int>(tid % per_row) << 3;
+  const long long h = p.idx_h[i];
+  const long long r_id = p.idx_r[i];
+  if (h < 0 || h >= p.num_entities || r_id < 0 || r_id >= p.num_relations) {
+    atomicCAS(p.status, 0, ST_BAD_INDEX);
+    return;
+  }
+  const long long row = p.q_row_offset + i;
+  if (j0 == 0 && p.ids_dst != nullptr) {
+    const long long d = p.dp_src != nullptr ? p.dp_src[i] : 0;
+    for (int k = 0; k < p.n_dst; ++k) {
+      long long* dst = p.ids_dst[k];
+      dst[row] = h;
+      dst[p.ids_stride + row] = r_id;
+      dst[2 * p.ids_stride + row] = d;
+    }
+  }
+  const float* hrow = p.ent[h % p.W] + (h / p.W) * p.D;
+  const float* rrow = p.rel + r_id * p.D;
+  float hv[K][8], rv[K][8], rh[K][8], nrm[K][8];
+  load_blocks8<K>(hrow, w, j0, hv);
+  load_blocks8<K>(rrow, w, j0, rv);
+  normalize_rel8<K>(p.norm_mode, rv, rh, nrm);
+  if (p.coeff != nullptr) {  // Keci Cl(0,1): the vector part of head and relation is scaled by the coefficient
+    const float c = *p.coeff;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { hv[K - 1][u] *= c; rh[K - 1][u] *= c; }
+  }
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    float q[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float acc = 0.f;
+#pragma unroll
+      for (int a = 0; a < K; ++a) acc = fmaf(Alg<K>::sgn(k, a) * hv[a][u], rh[Alg<K>::idx(k, a)][u], acc);
+      q[u] = p.additive ? hv[k][u] + rh[k][u] : acc;
+    }
+    uint4 pk;
+    __nv_bfloat162 b0 = __floats2bfloat162_rn(q[0], q[1]), b1 = __floats2bfloat162_rn(q[2], q[3]);
+    __nv_bfloat162 b2 = __floats2bfloat162_rn(q[4], q[5]), b3 = __floats2bfloat162_rn(q[6], q[7]);
+    pk.x = *reinterpret_cast<uint32_t*>(&b0);
+    pk.y = *reinterpret_cast<uint32_t*>(&b1);
+    pk.z = *reinterpret_cast<uint32_t*>(&b2);
+    pk.w = *reinterpret_cast<uint32_t*>(&b3);
+    const long long off = row * p.D + k * w + j0;
+    if (p.q_mc != nullptr) {
+      multimem_st_16(p.q_mc + off, pk);
+    } else {
+      for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint4*>(p.q_dst[d] + off) = pk;
+    }
+    if (p.q_f32 != nullptr) {
+      float* qf = p.q_f32 + static_cast<long long>(i) * p.D + k * w + j0;
+      *reinterpret_cast<float4*>(qf) = make_float4(q[0], q[1], q[2], q[3]);
+      *reinterpret_cast<float4*>(qf + 4) = make_float4(q[4], q[5], q[6], q[7]);
+    }
+  }
+}
+
+struct BwdOwnerParams {
+  const long long* idx_h;        // [n] global entity ids of the whole (global) batch
+  const long long* idx_r;        // [n]
+  const float* ent_local;        // this rank's fp32 shard
+  const float* rel;
+  const float* coeff;
+  const float* dq;               // [n, D] when the gradient is already complete locally (one rank)
+  const float* const* dq_table;  // [n_dq] every rank's partial query gradients (peer pointers), or null
+  const float* dq_mc;            // multicast address of the partial-gradient buffer, or null
+  float* g_ent_local;            // [rows_local, D] gradient shard of this rank
+  float* g_rel;                  // [R, D] this rank's partial relation gradient
+  float* g_coeff;                // single float or null
+  long long num_entities;
+  int num_relations;
+  int n, n_dq, D, W, rank, norm_mode, additive;
+  int* status;
+};
+
+template <int K>
+__global__ void __launch_bounds__(256) compose_backward_owner_kernel(const BwdOwnerParams p) {
+  if (*p.status != 0) return;
+  const int w = p.D / K;
+  const int per_row = w >> 3;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  float dc = 0.f;
+  bool active = tid < static_cast<long long>(p.n) * per_row;
+  int i = 0, j0 = 0;
+  long long h = 0, r_id = 0;
+  if (active) {
+    i = static_cast<int>(tid / per_row);
+    j0 = static_cast<int>(tid % per_row) << 3;
+    h = p.idx_h[i];
+    r_id = p.idx_r[i];
+    if (h < 0 || h >= p.num_entities || r_id < 0 || r_id >= p.num_relations) {
+      atomicCAS(p.status, 0, ST_BAD_INDEX);
+      active = false;
+    } else if (h % p.W != p.rank) {
+      active = false;   // another rank owns this head row
+    }
+  }
+  if (active) {
+    const float* hrow = p.ent_local + (h / p.W) * p.D;
+    const float* rrow = p.rel + r_id * p.D;
+    float hv[K][8], rv[K][8], rh[K][8], nrm[K][8], dq[K][8], dh[K][8], drh[K][8];
+    load_blocks8<K>(hrow, w, j0, hv);
+    load_blocks8<K>(rrow, w, j0, rv);
+    const long long qoff = static_cast<long long>(i) * p.D;
+    if (p.dq_mc != nullptr) {          // reduce-scatter inside the switch
+#pragma unroll
+      for (int a = 0; a < K; ++a) {
+        const float4 lo = multimem_ld_reduce_f32x4(p.dq_mc + qoff + a * w + j0);
+        const float4 hi = multimem_ld_reduce_f32x4(p.dq_mc + qoff + a * w + j0 + 4);
+        dq[a][0] = lo.x; dq[a][1] = lo.y; dq[a][2] = lo.z; dq[a][3] = lo.w;
+        dq[a][4] = hi.x; dq[a][5] = hi.y; dq[a][6] = hi.z; dq[a][7] = hi.w;
+      }
+    } else if (p.dq_table != nullptr) {  // sum of the ranks' partial rows by peer loads
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dq[a][u] = 0.f;
+      for (int k = 0; k < p.n_dq; ++k) {
+        float part[K][8];
+        load_blocks8<K>(p.dq_table[k] + qoff, w, j0, part);
+#pragma unroll
+        for (int a = 0; a < K; ++a)
+#pragma unroll
+          for (int u = 0; u < 8; ++u) dq[a][u] += part[a][u];
+      }
+    } else {
+      load_blocks8<K>(p.dq + qoff, w, j0, dq);
+    }
+    normalize_rel8<K>(p.norm_mode, rv, rh, nrm);
+    float c = 1.f;
+    if (p.coeff != nullptr) {
+      c = *p.coeff;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { hv[K - 1][u] *= c; rh[K - 1][u] *= c; }
+    }
+#pragma unroll
+    for (int a = 0; a < K; ++a)
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { dh[a][u] = 0.f; drh[a][u] = 0.f; }
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float g = Alg<K>::sgn(k, a) * dq[k][u];
+          dh[a][u] = fmaf(g, rh[Alg<K>::idx(k, a)][u], dh[a][u]);
+          drh[Alg<K>::idx(k, a)][u] = fmaf(g, hv[a][u], drh[Alg<K>::idx(k, a)][u]);
+        }
+    if (p.additive) {
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { dh[a][u] = dq[a][u]; drh[a][u] = dq[a][u]; }
+    }
+    if (p.coeff != nullptr) {
+      // hv[K-1] = c * h_raw, rh[K-1] = c * r_raw  =>  d/dc collects both, the raw gradients pick up a factor c
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float h_raw = (c != 0.f) ? hv[K - 1][u] / c : hrow[(K - 1) * w + j0 + u];
+        const float r_raw = (c != 0.f) ? rh[K - 1][u] / c : rrow[(K - 1) * w + j0 + u];
+        dc += dh[K - 1][u] * h_raw + drh[K - 1][u] * r_raw;
+        dh[K - 1][u] *= c;
+        drh[K - 1][u] *= c;
+      }
+    }
+    // back through the relation normalisation: dr = (drh - rh * <drh, rh>_group) / norm
+    if (p.norm_mode == NORM_ACROSS_BLOCKS) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float dot = 0.f;
+#pragma unroll
+        for (int a = 0; a < K; ++a) dot += drh[a][u] * rh[a][u];
+#pragma unroll
+        for (int a = 0; a < K; ++a) drh[a][u] = (drh[a][u] - rh[a][u] * dot) / nrm[a][u];
+      }
+    } else if (p.norm_mode == NORM_CONSECUTIVE4) {
+#pragma unroll
+      for (int a = 0; a < K; ++a)
+#pragma unroll
+        for (int g = 0; g < 8; g += 4) {
+          float dot = 0.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) dot += drh[a][g + u] * rh[a][g + u];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) drh[a][g + u] = (drh[a][g + u] - rh[a][g + u] * dot) / nrm[a][g + u];
+        }
+    }
+    float* ge = p.g_ent_local + (h / p.W) * p.D;
+    float* gr = p.g_rel + r_id * p.D;
+#pragma unroll
+    for (int a = 0; a < K; ++a) {
+      red_add_v4(ge + a * w + j0, dh[a][0], dh[a][1], dh[a][2], dh[a][3]);
+      red_add_v4(ge + a * w + j0 + 4, dh[a][4], dh[a][5], dh[a][6], dh[a][7]);
+      red_add_v4(gr + a * w + j0, drh[a][0], drh[a][1], drh[a][2], drh[a][3]);
+      red_add_v4(gr + a * w + j0 + 4, drh[a][4], drh[a][5], drh[a][6], drh[a][7]);
+    }
+  }
+  if (p.g_coeff != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dc += __shfl_xor_sync(0xffffffffu, dc, o);
+    if ((threadIdx.x & 31) == 0 && dc != 0.f) atomicAdd(p.g_coeff, dc);
+  }
+}
+
+template <int K>
+static int launch_lookup_vec(const LookupVecParams& p, cudaStream_t s) {
+  const long long n = static_cast<long long>(p.B) * (p.D / K / 8);
+  lookup_compose_vec_kernel<K><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+template <int K>
+static int launch_bwd_owner(const BwdOwnerParams& p, cudaStream_t s) {
+  const long long n = static_cast<long long>(p.n) * (p.D / K / 8);
+  compose_backward_owner_kernel<K><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static int algebra_blocks(int model) {
+  switch (model) {
+    case 0: case 5: return 1;
+    case 1: case 4: return 2;
+    case 2: return 4;
+    case 3: return 8;
+    default: return 0;
+  }
+}
+
+}  // namespace dice
+
+using namespace dice;
+
+// Returns 1 when the vectorised kernels cover (model, D): every algebra block must hold a multiple of 8 columns.
+extern "C" int dice_lookup_vec_supported(int model, int D) {
+  const int K = algebra_blocks(model);
+  return (K > 0 && D % (8 * K) == 0) ? 1 : 0;
+}
+
+// model codes as in dice_lookup_compose.  q_mc != null publishes the bf16 rows through the multicast mapping (all
+// bound GPUs receive them at the same offset); otherwise they are stored to each of the n_dst buffers of q_dst.
+// ids_dst (optional): n_dst index buffers receiving h, r and the data-point id of every row (three arrays, each
+// ids_stride long).  ent / q_dst / ids_dst are device arrays of base pointers.
+extern "C" int dice_lookup_compose_vec(int model, int normalize, const long long* idx_h, const long long* idx_r,
+                                       const long long* dp_src, const float* const* ent, int W,
+                                       long long num_entities, int num_relations, const float* rel,
+                                       const float* coeff, __nv_bfloat16* const* q_dst, int n_dst, void* q_mc,
+                                       long long q_row_offset, float* q_f32, long long* const* ids_dst,
+                                       long long ids_stride, int B, int D, int* status, void* stream) {
+  if (B <= 0) return 0;
+  if (!dice_lookup_vec_supported(model, D) || status == nullptr) return -6;
+  if ((reinterpret_cast<uintptr_t>(rel) & 15) || (reinterpret_cast<uintptr_t>(q_mc) & 15) ||
+      (reinterpret_cast<uintptr_t>(q_f32) & 15))
+    return -5;
+  LookupVecParams p{};
+  p.idx_h = idx_h; p.idx_r = idx_r; p.dp_src = dp_src; p.ent = ent; p.rel = rel; p.coeff = nullptr;
+  p.q_dst = q_dst; p.q_mc = static_cast<__nv_bfloat16*>(q_mc); p.q_f32 = q_f32; p.ids_dst = ids_dst;
+  p.ids_stride = ids_stride; p.q_row_offset = q_row_offset; p.num_entities = num_entities;
+  p.num_relations = num_relations; p.n_dst = n_dst; p.B = B; p.D = D; p.W = W; p.norm_mode = NORM_NONE;
+  p.additive = 0; p.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (model) {
+    case 0: return launch_lookup_vec<1>(p, s);
+    case 1: return launch_lookup_vec<2>(p, s);
+    case 2: p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_lookup_vec<4>(p, s);
+    case 3: p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_lookup_vec<8>(p, s);
+    case 4: p.coeff = coeff; return launch_lookup_vec<2>(p, s);
+    case 5: p.additive = 1; return launch_lookup_vec<1>(p, s);
+    default: return -6;
+  }
+}
+
+// Backward of the composition for the queries whose head row this rank owns (h % W == rank); with W == 1 that is
+// every query.  The query gradient comes from dq_mc (multimem.ld_reduce over all bound GPUs), else from the sum of
+// the n_dq buffers of dq_table, else from dq.  Row gradients are added to g_ent_local (this rank's shard), relation
+// gradients to g_rel (this rank's partial sum).
+extern "C" int dice_compose_backward_owner(int model, int normalize, const long long* idx_h, const long long* idx_r,
+                                           const float* ent_local, int W, int rank, long long num_entities,
+                                           int num_relations, const float* rel, const float* coeff, const float* dq,
+                                           const float* const* dq_table, int n_dq, const void* dq_mc,
+                                           float* g_ent_local, float* g_rel, float* g_coeff, int n, int D,
+                                           int* status, void* stream) {
+  if (n <= 0) return 0;
+  if (!dice_lookup_vec_supported(model, D) || status == nullptr) return -6;
+  if ((reinterpret_cast<uintptr_t>(rel) & 15) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
+      (reinterpret_cast<uintptr_t>(dq_mc) & 15) || (reinterpret_cast<uintptr_t>(ent_local) & 15) ||
+      (reinterpret_cast<uintptr_t>(g_ent_local) & 15) || (reinterpret_cast<uintptr_t>(g_rel) & 15))
+    return -5;
+  BwdOwnerParams p{};
+  p.idx_h = idx_h; p.idx_r = idx_r; p.ent_local = ent_local; p.rel = rel; p.coeff = nullptr; p.dq = dq;
+  p.dq_table = dq_table; p.dq_mc = static_cast<const float*>(dq_mc); p.g_ent_local = g_ent_local; p.g_rel = g_rel;
+  p.g_coeff = nullptr; p.num_entities = num_entities; p.num_relations = num_relations; p.n = n; p.n_dq = n_dq;
+  p.D = D; p.W = W; p.rank = rank; p.norm_mode = NORM_NONE; p.additive = 0; p.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (model) {
+    case 0: return launch_bwd_owner<1>(p, s);
+    case 1: return launch_bwd_owner<2>(p, s);
+    case 2: p.norm_mode = normalize ? NORM_CONSECUTIVE4 : NORM_NONE; return launch_bwd_owner<4>(p, s);
+    case 3: p.norm_mode = normalize ? NORM_ACROSS_BLOCKS : NORM_NONE; return launch_bwd_owner<8>(p, s);
+    case 4: p.coeff = coeff; p.g_coeff = g_coeff; return launch_bwd_owner<2>(p, s);
+    case 5: p.additive = 1; return launch_bwd_owner<1>(p, s);
+    default: return -6;
+  }
+}

@@ -114,6 +114,8 @@ struct CandParams {
   float margin;               // distance kind: score = margin - ||q + eps - t||
   float eps;
   int N, D, W, kind;          // kind 0: dot product, 1: negative Euclidean distance
+  long long num_entities;     // > 0 (with status): candidate ids outside [0, num_entities) are reported and replaced
+  int* status;                // by entity 0, whose contribution is then dropped
 };
 
 // One warp per query: the query stays in registers while its candidates stream through, CH candidate rows in flight
@@ -140,10 +142,15 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
       for (int j = 0; j < CH; ++j) {
         const int c = c0 + j < p.C ? c0 + j : c0;   // the tail of the list repeats a valid candidate; results are dropped
         ent_id[j] = p.cand[n * p.cand_stride + c * p.cand_step];
+        if (p.num_entities > 0 && (ent_id[j] < 0 || ent_id[j] >= p.num_entities)) {
+          if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, dice::ST_BAD_INDEX);
+          ent_id[j] = -1;
+        }
       }
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
-        const float* trow = p.ent[ent_id[j] % p.W] + static_cast<size_t>(ent_id[j] / p.W) * p.D;
+        const long long e_safe = ent_id[j] < 0 ? 0 : ent_id[j];
+        const float* trow = p.ent[e_safe % p.W] + static_cast<size_t>(e_safe / p.W) * p.D;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
           const int d = (v * 32 + lane) * 4;
@@ -177,7 +184,7 @@ __global__ void __launch_bounds__(256) candidate_bce_kernel(const CandParams p) 
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int c = c0 + j;
-        if (c >= p.C) continue;
+        if (c >= p.C || ent_id[j] < 0) continue;
         float dist = 0.f;
         float s = acc[j];
         if (p.kind == 1) {
@@ -389,13 +396,14 @@ extern "C" int dice_neg_sample(const long long* pos, int B, int k, long long num
 extern "C" int dice_candidate_bce(const float* q, const long long* cand, long long cand_stride, long long cand_step,
                                   int C, const float* labels, const float* const* ent, float* const* g_ent, float* dq,
                                   float* scores, double* loss, float scale, int kind, float margin, float eps, int N,
-                                  int D, int W, unsigned char* const* touched, void* stream) {
+                                  int D, int W, unsigned char* const* touched, long long num_entities, int* status,
+                                  void* stream) {
   using namespace dice::triple;
   if (N <= 0 || C <= 0) return 0;
   if (D % 4 || D > 512 || W <= 0) return -6;
   if ((dq == nullptr) != (g_ent == nullptr)) return -6;
   CandParams p{q, cand, cand_stride, cand_step, C, labels, ent, g_ent, touched, dq, scores, loss, scale, margin, eps,
-               N, D, W, kind};
+               N, D, W, kind, num_entities, status};
   const int threads = 256;
   long long blocks = (static_cast<long long>(N) * 32 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;

@@ -90,20 +90,24 @@ _d = ctypes.c_double
 class _Sigs:
     dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _p, _i, _f, _p]
     dice_build_label_masks = [_p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
-    dice_build_label_masks_flat = [_p, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
+    dice_build_label_masks_flat = [_p, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _l, _l, _p, _p]
+    dice_lookup_vec_supported = [_i, _i]
+    dice_lookup_compose_vec = [_i, _i, _p, _p, _p, _p, _i, _l, _i, _p, _p, _p, _i, _p, _l, _p, _p, _l, _i, _i, _p, _p]
+    dice_compose_backward_owner = [_i, _i, _p, _p, _p, _i, _i, _l, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p, _p]
+    dice_positive_correction_noalloc = [_p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p]
     dice_lookup_compose = [_i, _i, _p, _p, _p, _i, _l, _p, _p, _p, _i, _l, _p, _i, _i, _p, _p, _p, _p]
     dice_compose_backward = [_i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _i, _l, _p]
     dice_positive_scan = [_p, _p, _i, _p, _p]
     dice_positive_correction = [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p, _i, _p]
-    dice_optimizer_step = [_i, _p, _p, _p, _p, _p, _p, _l, _f, _f, _f, _f, _f, _p, _i, _p]
+    dice_optimizer_step = [_i, _p, _p, _p, _p, _p, _p, _l, _f, _f, _f, _f, _f, _p, _i, _p, _p, _p]
     dice_cast_bf16 = [_p, _p, _l, _p]
-    dice_finish_step = [_p, _p, _d, _p, _p, _i, _p]
+    dice_finish_step = [_p, _p, _d, _p, _p, _i, _p, _p]
     dice_p2p_barrier = [_p, _i, _i, _p, _p, ctypes.c_uint, _p]
     dice_kvsall_set_trace = [_p]
     dice_timestamp = [_p, _p]
     dice_uniform_int = [_p, _l, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _l, _l, _p]
     dice_neg_sample = [_p, _i, _i, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _i, _f, _f, _p, _p, _p, _p, _p, _p]
-    dice_candidate_bce = [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p, _f, _i, _f, _f, _i, _i, _i, _p, _p]
+    dice_candidate_bce = [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p, _f, _i, _f, _f, _i, _i, _i, _p, _l, _p, _p]
     dice_sparse_rows_optimizer = [_i, _p, _p, _p, _p, _p, _p, _l, _i, _p, _f, _f, _f, _f, _f, _p]
     dice_eval_rank = [_p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _p, _p]
     dice_eval_rank_cand_cap = [_i, _i, _i, _i, _i]

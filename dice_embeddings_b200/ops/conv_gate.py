@@ -50,11 +50,9 @@ class _ConvGateFunction(torch.autograd.Function):
         stats = torch.empty(2 * C, dtype=torch.float64, device=dev)
         fold = torch.empty(4 * C, dtype=torch.float32, device=dev)
         out = torch.empty(B, C * H * W, dtype=torch.float32, device=dev)
-        rc = _lib.lib().dice_conv_gate_forward(B, H, W, C, int(training), x.data_ptr(), w.data_ptr(), b.data_ptr(),
-                                               K._ptr(gamma), K._ptr(beta), K._ptr(run_mean), K._ptr(run_var),
-                                               float(momentum), float(eps), stats.data_ptr(), fold.data_ptr(),
-                                               out.data_ptr(), K._stream())
-        K._check(rc, "dice_conv_gate_forward")
+        K._call("dice_conv_gate_forward", x, B, H, W, C, int(training), x.data_ptr(), w.data_ptr(), b.data_ptr(),
+                K._ptr(gamma), K._ptr(beta), K._ptr(run_mean), K._ptr(run_var), float(momentum), float(eps),
+                stats.data_ptr(), fold.data_ptr(), out.data_ptr(), others=(w, b, gamma, beta, run_mean, run_var))
         ctx.save_for_backward(x, w, b, fold)
         ctx.shape = (B, H, W, C, bool(training))
         ctx.has_affine = gamma is not None
@@ -69,10 +67,8 @@ class _ConvGateFunction(torch.autograd.Function):
         bstats = torch.empty(2 * C, dtype=torch.float64, device=dev)
         dwb = torch.empty(10 * C, dtype=torch.float64, device=dev)
         dx = torch.empty_like(x)
-        rc = _lib.lib().dice_conv_gate_backward(B, H, W, C, int(training), x.data_ptr(), w.data_ptr(), b.data_ptr(),
-                                                fold.data_ptr(), g.data_ptr(), bstats.data_ptr(), dx.data_ptr(),
-                                                dwb.data_ptr(), K._stream())
-        K._check(rc, "dice_conv_gate_backward")
+        K._call("dice_conv_gate_backward", x, B, H, W, C, int(training), x.data_ptr(), w.data_ptr(), b.data_ptr(),
+                fold.data_ptr(), g.data_ptr(), bstats.data_ptr(), dx.data_ptr(), dwb.data_ptr(), others=(w, b, fold, g))
         dweight = dwb[: 9 * C].to(torch.float32).reshape(C, 1, 3, 3)
         dbias = dwb[9 * C:].to(torch.float32)
         dgamma = bstats[:C].to(torch.float32) if ctx.has_affine else None

@@ -2,13 +2,13 @@
 
 One step is a short fixed sequence of kernel launches replayed from a CUDA graph:
 
-1. ``lookup_compose``      gather ``E[h]``, ``R[r]`` (fp32 masters), compose the query, write it as bf16
+1. ``lookup_compose_vec``  gather ``E[h]``, ``R[r]`` (fp32 masters), compose the query, write it as bf16
 2. ``kvsall_fused`` (E)    X = bf16 entity table, Y = queries  →  dense part of ``dE`` and of the loss
 3. ``kvsall_fused`` (Q)    X = queries, Y = entity table        →  dense part of ``dQ``
 4. labels: either ``build_label_masks`` before 2–3 (bit masks of the batch's known tails in both orientations,
    read by the scoring epilogue) or, for tables too large for masks, ``positive_scan`` + ``positive_correction``
    after them (sparse label term from the CSR)
-5. ``compose_backward``    chain rule of the composition, row gradients scattered into ``dE`` / ``dR``
+5. ``compose_backward_owner``  chain rule of the composition, row gradients added into ``dE`` / ``dR``
 6. ``optimizer_step`` ×k   Adam / AdamW / SGD / ADOPT over E (refreshing the bf16 shadow), R and the coefficient
 7. ``finish_step``         loss = accumulator / (B·|E|), accumulator = 0, step += 1
 
@@ -165,8 +165,8 @@ class FusedKvsAllEngine:
                 K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e, first=b.first)
         b.h.copy_(b.x_in[:, 0])   # inside the captured sequence: callers only fill x_in and dp
         b.r.copy_(b.x_in[:, 1])
-        K.lookup_compose(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.NE, self.R, self.coeff, b.q_tab, 1, 0,
-                         None, n, self.D, self.status)
+        K.lookup_compose_vec(self.code, self.normalize, b.h, b.r, None, b.ent_tab, 1, self.NE, self.NR, self.R,
+                             self.coeff, b.q_tab, 1, 0, 0, None, None, 0, n, self.D, self.status)
         if self.label_mode == "mask":
             main.wait_stream(self._side)
             lq = self.loss_in_query_pass
@@ -180,8 +180,9 @@ class FusedKvsAllEngine:
             K.positive_scan(b.dp, self.offsets, n, b.first)
             K.positive_correction(b.dp, self.offsets, self.values, b.first, b.Q, self.E_bf16, b.dQ, self.gE,
                                   self.loss_acc, self.pos_weight, scale, n, self.D, 1, 0)
-        K.compose_backward(self.code, self.normalize, b.h, b.r, b.ent_tab, 1, self.R, self.coeff, b.dQ, b.gent_tab,
-                           self.gR, self.gC if self.coeff_trainable else None, n, self.D)
+        K.compose_backward_owner(self.code, self.normalize, b.h, b.r, self.E, 1, 0, self.NE, self.NR, self.R,
+                                 self.coeff, b.dQ, None, 0, 0, self.gE, self.gR,
+                                 self.gC if self.coeff_trainable else None, n, self.D, self.status)
         b1, b2 = self.betas
         # the small updates (relations, coefficient, clearing dQ) run beside the sweep over the entity table
         self._side.wait_stream(main)

@@ -1,8 +1,10 @@
 """Typed Python wrappers over the ``extern "C"`` kernel entry points.
 
-Every wrapper takes CUDA tensors, checks dtype / contiguity / device, passes raw pointers plus the current stream
-and raises on a non-zero return code.  There is no silent fallback: if the library is missing or the launch is
-rejected the call fails.
+Every wrapper takes CUDA tensors, checks dtype / contiguity / device, passes raw pointers plus a stream and raises on
+a non-zero return code.  The launch happens on the device that holds the operands, not on whatever device happens to
+be current: the wrapper makes that device current for the call and uses *its* current stream, and it refuses operands
+that live on different devices.  There is no silent fallback: if the library is missing or the launch is rejected
+the call fails.
 """
 from __future__ import annotations
 
@@ -27,8 +29,19 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
+def _call(name: str, anchor: torch.Tensor, *args, others: Sequence[Optional[torch.Tensor]] = ()) -> None:
+    """Launch entry point ``name`` on the device of ``anchor`` (made current for the call) and on that device's
+    current stream, which is appended as the last argument.  ``others`` are further tensor operands that must live
+    on the same device."""
+    dev = anchor.device
+    if dev.type != "cuda":
+        raise KernelError(f"{name}: operands must be CUDA tensors, got {dev}")
+    for t in others:
+        if t is not None and t.device != dev:
+            raise KernelError(f"{name}: operands on different devices ({dev} and {t.device})")
+    with torch.cuda.device(dev):
+        rc = getattr(_lib.lib(), name)(*args, torch.cuda.current_stream(dev).cuda_stream)
+    _check(rc, name)
 
 
 def _check(rc: int, what: str):
@@ -61,22 +74,39 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     assert y.shape[1] == D
     if with_loss:
         _req(loss_acc, torch.float64, "loss_acc")
-    rc = _lib.lib().dice_kvsall_fused(_ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
-                                      float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas),
-                                      _ptr(out_table), int(out_block_rows), _ptr(mask),
-                                      0 if mask is None else mask.shape[1], float(pos_delta), _stream())
-    _check(rc, "dice_kvsall_fused")
+    _call("dice_kvsall_fused", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
+          float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas), _ptr(out_table),
+          int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta),
+          others=(y, out, loss_acc, status, mask))
 
 
 def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.Tensor, W: int, num_entities: int,
-                   rel: torch.Tensor, coeff: Optional[torch.Tensor], q_dst_table: torch.Tensor, n_dst: int,
+                   rel: torch.Tensor, coeff: Optional[torch.Tensor], q_dst_table: Optional[torch.Tensor], n_dst: int,
                    q_row_offset: int, q_f32: Optional[torch.Tensor], B: int, D: int, status: torch.Tensor,
                    dp_src: Optional[torch.Tensor] = None, dp_dst_table: Optional[torch.Tensor] = None) -> None:
-    rc = _lib.lib().dice_lookup_compose(model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
-                                        int(num_entities), _ptr(rel), _ptr(coeff), _ptr(q_dst_table), n_dst,
-                                        int(q_row_offset), _ptr(q_f32), B, D, _ptr(status), _ptr(dp_src),
-                                        _ptr(dp_dst_table), _stream())
-    _check(rc, "dice_lookup_compose")
+    _call("dice_lookup_compose", rel, model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
+          int(num_entities), _ptr(rel), _ptr(coeff), _ptr(q_dst_table), n_dst, int(q_row_offset), _ptr(q_f32), B, D,
+          _ptr(status), _ptr(dp_src), _ptr(dp_dst_table), others=(idx_h, idx_r, ent_table, status, q_f32))
+
+
+def lookup_vec_supported(model: int, D: int) -> bool:
+    """True when the vectorised lookup / backward kernels cover this model code and embedding width."""
+    return bool(_lib.lib().dice_lookup_vec_supported(int(model), int(D)))
+
+
+def lookup_compose_vec(model: int, normalize: bool, idx_h, idx_r, dp_src: Optional[torch.Tensor],
+                       ent_table: torch.Tensor, W: int, num_entities: int, num_relations: int, rel: torch.Tensor,
+                       coeff: Optional[torch.Tensor], q_dst_table: Optional[torch.Tensor], n_dst: int, q_mc: int,
+                       q_row_offset: int, q_f32: Optional[torch.Tensor], ids_dst_table: Optional[torch.Tensor],
+                       ids_stride: int, B: int, D: int, status: torch.Tensor) -> None:
+    """Head rows are pulled from their owners, composed with the relation rows, and the bf16 query rows are published
+    either through the multicast address ``q_mc`` (one ``multimem.st`` per 16 bytes reaches every rank) or to the
+    ``n_dst`` buffers of ``q_dst_table``.  ``ids_dst_table``: per-destination index buffers receiving ``h | r | dp``
+    (three arrays of ``ids_stride`` entries each)."""
+    _call("dice_lookup_compose_vec", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(dp_src),
+          _ptr(ent_table), int(W), int(num_entities), int(num_relations), _ptr(rel), _ptr(coeff), _ptr(q_dst_table),
+          int(n_dst), int(q_mc) or None, int(q_row_offset), _ptr(q_f32), _ptr(ids_dst_table), int(ids_stride), int(B),
+          int(D), _ptr(status), others=(idx_h, idx_r, dp_src, ent_table, status, q_f32))
 
 
 def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: int, rel, coeff, dq, g_ent_table,
@@ -85,11 +115,25 @@ def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: in
     """Chain rule of the composition.  With ``dq_table`` the query gradient of batch item ``i`` is the sum over the
     ``n_dq`` buffers (one per rank) of their row ``dq_row_offset + i``: the reduce-scatter of the partial query
     gradients happens here, by peer loads."""
-    rc = _lib.lib().dice_compose_backward(model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
-                                          _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(g_ent_table), _ptr(g_rel),
-                                          _ptr(g_coeff), B, D, _ptr(touched_table), _ptr(dq_table), int(n_dq),
-                                          int(dq_row_offset), _stream())
-    _check(rc, "dice_compose_backward")
+    _call("dice_compose_backward", rel, model, int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_table), W,
+          _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(g_ent_table), _ptr(g_rel), _ptr(g_coeff), B, D, _ptr(touched_table),
+          _ptr(dq_table), int(n_dq), int(dq_row_offset), others=(idx_h, idx_r, dq, g_rel))
+
+
+def compose_backward_owner(model: int, normalize: bool, idx_h, idx_r, ent_local: torch.Tensor, W: int, rank: int,
+                           num_entities: int, num_relations: int, rel: torch.Tensor, coeff, dq, dq_table, n_dq: int,
+                           dq_mc: int, g_ent_local: torch.Tensor, g_rel: torch.Tensor, g_coeff, n: int, D: int,
+                           status: torch.Tensor) -> None:
+    """Backward of the composition for the queries whose head row this rank owns.  The query gradient is read through
+    the multicast address ``dq_mc`` (``multimem.ld_reduce``: the sum over all ranks is formed inside the switch), else
+    as the sum of the ``n_dq`` buffers of ``dq_table`` (peer loads), else from ``dq``.  Row gradients stay local."""
+    _req(ent_local, torch.float32, "ent_local")
+    _req(g_ent_local, torch.float32, "g_ent_local")
+    _req(g_rel, torch.float32, "g_rel")
+    _call("dice_compose_backward_owner", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_local),
+          int(W), int(rank), int(num_entities), int(num_relations), _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(dq_table),
+          int(n_dq), int(dq_mc) or None, _ptr(g_ent_local), _ptr(g_rel), _ptr(g_coeff), int(n), int(D), _ptr(status),
+          others=(idx_h, idx_r, ent_local, dq, g_ent_local, g_rel, status))
 
 
 def mask_stride(n_bits: int) -> int:
@@ -98,71 +142,75 @@ def mask_stride(n_bits: int) -> int:
 
 
 def build_label_masks(dp_idx, offsets, values, n: int, W: int, rank: int, mask_q: torch.Tensor,
-                      mask_e: torch.Tensor, first: Optional[torch.Tensor] = None) -> None:
+                      mask_e: torch.Tensor, first: Optional[torch.Tensor] = None,
+                      num_data_points: int = 0, num_local_rows: int = 0,
+                      status: Optional[torch.Tensor] = None) -> None:
     """Set the positive-label bits of a batch in both mask orientations (masks must be zeroed by the caller).
     With ``first`` (int32 ``[n + 1]`` scratch) the work is spread one thread per positive label instead of one warp
-    per data point, which is faster when a few data points own most of the positives."""
+    per data point, which is faster when a few data points own most of the positives.  ``num_data_points`` /
+    ``num_local_rows`` (with ``status``) switch on range checks of the data-point ids and of the CSR values."""
     _req(mask_q, torch.int32, "mask_q")
     _req(mask_e, torch.int32, "mask_e")
     if first is not None:
         _req(first, torch.int32, "first")
         assert first.numel() >= n + 1
-        rc = _lib.lib().dice_build_label_masks_flat(_ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), n, W,
-                                                    rank, _ptr(mask_q), mask_q.shape[1], _ptr(mask_e),
-                                                    mask_e.shape[1], _stream())
-        _check(rc, "dice_build_label_masks_flat")
+        _call("dice_build_label_masks_flat", mask_q, _ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), n, W,
+              rank, _ptr(mask_q), mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], int(num_data_points),
+              int(num_local_rows), _ptr(status), others=(dp_idx, offsets, values, first, mask_e, status))
         return
-    rc = _lib.lib().dice_build_label_masks(_ptr(dp_idx), _ptr(offsets), _ptr(values), n, W, rank, _ptr(mask_q),
-                                           mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], _stream())
-    _check(rc, "dice_build_label_masks")
+    _call("dice_build_label_masks", mask_q, _ptr(dp_idx), _ptr(offsets), _ptr(values), n, W, rank, _ptr(mask_q),
+          mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], others=(dp_idx, offsets, values, mask_e))
 
 
 def positive_scan(dp_idx, offsets, n: int, first) -> None:
-    _check(_lib.lib().dice_positive_scan(_ptr(dp_idx), _ptr(offsets), n, _ptr(first), _stream()), "dice_positive_scan")
+    _call("dice_positive_scan", first, _ptr(dp_idx), _ptr(offsets), n, _ptr(first), others=(dp_idx, offsets))
 
 
 def positive_correction(dp_idx, offsets, values, first, q, e, dq, de, loss_acc, weight: float, scale: float, n: int,
                         D: int, W: int = 1, rank: int = 0, dq_table: Optional[torch.Tensor] = None,
                         dq_block_rows: int = 0) -> None:
-    rc = _lib.lib().dice_positive_correction(_ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), _ptr(q), _ptr(e),
-                                             _ptr(dq), _ptr(de), _ptr(loss_acc), float(weight), float(scale), n, D, W,
-                                             rank, _ptr(dq_table), int(dq_block_rows), _stream())
-    _check(rc, "dice_positive_correction")
+    _call("dice_positive_correction", q, _ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), _ptr(q), _ptr(e),
+          _ptr(dq), _ptr(de), _ptr(loss_acc), float(weight), float(scale), n, D, W, rank, _ptr(dq_table),
+          int(dq_block_rows), others=(dp_idx, offsets, values, first, e, dq, de, loss_acc))
 
 
 def optimizer_step(kind: int, param, grad, m, v, shadow, step, lr, beta1, beta2, eps, weight_decay,
-                   grad_table: Optional[torch.Tensor] = None, n_grad: int = 0) -> None:
-    rc = _lib.lib().dice_optimizer_step(kind, _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow), _ptr(step),
-                                        param.numel(), float(lr), float(beta1), float(beta2), float(eps),
-                                        float(weight_decay), _ptr(grad_table), int(n_grad), _stream())
-    _check(rc, "dice_optimizer_step")
+                   grad_table: Optional[torch.Tensor] = None, n_grad: int = 0, grad_mc: int = 0,
+                   status: Optional[torch.Tensor] = None) -> None:
+    """Fused Adam / AdamW / SGD / ADOPT sweep.  The gradient is ``grad``, or the sum of the ``n_grad`` buffers of
+    ``grad_table`` (peer loads), or the sum over all ranks read through the multicast address ``grad_mc``
+    (``multimem.ld_reduce``); with ``status`` the sweep is skipped once that word holds an error."""
+    _call("dice_optimizer_step", param, kind, _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow), _ptr(step),
+          param.numel(), float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), _ptr(grad_table),
+          int(n_grad), int(grad_mc) or None, _ptr(status), others=(grad, m, v, shadow, step, status))
 
 
 def cast_bf16(src: torch.Tensor, dst: torch.Tensor) -> None:
-    _check(_lib.lib().dice_cast_bf16(_ptr(src), _ptr(dst), src.numel(), _stream()), "dice_cast_bf16")
+    _call("dice_cast_bf16", src, _ptr(src), _ptr(dst), src.numel(), others=(dst,))
 
 
-def finish_step(acc, loss_out, inv_count: float, step, acc_table: Optional[torch.Tensor] = None, n_acc: int = 0) -> None:
-    _check(_lib.lib().dice_finish_step(_ptr(acc), _ptr(loss_out), float(inv_count), _ptr(step), _ptr(acc_table),
-                                       int(n_acc), _stream()), "dice_finish_step")
+def finish_step(acc, loss_out, inv_count: float, step, acc_table: Optional[torch.Tensor] = None, n_acc: int = 0,
+                status: Optional[torch.Tensor] = None) -> None:
+    _call("dice_finish_step", loss_out, _ptr(acc), _ptr(loss_out), float(inv_count), _ptr(step), _ptr(acc_table),
+          int(n_acc), _ptr(status), others=(acc, step, status))
 
 
 def p2p_barrier(sig_table: torch.Tensor, rank: int, world: int, count: torch.Tensor, status: torch.Tensor,
                 spin_limit: int = 0) -> None:
     """Bounded device-side barrier over the ranks' signal arrays (see ``p2p_barrier_kernel``)."""
-    _check(_lib.lib().dice_p2p_barrier(_ptr(sig_table), rank, world, _ptr(count), _ptr(status), int(spin_limit),
-                                       _stream()), "dice_p2p_barrier")
+    _call("dice_p2p_barrier", count, _ptr(sig_table), rank, world, _ptr(count), _ptr(status), int(spin_limit),
+          others=(sig_table, status))
 
 
 def timestamp(slots: torch.Tensor, index: int) -> None:
     """Write the GPU nanosecond timer into ``slots[index]`` (int64) in stream order; capturable in a CUDA graph."""
     _req(slots, torch.int64, "slots")
-    _check(_lib.lib().dice_timestamp(slots.data_ptr() + 8 * int(index), _stream()), "dice_timestamp")
+    _call("dice_timestamp", slots, slots.data_ptr() + 8 * int(index))
 
 
 def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
     """Register (or clear with ``None``) a ``[64, 8]`` int64 device buffer receiving per-tile clock stamps of CTA 0 of
-    every following ``kvsall_fused`` launch (pipeline diagnostics; see ``profile_fused --trace``)."""
+    every following ``kvsall_fused`` launch (pipeline diagnostics)."""
     if buffer is not None:
         _req(buffer, torch.int64, "trace buffer")
         assert buffer.numel() >= 512
@@ -180,9 +228,8 @@ def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0, step: 
     else:
         assert out.dim() == 2 and out.stride(1) == 1, "only column blocks of a row-major matrix are supported"
         stride, row_len = out.stride(0), out.shape[1]
-    _check(_lib.lib().dice_uniform_int(_ptr(out), out.numel(), int(high), int(seed) & (2 ** 64 - 1),
-                                       int(offset) & (2 ** 64 - 1), _ptr(step), int(stride), int(row_len),
-                                       _stream()), "dice_uniform_int")
+    _call("dice_uniform_int", out, _ptr(out), out.numel(), int(high), int(seed) & (2 ** 64 - 1),
+          int(offset) & (2 ** 64 - 1), _ptr(step), int(stride), int(row_len), others=(step,))
 
 
 def neg_sample(pos: torch.Tensor, k: int, num_entities: int, seed: int, offset: int, y: torch.Tensor,
@@ -206,10 +253,9 @@ def neg_sample(pos: torch.Tensor, k: int, num_entities: int, seed: int, offset: 
         for c in (h, r, t):
             _req(c, torch.int64, "hrt")
             assert c.numel() >= N
-    _check(_lib.lib().dice_neg_sample(_ptr(pos), B, int(k), int(num_entities), int(seed) & (2 ** 64 - 1),
-                                      int(offset) & (2 ** 64 - 1), _ptr(step), int(per_negative_coin),
-                                      float(label_pos), float(label_neg), _ptr(x), _ptr(h), _ptr(r), _ptr(t),
-                                      _ptr(y), _stream()), "dice_neg_sample")
+    _call("dice_neg_sample", pos, _ptr(pos), B, int(k), int(num_entities), int(seed) & (2 ** 64 - 1),
+          int(offset) & (2 ** 64 - 1), _ptr(step), int(per_negative_coin), float(label_pos), float(label_neg),
+          _ptr(x), _ptr(h), _ptr(r), _ptr(t), _ptr(y), others=(y, x, h, r, t, step))
 
 
 def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_step: int, C: int,
@@ -217,8 +263,10 @@ def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_st
                   g_ent_table: Optional[torch.Tensor] = None, dq: Optional[torch.Tensor] = None,
                   scores: Optional[torch.Tensor] = None, loss_acc: Optional[torch.Tensor] = None,
                   scale: float = 1.0, kind: int = 0, margin: float = 0.0, eps: float = 0.0,
-                  touched_table: Optional[torch.Tensor] = None) -> None:
-    """Scores of every query against its own candidate list, BCE loss and gradients (see ``dice_candidate_bce``)."""
+                  touched_table: Optional[torch.Tensor] = None, num_entities: int = 0,
+                  status: Optional[torch.Tensor] = None) -> None:
+    """Scores of every query against its own candidate list, BCE loss and gradients (see ``dice_candidate_bce``).
+    With ``num_entities`` and ``status`` candidate ids outside ``[0, num_entities)`` are reported and skipped."""
     _req(q, torch.float32, "q")
     _req(cand, torch.int64, "cand")
     if labels is not None:
@@ -228,10 +276,10 @@ def candidate_bce(q: torch.Tensor, cand: torch.Tensor, cand_stride: int, cand_st
     if loss_acc is not None:
         _req(loss_acc, torch.float64, "loss_acc")
     N, D = q.shape
-    _check(_lib.lib().dice_candidate_bce(_ptr(q), _ptr(cand), int(cand_stride), int(cand_step), int(C), _ptr(labels),
-                                         _ptr(ent_table), _ptr(g_ent_table), _ptr(dq), _ptr(scores), _ptr(loss_acc),
-                                         float(scale), int(kind), float(margin), float(eps), N, D, int(W),
-                                         _ptr(touched_table), _stream()), "dice_candidate_bce")
+    _call("dice_candidate_bce", q, _ptr(q), _ptr(cand), int(cand_stride), int(cand_step), int(C), _ptr(labels),
+          _ptr(ent_table), _ptr(g_ent_table), _ptr(dq), _ptr(scores), _ptr(loss_acc), float(scale), int(kind),
+          float(margin), float(eps), N, D, int(W), _ptr(touched_table), int(num_entities), _ptr(status),
+          others=(cand, labels, ent_table, dq, scores, loss_acc, status))
 
 
 def sparse_rows_optimizer(kind: int, param, grad, m, v, shadow, touched: torch.Tensor, step, lr, beta1, beta2, eps,
@@ -239,10 +287,9 @@ def sparse_rows_optimizer(kind: int, param, grad, m, v, shadow, touched: torch.T
     """Update only the rows of ``param [rows, D]`` whose ``touched`` flag (uint8) is set; clears flag and gradient."""
     _req(touched, torch.uint8, "touched")
     rows, D = param.shape
-    _check(_lib.lib().dice_sparse_rows_optimizer(int(kind), _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow),
-                                                 _ptr(touched), int(rows), int(D), _ptr(step), float(lr),
-                                                 float(beta1), float(beta2), float(eps), float(weight_decay),
-                                                 _stream()), "dice_sparse_rows_optimizer")
+    _call("dice_sparse_rows_optimizer", param, int(kind), _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow),
+          _ptr(touched), int(rows), int(D), _ptr(step), float(lr), float(beta1), float(beta2), float(eps),
+          float(weight_decay), others=(grad, m, v, shadow, touched, step))
 
 
 def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], target_idx: Optional[torch.Tensor],
@@ -277,13 +324,12 @@ def eval_rank(x: torch.Tensor, y: torch.Tensor, target: Optional[torch.Tensor], 
         _req(cand_idx, torch.int32, "cand_idx")
         _req(cand_count, torch.int32, "cand_count")
         cap = cand_score.shape[1]
-    rc = _lib.lib().dice_eval_rank(_ptr(x), x.shape[0], _ptr(y), y.shape[0], x.shape[1], _ptr(target),
-                                   _ptr(target_idx), _ptr(col_bias), int(y_offset), int(y_stride), _ptr(greater),
-                                   int(k), int(cap), _ptr(cand_score), _ptr(cand_idx), _ptr(cand_count),
-                                   _ptr(status), int(num_ctas), _ptr(margin), _ptr(band_rows), _ptr(band_cols),
-                                   _ptr(band_count), 0 if band_rows is None else band_rows.numel(),
-                                   _ptr(row_floor), _stream())
-    _check(rc, "dice_eval_rank")
+    _call("dice_eval_rank", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], x.shape[1], _ptr(target), _ptr(target_idx),
+          _ptr(col_bias), int(y_offset), int(y_stride), _ptr(greater), int(k), int(cap), _ptr(cand_score),
+          _ptr(cand_idx), _ptr(cand_count), _ptr(status), int(num_ctas), _ptr(margin), _ptr(band_rows),
+          _ptr(band_cols), _ptr(band_count), 0 if band_rows is None else band_rows.numel(), _ptr(row_floor),
+          others=(y, target, target_idx, greater, status, col_bias, cand_score, cand_idx, cand_count, margin,
+                  band_rows, band_cols, band_count, row_floor))
 
 
 def eval_band_exact(q: torch.Tensor, y: torch.Tensor, band_rows: torch.Tensor, band_cols: torch.Tensor,
@@ -296,10 +342,9 @@ def eval_band_exact(q: torch.Tensor, y: torch.Tensor, band_rows: torch.Tensor, b
     _req(band_cols, torch.int32, "band_cols")
     _req(band_count, torch.int64, "band_count")
     _req(greater, torch.int32, "greater")
-    _check(_lib.lib().dice_eval_band_exact(_ptr(q), _ptr(y), q.shape[1], y.shape[0], int(y_offset), int(y_stride),
-                                           _ptr(col_bias), _ptr(band_rows), _ptr(band_cols), _ptr(band_count),
-                                           band_rows.numel(), _ptr(target), _ptr(greater), _stream()),
-           "dice_eval_band_exact")
+    _call("dice_eval_band_exact", q, _ptr(q), _ptr(y), q.shape[1], y.shape[0], int(y_offset), int(y_stride),
+          _ptr(col_bias), _ptr(band_rows), _ptr(band_cols), _ptr(band_count), band_rows.numel(), _ptr(target),
+          _ptr(greater), others=(y, band_rows, band_cols, band_count, target, greater, col_bias))
 
 
 def eval_rank_cand_cap(x_rows: int, y_rows: int, D: int, k: int, num_ctas: int = 0) -> int:
@@ -320,11 +365,10 @@ def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, targ
     if filt_ptr is not None:
         _req(filt_ptr, torch.int64, "filt_ptr")
         _req(filt_cols, torch.int32, "filt_cols")
-    rc = _lib.lib().dice_eval_sparse(_ptr(q), _ptr(y), q.shape[0], q.shape[1], y.shape[0], int(y_offset),
-                                     int(y_stride), _ptr(target_idx), _ptr(col_bias), _ptr(target_in),
-                                     _ptr(filt_ptr), _ptr(filt_cols), _ptr(target_score), _ptr(filtered_greater),
-                                     int(fp32), _stream())
-    _check(rc, "dice_eval_sparse")
+    _call("dice_eval_sparse", q, _ptr(q), _ptr(y), q.shape[0], q.shape[1], y.shape[0], int(y_offset), int(y_stride),
+          _ptr(target_idx), _ptr(col_bias), _ptr(target_in), _ptr(filt_ptr), _ptr(filt_cols), _ptr(target_score),
+          _ptr(filtered_greater), int(fp32),
+          others=(y, target_idx, col_bias, target_in, filt_ptr, filt_cols, target_score, filtered_greater))
 
 
 def check_status(status: torch.Tensor, where: str = "") -> None:

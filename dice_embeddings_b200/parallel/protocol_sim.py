@@ -1,7 +1,7 @@
 """Host-side replay of the sharded training step's communication protocol with Python threads.
 
 The GPU step (:mod:`dice_embeddings_b200.parallel.sharded_engine`) lets kernels read and write peer memory directly
-and orders them with four bounded device barriers.  There is no memory checker for that on the target machines, so
+and orders them with three bounded device barriers per step.  There is no memory checker for that on the target machines, so
 the same sequence of reads, writes, reductions and barriers is replayed here on NumPy arrays, one thread per rank:
 
 * :class:`SimHeap` – one named buffer per rank, visible to all ranks; every access is tagged with the *phase* of
@@ -10,9 +10,9 @@ the same sequence of reads, writes, reductions and barriers is replayed here on 
 * :class:`SimBarrier` – the signal-counter barrier of ``p2p_barrier_kernel``: add 1 to ``sig[peer][rank]`` on every
   peer, then wait until ``sig[rank][p] >= count`` for all ``p``, giving up after a bounded number of polls with
   status ``TIMEOUT_PEER``;
-* :func:`run_sharded_step` – the step itself (lookup by peer reads, query broadcast by peer writes, scoring of the
-  local shard, reduce-scatter of the query gradient by peer loads at the consumer, scatter of row gradients to their owners,
-  replicated update of the relation table from all ranks' gradient buffers) on a toy DistMult model, compared by the
+* :func:`run_sharded_step` – the step itself (lookup by peer reads, broadcast of queries and batch indices by peer
+  writes, scoring of the local shard, owner-side backward that sums a query's gradient partials from all ranks where
+  its head row lives, replicated update of the relation table from all ranks' gradient buffers) on a toy DistMult model, compared by the
   tests against a single-process computation; faults (a rank that never arrives, a dropped signal, a removed
   barrier) are injected on the host.
 """
@@ -43,7 +43,8 @@ class SimHeap:
     For every (name, owner) buffer the heap remembers, per phase, which ranks read, wrote or reduced into it.
     Within one phase these combinations are legal: many readers; many reducers (commutative adds); one writer per
     disjoint region (callers pass ``region`` keys; the same region written twice in a phase is a hazard).  A read in
-    a phase in which anyone writes or reduces the same buffer is a hazard, and so is a write next to a reduce."""
+    a phase in which another rank writes or reduces the same buffer is a hazard, and so is one rank's write next to
+    another rank's reduce (a rank's own accesses follow stream order)."""
 
     def __init__(self, world: int):
         self.world = world
@@ -63,7 +64,7 @@ class SimHeap:
                 raise ProtocolHazard(f"rank {rank} reads {name}@{owner} while {e['w'] | e['a']} modify it (phase {key[2]})")
             if kind in ("w", "a") and e["r"] - {rank}:
                 raise ProtocolHazard(f"rank {rank} modifies {name}@{owner} while {e['r']} read it (phase {key[2]})")
-            if kind == "w" and e["a"] or kind == "a" and e["w"]:
+            if kind == "w" and e["a"] - {rank} or kind == "a" and e["w"] - {rank}:   # one rank's own accesses are stream-ordered
                 raise ProtocolHazard(f"write and reduce of {name}@{owner} in one phase ({key[2]})")
             if kind == "w":
                 if region in e["regions"]:
@@ -136,10 +137,20 @@ def reference_step(E, R, h, r, labels, lr):
 def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[str] = None,
                      absent_rank: Optional[int] = None, drop: Optional[Callable[[int, int, int], bool]] = None,
                      poll_limit: int = 20000, steps: int = 1):
-    """Replay one sharded step.  ``h, r, labels`` hold the *global* batch (rank ``k`` owns its rows
+    """Replay the sharded step.  ``h, r, labels`` hold the *global* batch (rank ``k`` owns its rows
     ``[k·b, (k+1)·b)``); entity ``e`` lives on rank ``e % world`` at row ``e // world``.
 
-    Fault injection: ``skip_barrier`` ∈ {"S0","S1","S2","S3"} removes that barrier on every rank (the phases it
+    Three barriers per step:
+
+    * ``S1`` after the lookup (peer reads of head rows) and the broadcast of query rows and batch indices,
+    * ``S2`` after the two scoring passes over the local shard (every rank's partial ``dQ`` is complete),
+    * ``S3`` after the *owner-side* backward (the owner of a head row sums that query's ``dQ`` partials from all
+      ranks, applies the chain rule and adds the row gradient to its own shard, so no row gradient crosses the
+      fabric) and the update of the local entity shard; behind it the replicated relation table is updated from
+      all ranks' gradient buffers and the loss partials are summed.  ``S3`` also orders the next step's peer reads
+      of the updated entity rows, so no barrier opens a step.
+
+    Fault injection: ``skip_barrier`` ∈ {"S1","S2","S3"} removes that barrier on every rank (the phases it
     separated then count as one, which is what the hazard check looks at); ``absent_rank`` never starts;
     ``drop(sender, peer, count)`` suppresses single barrier signals.  ``steps`` repeats the step on the same batch.
     Returns ``(E_new, R_new, loss)`` assembled from the shards, or raises the first rank failure."""
@@ -150,9 +161,11 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
     b = B // W
     rows = (NE + W - 1) // W
     heap = SimHeap(W)
-    for name, shape in (("E", (rows, D)), ("gE", (rows, D)), ("Q", (B, D)), ("dQ", (B, D)), ("gR", R.shape),
-                        ("loss", (1,))):
-        heap.alloc(name, shape)
+    for name, shape, dt in (("E", (rows, D), np.float64), ("Q", (B, D), np.float64), ("dQ", (B, D), np.float64),
+                            ("gR", R.shape, np.float64), ("loss", (1,), np.float64), ("h", (B,), np.int64),
+                            ("r", (B,), np.int64)):
+        heap.alloc(name, shape, dt)
+    gE = [np.zeros((rows, D)) for _ in range(W)]               # row gradients never leave their owner
     Rrep = [R.copy() for _ in range(W)]
     for e in range(NE):
         heap.bufs["E"][e % W][e // W] = E[e]
@@ -174,15 +187,16 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
             own = np.arange(rank, NE, W)                       # global ids of the local rows
             n_own = len(own)
             for _ in range(steps):
-                barrier(rank, "S0")                            # the previous step's updates are visible everywhere
-                # lookup by peer reads + compose + broadcast of the queries by peer writes
+                # lookup by peer reads + compose + broadcast of the queries and of the batch indices by peer writes
                 hv = np.stack([heap.read("E", int(e) % W, rank)[int(e) // W] for e in my_h])
                 q = hv * Rrep[rank][my_r]
                 for peer in range(W):
                     heap.write("Q", peer, rank, slice(lo, lo + b), q, region=("rows", lo))
+                    heap.write("h", peer, rank, slice(lo, lo + b), my_h, region=("rows", lo))
+                    heap.write("r", peer, rank, slice(lo, lo + b), my_r, region=("rows", lo))
+                barrier(rank, "S1")                            # all queries have landed; last step's sums were read
                 heap.write("gR", rank, rank, slice(None), 0.0)
                 heap.write("loss", rank, rank, slice(None), 0.0)
-                barrier(rank, "S1")                            # all queries have landed, accumulators are clear
                 Eloc = heap.read("E", rank, rank)[:n_own]
                 Q = heap.read("Q", rank, rank)
                 s = Q @ Eloc.T                                 # [B, local rows]
@@ -190,23 +204,23 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 sig = 1.0 / (1.0 + np.exp(-s))
                 heap.add("loss", rank, rank, 0, np.sum(np.maximum(s, 0) - s * y + np.log1p(np.exp(-np.abs(s)))))
                 ds = (sig - y) / (B * NE)
-                heap.add("gE", rank, rank, np.arange(n_own), ds.T @ Q)
+                gE[rank][:n_own] += ds.T @ Q
                 heap.add("dQ", rank, rank, np.arange(B), ds @ Eloc)   # partial over this shard, kept locally
                 barrier(rank, "S2")                            # every rank's partial of dQ is complete
-                # reduce-scatter, consumer side: the owner of the batch slice sums all ranks' partial rows
-                dq = sum(heap.read("dQ", p, rank)[lo:lo + b] for p in range(W))
-                gh = dq * Rrep[rank][my_r]
-                for e, g in zip(my_h, gh):                     # row gradients go to the owners of the head rows
-                    heap.add("gE", int(e) % W, rank, int(e) // W, g)
-                heap.add("gR", rank, rank, my_r, dq * hv)
-                barrier(rank, "S3")                            # all gradients are complete
+                # owner-side backward: queries whose head row lives here; their dQ is the sum of all ranks' partials
+                h_all, r_all = heap.read("h", rank, rank), heap.read("r", rank, rank)
+                mine = np.nonzero(h_all % W == rank)[0]
+                dq = sum(heap.read("dQ", p, rank)[mine] for p in range(W)) if len(mine) else np.zeros((0, D))
+                hv_own = heap.read("E", rank, rank)[h_all[mine] // W]
+                np.add.at(gE[rank], h_all[mine] // W, dq * Rrep[rank][r_all[mine]])
+                heap.add("gR", rank, rank, r_all[mine], dq * hv_own)
+                g_own = gE[rank].copy()                        # the update follows this rank's own reads in stream order
+                heap.write("E", rank, rank, slice(None), heap.bufs["E"][rank] - lr * g_own)
+                gE[rank][:] = 0.0
+                barrier(rank, "S3")                            # shards updated, all partial sums complete, dQ pulls done
                 gR = sum(heap.read("gR", p, rank) for p in range(W))     # replicated all-reduce by peer reads
                 loss = sum(float(heap.read("loss", p, rank)[0]) for p in range(W)) / (B * NE)
-                g_own = heap.read("gE", rank, rank).copy()
-                heap.next_phase(rank)                          # optimiser: ordered after this rank's own reads only
                 Rrep[rank] = Rrep[rank] - lr * gR
-                heap.write("E", rank, rank, slice(None), heap.bufs["E"][rank] - lr * g_own)
-                heap.write("gE", rank, rank, slice(None), 0.0)
                 heap.write("dQ", rank, rank, slice(None), 0.0)
                 losses[rank] = loss
         except BaseException as exc:  # noqa: BLE001 - reported to the caller

@@ -1,28 +1,36 @@
 """Row-sharded fused training step over several GPUs of one node (one process per GPU).
 
 Entity row ``e`` lives on rank ``e % W`` at local row ``e // W``; relations (and the Keci coefficient) are
-replicated.  With ``comm="p2p"`` every communication step of the reference-free design happens *inside* the
-kernels through peer pointers of a symmetric heap:
+replicated.  With ``comm="p2p"`` every communication step happens *inside* the kernels through a symmetric heap that
+is mapped on every rank and, where the fabric offers it, bound to an NVSwitch multicast object:
 
 ====  =====================================================  ==================================================
 step  kernel                                                 traffic over NVLink
 ====  =====================================================  ==================================================
-S0    ``p2p_barrier``                                        flags
-1     ``lookup_compose``: pull ``E[h]`` from the owner,       peer loads of rows; peer stores of bf16 query rows
-      compose, push the query row (+ data-point id) to         (the all-gather of Q)
-      every rank's ``Q`` buffer
+1     ``lookup_compose_vec``: pull ``E[h]`` from the owner,    peer loads of rows; one ``multimem.st`` per 16 bytes
+      compose, publish the bf16 query row and the batch        of query row reaches every rank (the all-gather of
+      indices on every rank                                    Q); without multicast, one store per rank
 S1    ``p2p_barrier``
-2     ``build_label_masks`` + ``kvsall_fused`` (entity-       none (local shard × all queries)
-      stationary): loss and dense ``dE`` of the local shard
+2     ``build_label_masks`` + ``kvsall_fused`` (entity-        none (local shard × all queries; the label CSR is
+      stationary): loss and dense ``dE`` of the local shard    partitioned by owner when the engine is built)
 3     ``kvsall_fused`` (query-stationary): partial ``dQ``      none (the partials of the whole batch stay local)
       of the local shard for all queries
 S2    ``p2p_barrier``
-4     ``compose_backward``: the owner of a batch slice sums    peer loads (the reduce-scatter of dQ, consumer side);
-      all ranks' partial ``dQ`` rows, chain rule, row grads    peer ``red.add`` into the owner's gradient shard
+4     ``compose_backward_owner``: the *owner of the head       ``multimem.ld_reduce.add`` of the query-gradient rows
+      row* sums that query's partial ``dQ`` over all ranks,     (summed inside the switch: the reduce-scatter of
+      applies the chain rule and adds the row gradient to       dQ); without multicast, W peer loads per element.
+      its own gradient shard                                    No row gradient crosses the fabric.
+5     ``optimizer_step`` over the local entity shard           none
 S3    ``p2p_barrier``
-5     ``optimizer_step``: local shard; relations read every    peer loads (all-reduce folded into the update)
-      rank's gradient buffer; ``finish_step`` sums the losses
+6     ``optimizer_step`` of the replicated tables from the     ``multimem.ld_reduce`` (or peer loads) of every
+      sum of all ranks' gradient buffers; ``finish_step``       rank's buffer: the all-reduce folded into the update
+      sums the loss partials
 ====  =====================================================  ==================================================
+
+``S3`` also orders the next step's peer reads of the updated entity rows, so a step needs three barriers.  Buffers
+that peers read after a barrier (``gR``, loss partials) are cleared behind the *next* barrier, when every peer is
+known to have read them.  Once a barrier times out the status word is set and every later kernel that would touch
+peer memory returns at once; :meth:`check` reports it.
 
 ``comm="nccl"`` runs the same local kernels but moves data with ``torch.distributed`` collectives
 (all-gather, reduce-scatter, all-reduce); it is the comparison pipeline.  Buffers are never handed to library
@@ -40,6 +48,17 @@ import torch.distributed as dist
 from ..ops import kernels as K
 from ..ops.fused_step import fused_model_code
 from .symm import SymmetricHeap
+
+
+def partition_csr(offsets: torch.Tensor, values: torch.Tensor, world: int, rank: int):
+    """CSR restricted to the values owned by ``rank`` (``value % world == rank``), re-numbered as local rows
+    (``value // world``); row ``i`` of the result lists the owned entries of row ``i`` of the input."""
+    own = (values % world) == rank
+    csum = torch.zeros(values.numel() + 1, dtype=torch.int64, device=values.device)
+    torch.cumsum(own.to(torch.int64), 0, out=csum[1:])
+    new_offsets = csum[offsets].contiguous()
+    new_values = torch.div(values[own], world, rounding_mode="floor").contiguous()
+    return new_offsets, new_values
 
 
 def owner_of(e: torch.Tensor, world: int) -> torch.Tensor:
@@ -65,7 +84,8 @@ def scatter_shard_back(full: torch.Tensor, shard: torch.Tensor, rank: int, world
 
 class ShardedKvsAllEngine:
     def __init__(self, model, dataset, batch_size: int, lr: float, weight_decay: float = 0.0, device=None,
-                 comm: str = "p2p", group=None, use_graph: bool = True, label_mode: Optional[str] = None):
+                 comm: str = "p2p", group=None, use_graph: bool = True, label_mode: Optional[str] = None,
+                 multimem: Optional[bool] = None):
         assert dist.is_initialized(), "ShardedKvsAllEngine needs an initialised process group"
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.W = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -95,18 +115,21 @@ class ShardedKvsAllEngine:
 
         heap = SymmetricHeap(self.group, dev)
         heap.plan("E", (self.rows_pad, D), torch.float32)
-        heap.plan("gE", (self.rows_pad, D), torch.float32)
         heap.plan("gR", (self.NR, D), torch.float32)
         heap.plan("gC", (4,), torch.float32)
         heap.plan("Q", (W * B, D), torch.bfloat16)
         heap.plan("dQ", (W * B, D), torch.float32)   # this rank's partial query gradients for the whole batch
-        heap.plan("dp", (W * B,), torch.int64)
+        heap.plan("ids", (3, W * B), torch.int64)    # h | r | data point of every query of the global batch
         heap.plan("loss", (2,), torch.float64)
         heap.plan("sig", (64,), torch.int32)
         heap.commit()
         self.heap = heap
-        self.E, self.gE, self.gR, self.gC = heap.local("E"), heap.local("gE"), heap.local("gR"), heap.local("gC")
-        self.Q, self.dQ, self.dp_all = heap.local("Q"), heap.local("dQ"), heap.local("dp")
+        want = os.environ.get("DICE_B200_MULTIMEM", "1") != "0" if multimem is None else bool(multimem)
+        self.multimem = bool(want and heap.mc_base and comm == "p2p")
+        self.E, self.gR, self.gC = heap.local("E"), heap.local("gR"), heap.local("gC")
+        self.gE = torch.zeros(self.rows_pad, D, dtype=torch.float32, device=dev)   # row gradients never leave the owner
+        self.Q, self.dQ, self.ids_all = heap.local("Q"), heap.local("dQ"), heap.local("ids")
+        self.h_all, self.r_all, self.dp_all = self.ids_all[0], self.ids_all[1], self.ids_all[2]
         self.loss_acc = heap.local("loss")
         self.E[: self.rows].copy_(take_shard(model.entity_embeddings.weight.data, self.rank, W))
         self.R = model.relation_embeddings.weight.data
@@ -122,9 +145,12 @@ class ShardedKvsAllEngine:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier_count = torch.zeros(1, dtype=torch.int32, device=dev)
 
-        self.tab = SimpleNamespace(E=heap.table("E"), gE=heap.table("gE"), gR=heap.table("gR"), gC=heap.table("gC"),
-                                   Q=heap.table("Q"), dQ=heap.table("dQ"), dp=heap.table("dp"),
+        self.tab = SimpleNamespace(E=heap.table("E"), gR=heap.table("gR"), gC=heap.table("gC"),
+                                   Q=heap.table("Q"), dQ=heap.table("dQ"), ids=heap.table("ids"),
                                    loss=heap.table("loss"), sig=heap.table("sig"))
+        mm = self.multimem
+        self.mc = SimpleNamespace(Q=heap.mc_address("Q") if mm else 0, dQ=heap.mc_address("dQ") if mm else 0,
+                                  gR=heap.mc_address("gR") if mm else 0, gC=heap.mc_address("gC") if mm else 0)
 
         # dataset (replicated): pairs and CSR of known tails
         self.dataset = dataset
@@ -139,6 +165,13 @@ class ShardedKvsAllEngine:
             self.values = self.pairs[:, 2].contiguous()
             pos, base = 1.0, 0.0
         self.pos_weight, self.base = float(pos - base), float(base)
+        self.num_data_points = int(self.offsets.numel() - 1)
+        # the label CSR is partitioned by owner once: this rank keeps the known tails that live in its shard, as
+        # local row numbers, so the label kernels of a step walk 1/W of the positives and filter nothing
+        if comm == "p2p":
+            self.offsets_loc, self.values_loc = partition_csr(self.offsets, self.values, W, self.rank)
+        else:
+            self.offsets_loc, self.values_loc = self.offsets, self.values
 
         self.h = torch.zeros(B, dtype=torch.int64, device=dev)
         self.r = torch.zeros(B, dtype=torch.int64, device=dev)
@@ -170,23 +203,15 @@ class ShardedKvsAllEngine:
     def _barrier(self) -> None:
         K.p2p_barrier(self.tab.sig, self.rank, self.W, self.barrier_count, self.status)
 
-    def _optimizers_and_finish(self, scale: float, reduced: bool) -> None:
-        """``reduced``: replicated gradients / loss were already summed by a collective (nccl flavour)."""
+    def _optimizers_and_finish(self, scale: float) -> None:
+        """Collective flavour: replicated gradients and the loss were already summed by library collectives."""
         b1, b2 = self.betas
         a = (self.lr, b1, b2, self.eps, self.weight_decay)
         K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a)
-        if reduced:
-            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a)
-            if self.coeff_trainable:
-                K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a)
-            K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
-        else:
-            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a,
-                             grad_table=self.tab.gR, n_grad=self.W)
-            if self.coeff_trainable:
-                K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a,
-                                 grad_table=self.tab.gC, n_grad=self.W)
-            K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=self.W)
+        K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a)
+        if self.coeff_trainable:
+            K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a)
+        K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
 
     def _mark(self, name: str) -> None:
         """Phase timing (``DICE_B200_PHASE_TIMING=1``): a one-thread kernel stores the GPU timer after each phase, so
@@ -208,30 +233,33 @@ class ShardedKvsAllEngine:
     def _launch_p2p(self) -> None:
         W, B, D, n = self.W, self.B, self.D, self.W * self.B
         scale = 1.0 / (float(n) * float(self.NE))
+        b1, b2 = self.betas
+        a = (self.lr, b1, b2, self.eps, self.weight_decay)
         self._mark("start")
-        self._barrier()                                   # S0: everyone finished the previous step
-        self._mark("S0")
         self.h.copy_(self.x_in[:, 0])                     # callers only fill x_in and dp
         self.r.copy_(self.x_in[:, 1])
-        self.gR.zero_()
-        self.gC.zero_()
-        self.loss_acc.zero_()
         masks = self.label_mode == "mask"
+        main = torch.cuda.current_stream(self.device)
         if masks:   # cleared on a parallel branch; joined before the masks are built
-            main = torch.cuda.current_stream(self.device)
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
                 self.mask_q.zero_()
                 self.mask_e.zero_()
-        K.lookup_compose(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.NE, self.R, self.coeff,
-                         self.tab.Q, W, self.rank * B, None, B, D, self.status, dp_src=self.dp, dp_dst_table=self.tab.dp)
-        self._mark("zero+lookup")
+        # head rows by peer loads, query rows and batch indices to every rank (multimem.st or one store per rank)
+        K.lookup_compose_vec(self.code, self.normalize, self.h, self.r, self.dp, self.tab.E, W, self.NE, self.NR,
+                             self.R, self.coeff, self.tab.Q, W, self.mc.Q, self.rank * B, None, self.tab.ids, n, B, D,
+                             self.status)
+        self._mark("lookup+allgather")
         self._barrier()                                   # S1: all query rows have landed everywhere
         self._mark("S1")
+        self.gR.zero_()                                   # every peer has read last step's partial sums by now
+        self.gC.zero_()
+        self.loss_acc.zero_()
         if masks:
             main.wait_stream(self._side)
-            K.build_label_masks(self.dp_all, self.offsets, self.values, n, W, self.rank, self.mask_q, self.mask_e,
-                                first=self.first)
+            K.build_label_masks(self.dp_all, self.offsets_loc, self.values_loc, n, 1, 0, self.mask_q, self.mask_e,
+                                first=self.first, num_data_points=self.num_data_points, num_local_rows=self.rows_pad,
+                                status=self.status)
             self._mark("masks")
         e_loc = self.E_bf16[: self.rows]
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
@@ -239,30 +267,42 @@ class ShardedKvsAllEngine:
         self._mark("fused_E")
         K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
                        mask=self.mask_q, pos_delta=self.pos_weight)
-        self._mark("fused_Q+rs")
+        self._mark("fused_Q")
         if not masks:
-            # label term of the positives whose tail lives in this shard: loss, dE rows here, dQ rows at their owners
-            K.positive_scan(self.dp_all, self.offsets, n, self.first)
-            K.positive_correction(self.dp_all, self.offsets, self.values, self.first, self.Q, self.E_bf16, self.dQ,
-                                  self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, W, self.rank)
+            # label term of the positives whose tail lives in this shard: loss, dE rows here, partial dQ rows here
+            K.positive_scan(self.dp_all, self.offsets_loc, n, self.first)
+            K.positive_correction(self.dp_all, self.offsets_loc, self.values_loc, self.first, self.Q, self.E_bf16,
+                                  self.dQ, self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, 1, 0)
             self._mark("positives")
-        self._barrier()                                   # S2: every rank's dQ block is complete
+        self._barrier()                                   # S2: every rank's partial dQ is complete
         self._mark("S2")
-        # the owner of a batch slice sums all ranks' partial query gradients by peer loads (the reduce-scatter)
-        K.compose_backward(self.code, self.normalize, self.h, self.r, self.tab.E, W, self.R, self.coeff, None,
-                           self.tab.gE, self.gR, self.gC if self.coeff_trainable else None, B, D,
-                           dq_table=self.tab.dQ, n_dq=W, dq_row_offset=self.rank * B)
-        self._mark("compose_bwd")
-        self._barrier()                                   # S3: all row gradients reached their owners, all pulls done
+        # owner-side backward: dQ rows summed over the ranks inside the switch (or by peer loads), row gradients local
+        K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank, self.NE,
+                                 self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ, self.gE, self.gR,
+                                 self.gC if self.coeff_trainable else None, n, D, self.status)
+        self._mark("backward+reduce_scatter")
+        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
+                         status=self.status)
+        self._mark("optim_E")
+        self._barrier()                                   # S3: shards updated, partial sums complete, dQ pulls done
         self._mark("S3")
-        self.dQ.zero_()
-        self._optimizers_and_finish(scale, reduced=False)
-        self._mark("optim")
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            self.dQ.zero_()
+        K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a,
+                         grad_table=self.tab.gR, n_grad=W, grad_mc=self.mc.gR, status=self.status)
+        if self.coeff_trainable:
+            K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a,
+                             grad_table=self.tab.gC, n_grad=W, status=self.status)
+        K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=W,
+                      status=self.status)
+        main.wait_stream(self._side)
+        self._mark("optim_R")
 
     def launches_per_step(self) -> int:
         if self.comm != "p2p":
             return 9
-        return 4 + (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
+        return 3 + (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
 
     # ------------------------------------------------------------------ the step, collective flavour
     def _init_nccl_buffers(self) -> None:
@@ -315,7 +355,7 @@ class ShardedKvsAllEngine:
         dist.all_reduce(self.gR, group=g)
         dist.all_reduce(self.gC, group=g)
         dist.all_reduce(self.loss_acc, group=g)
-        self._optimizers_and_finish(scale, reduced=True)
+        self._optimizers_and_finish(scale)
 
     # ------------------------------------------------------------------ driving
     def _run(self) -> None:

@@ -9,14 +9,17 @@ device-side barrier live in the same heap.
 The reference has nothing comparable: its only cross-device traffic is DDP's all-reduce and ``.to('cuda:0')``
 copies (``dicee/trainer/torch_trainer_ddp.py:88``, ``dicee/models/ensemble.py:92-98``).
 
-NVLink multicast binding of the heap is switched off unless ``DICE_B200_MULTICAST=1``: the kernels here use
-unicast peer accesses only, and a rank that exits while its memory is bound to a multicast object can fault its
-peers.
+When the fabric supports it the heap is also bound to an NVLink multicast object (NVSwitch): ``mc_base`` is then the
+multicast address of the heap, and a region's multicast address is ``mc_base + offset``.  A ``multimem.st`` to that
+address stores into every rank's copy of the region and a ``multimem.ld_reduce`` returns the sum over all ranks,
+formed inside the switch.  ``DICE_B200_MULTICAST=0`` (or ``multicast=False``) keeps the heap unicast-only; a rank must
+never exit while its peers still issue ``multimem`` operations, so every user of the heap ends with a barrier and the
+kernels stop touching peer memory once their status word holds an error.
 """
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -35,8 +38,10 @@ class SymmetricHeap:
     """Declare regions with :meth:`plan`, call :meth:`commit` once (collective), then use :meth:`local`,
     :meth:`peer` and :meth:`table`."""
 
-    def __init__(self, group=None, device=None):
+    def __init__(self, group=None, device=None, multicast: Optional[bool] = None):
         self.group = group if group is not None else dist.group.WORLD
+        self.multicast = (os.environ.get("DICE_B200_MULTICAST", "1") != "0") if multicast is None else bool(multicast)
+        self.mc_base = 0
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -55,13 +60,18 @@ class SymmetricHeap:
 
     def commit(self) -> "SymmetricHeap":
         import torch.distributed._symmetric_memory as symm_mem
-        if os.environ.get("DICE_B200_MULTICAST") != "1":
+        if not self.multicast:   # read by the allocator when the first block of the process is created
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         total = (self._size + _ALIGN - 1) // _ALIGN * _ALIGN
         self._heap = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self._heap.zero_()
         self._hdl = symm_mem.rendezvous(self._heap, self.group)
         self.base_ptrs: List[int] = [int(p) for p in self._hdl.buffer_ptrs]
+        mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0) if (self.multicast and self.world > 1) else 0
+        # every rank must take the same path: use the multicast mapping only when all of them have one
+        flag = torch.tensor([1 if mc else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        self.mc_base = mc if int(flag.item()) == 1 else 0
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
         return self
@@ -90,6 +100,10 @@ class SymmetricHeap:
 
     def address(self, name: str, rank: int) -> int:
         return self.base_ptrs[rank] + self._plan[name][2]
+
+    def mc_address(self, name: str) -> int:
+        """Multicast address of region ``name`` (0 when the heap has no multicast mapping)."""
+        return self.mc_base + self._plan[name][2] if self.mc_base else 0
 
     def table(self, name: str) -> torch.Tensor:
         """Device int64 tensor with the address of region ``name`` on every rank (index = rank)."""

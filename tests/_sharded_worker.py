@@ -1,5 +1,6 @@
 """Worker for the multi-GPU tests (launched with torch.distributed.run): trains the same model with the
-peer-memory sharded engine, the collective-based sharded engine and — on rank 0 — the single-GPU engine on the
+peer-memory sharded engine (multimem and unicast flavours, mask and sparse labels), the collective-based sharded
+engine and — on rank 0 — the single-GPU engine on the
 concatenated batch, and checks that losses and final tables agree."""
 import os
 import sys
@@ -42,11 +43,15 @@ def main():
 
     g = torch.Generator().manual_seed(5)
     results = {}
-    for comm in ("p2p", "p2p-sparse", "nccl"):
+    mm_used = None
+    for comm in ("p2p", "p2p-unicast", "p2p-sparse", "nccl"):
         ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(dev)
         model = make()
         eng = ShardedKvsAllEngine(model, ds, batch_size=B, lr=lr, device=dev, comm=comm.split("-")[0],
-                                  label_mode="sparse" if comm.endswith("sparse") else "mask")
+                                  label_mode="sparse" if comm.endswith("sparse") else "mask",
+                                  multimem=False if comm.endswith("unicast") else None)
+        if comm == "p2p":
+            mm_used = eng.multimem
         g.manual_seed(5)
         losses = []
         for _ in range(steps):
@@ -66,6 +71,14 @@ def main():
     d_r = (rp - rn).abs().max().item() / rn.abs().max().item()
     ok &= d_e < 2e-2 and d_r < 2e-2
     msg.append(f"p2p vs nccl: losses {lp} / {ln}; rel diff E {d_e:.2e} R {d_r:.2e}")
+    lu, eu, ru = results["p2p-unicast"]
+    for a, b in zip(lu, lp):
+        ok &= abs(a - b) < 2e-3 * abs(b) + 1e-6
+    d_e = (eu - ep).abs().max().item() / ep.abs().max().item()
+    d_r = (ru - rp).abs().max().item() / rp.abs().max().item()
+    ok &= d_e < 2e-2 and d_r < 2e-2
+    msg.append(f"multimem ({'on' if mm_used else 'unavailable: both runs unicast'}) vs unicast: losses {lp} / {lu}; "
+               f"rel diff E {d_e:.2e} R {d_r:.2e}")
     lsp, esp, rsp = results["p2p-sparse"]
     for a, b in zip(lsp, lp):
         ok &= abs(a - b) < 2e-3 * abs(b) + 1e-6

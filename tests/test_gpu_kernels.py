@@ -135,6 +135,84 @@ def test_positive_correction_matches_dense():
     assert torch.allclose(de, -w * scale * (Y.t() @ q.float()), atol=1e-4, rtol=1e-3)
 
 
+@pytest.mark.parametrize("name,code,norm", [("DistMult", 0, False), ("ComplEx", 1, False), ("QMult", 2, True),
+                                             ("OMult", 3, True), ("Keci", 4, False)])
+@pytest.mark.parametrize("D", [64, 256])
+def test_vectorised_lookup_and_owner_backward(name, code, norm, D):
+    """The 16-byte-per-thread lookup and the owner-side backward against autograd.  The backward is run as W = 3
+    emulated ranks on one device (one launch per rank over the same batch, each keeping the rows it owns), which
+    must add up to the single-table gradient."""
+    torch.manual_seed(1)
+    NE, NR, B, W = 500, 20, 333, 3
+    E = torch.randn(NE, D, device=DEV, requires_grad=True)
+    R = torch.randn(NR, D, device=DEV, requires_grad=True)
+    c = torch.tensor([[0.7]], device=DEV, requires_grad=True) if code == 4 else None
+    h = torch.randint(0, NE, (B,), device=DEV)
+    r = torch.randint(0, NR, (B,), device=DEV)
+    hv, rv = E[h], R[r]
+    if code == 0:
+        q = algebra.compose_distmult(hv, rv)
+    elif code == 1:
+        q = algebra.compose_complex(hv, rv)
+    elif code == 2:
+        q = algebra.compose_quaternion(hv, algebra.quaternion_normalizer(rv))
+    elif code == 3:
+        q = algebra.compose_octonion(hv, rv, True)
+    else:
+        q, _ = algebra.compose_clifford(hv, rv, D // 2, 0, 1, 0, None, c)
+    assert K.lookup_vec_supported(code, D)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    Ed, Rd = E.detach().contiguous(), R.detach().contiguous()
+    cd = None if c is None else c.detach()
+    # rows sharded cyclically over W tables on the same device
+    rows = (NE + W - 1) // W
+    shards = [torch.zeros(rows, D, device=DEV) for _ in range(W)]
+    for k in range(W):
+        shards[k][: len(range(k, NE, W))] = Ed[k::W]
+    Q = [torch.zeros(B + 5, D, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    ids = [torch.zeros(3, B + 5, dtype=torch.int64, device=DEV) for _ in range(2)]
+    Qf = torch.zeros(B, D, device=DEV)
+    dp = torch.arange(B, device=DEV) * 7
+    K.lookup_compose_vec(code, norm, h, r, dp, K.pointer_table(shards, DEV), W, NE, NR, Rd, cd,
+                         K.pointer_table(Q, DEV), 2, 0, 5, Qf, K.pointer_table(ids, DEV), B + 5, B, D, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    assert torch.allclose(Qf, q.detach(), atol=1e-4, rtol=1e-4)
+    for k in range(2):   # both destinations, at the row offset
+        assert torch.allclose(Q[k][5:].float(), q.detach(), atol=3e-2, rtol=2e-2)
+        assert torch.equal(ids[k][0, 5:], h) and torch.equal(ids[k][1, 5:], r) and torch.equal(ids[k][2, 5:], dp)
+    dq = torch.randn(B, D, device=DEV)
+    q.backward(dq)
+    gR = torch.zeros_like(Rd)
+    gC = torch.zeros(1, 1, device=DEV) if c is not None else None
+    gshards = [torch.zeros(rows, D, device=DEV) for _ in range(W)]
+    half = [0.25 * dq, 0.75 * dq]   # two partial-gradient buffers summed by the kernel
+    for k in range(W):
+        K.compose_backward_owner(code, norm, h, r, shards[k], W, k, NE, NR, Rd, cd, None, K.pointer_table(half, DEV),
+                                 2, 0, gshards[k], gR, gC, B, D, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    gE = torch.zeros_like(Ed)
+    for k in range(W):
+        gE[k::W] = gshards[k][: len(range(k, NE, W))]
+    assert torch.allclose(gE, E.grad, atol=2e-3, rtol=1e-3)
+    assert torch.allclose(gR, R.grad, atol=2e-3, rtol=1e-3)
+    if c is not None:
+        assert torch.allclose(gC, c.grad, atol=1e-2, rtol=1e-3)
+    # a bad relation id is reported through the status word, and later launches return at once
+    r_bad = r.clone()
+    r_bad[7] = NR
+    K.lookup_compose_vec(code, norm, h, r_bad, None, K.pointer_table(shards, DEV), W, NE, NR, Rd, cd,
+                         K.pointer_table(Q, DEV), 1, 0, 0, None, None, 0, B, D, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5
+    before = gR.clone()
+    K.compose_backward_owner(code, norm, h, r, shards[0], W, 0, NE, NR, Rd, cd, dq, None, 0, 0, gshards[0], gR, gC, B,
+                             D, status)
+    torch.cuda.synchronize()
+    assert torch.equal(before, gR)
+
+
 @pytest.mark.parametrize("kind,name", [(0, "Adam"), (1, "AdamW"), (2, "SGD"), (3, "Adopt")])
 def test_optimizer_kernels_match_torch(kind, name):
     torch.manual_seed(3)

@@ -23,14 +23,14 @@ def test_sharded_protocol_equals_single_process_step(world):
     assert np.allclose(E1, E2, atol=1e-12) and np.allclose(R1, R2, atol=1e-12) and abs(l1 - l2) < 1e-12
 
 
-def test_two_steps_match_and_s0_matters():
+def test_two_steps_match_and_the_closing_barrier_orders_the_next_lookup():
     E, R, h, r, y = _problem(seed=1)
     Ea, Ra, _ = ps.reference_step(E, R, h, r, y, lr=0.3)
     Ea, Ra, la = ps.reference_step(Ea, Ra, h, r, y, lr=0.3)
     Eb, Rb, lb = ps.run_sharded_step(3, E, R, h, r, y, lr=0.3, steps=2)
     assert np.allclose(Ea, Eb, atol=1e-12) and np.allclose(Ra, Rb, atol=1e-12) and abs(la - lb) < 1e-12
     with pytest.raises(ps.ProtocolHazard):
-        ps.run_sharded_step(3, E, R, h, r, y, lr=0.3, steps=2, skip_barrier="S0")
+        ps.run_sharded_step(3, E, R, h, r, y, lr=0.3, steps=2, skip_barrier="S3")
 
 
 @pytest.mark.parametrize("name", ["S1", "S2", "S3"])
@@ -49,7 +49,7 @@ def test_absent_rank_ends_in_bounded_timeout():
 
 def test_dropped_signal_ends_in_bounded_timeout():
     E, R, h, r, y = _problem(seed=4)
-    drop = lambda sender, peer, count: sender == 0 and peer == 1 and count == 2   # noqa: E731 - S1's signal 0 -> 1
+    drop = lambda sender, peer, count: sender == 0 and peer == 1 and count == 2   # noqa: E731 - S2's signal 0 -> 1
     with pytest.raises(ps.PeerTimeout) as ei:
         ps.run_sharded_step(2, E, R, h, r, y, lr=0.1, drop=drop, poll_limit=300)
     assert ei.value.rank == 1 and ei.value.missing == [0]

@@ -24,7 +24,7 @@ DEV = torch.device("cuda:0")
 
 
 def _noalloc_symbol():
-    lib = ctypes.CDLL(_lib.LIB_PATH)
+    lib = _lib.lib()   # builds the library first when the tree is fresh; the symbol is then taken from that handle
     fn = lib.dice_positive_correction_noalloc
     p, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     fn.restype = ctypes.c_int
@@ -66,6 +66,15 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.allclose(dq, dq_ref, atol=1e-4, rtol=1e-3)
         assert torch.allclose(de, de_ref, atol=1e-4, rtol=1e-3)
         assert abs(loss.item() - loss_ref.item()) < 1e-3 * (1 + abs(loss_ref.item()))
+        # and against the dense fp32 statement of the same correction
+        Y = torch.zeros(B, NE, device=DEV)
+        for i in range(B):
+            d = int(dp[i])
+            Y[i, values[offsets[d]:offsets[d + 1]]] = 1.0
+        s = q.float() @ e.float().t()
+        assert abs(loss.item() + w * (Y * s).sum().item()) < 1e-3 * (1 + abs(loss.item()))
+        assert torch.allclose(dq, -w * scale * (Y @ e.float()), atol=1e-4, rtol=1e-3)
+        assert torch.allclose(de, -w * scale * (Y.t() @ q.float()), atol=1e-4, rtol=1e-3)
 
 
 def test_noalloc_rejects_oversized_batches():
