@@ -8,6 +8,7 @@ the call fails.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -59,10 +60,16 @@ def pointer_table(tensors: Sequence[torch.Tensor], device) -> torch.Tensor:
     return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=device)
 
 
+def pair_kernel_enabled() -> bool:
+    """The CTA-pair scoring kernel serves d = 256 unless ``DICE_B200_PAIR=0`` selects the one-CTA kernel."""
+    return os.environ.get("DICE_B200_PAIR", "1") != "0"
+
+
 def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: Optional[torch.Tensor],
                  status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0,
                  out_table: Optional[torch.Tensor] = None, out_block_rows: int = 0,
-                 mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0) -> None:
+                 mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0,
+                 trace: Optional[torch.Tensor] = None) -> None:
     """``out[x_rows, D] += scale · (sigmoid(X Yᵀ) − base) · Y`` and optionally
     ``loss_acc += Σ softplus(X Yᵀ) − base · X Yᵀ`` on the tcgen05 path.  ``x``/``y`` bf16, ``out`` fp32."""
     _req(x, torch.bfloat16, "x")
@@ -74,6 +81,13 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     assert y.shape[1] == D
     if with_loss:
         _req(loss_acc, torch.float64, "loss_acc")
+    if D == 256 and out_table is None and pair_kernel_enabled():
+        # CTA-pair kernel (tcgen05.mma.cta_group::2): num_ctas counts CTAs, two per pair
+        _call("dice_kvsall_pair", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
+              float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas) // 2 if num_ctas > 1 else int(num_ctas),
+              _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
+              others=(y, out, loss_acc, status, mask, trace))
+        return
     _call("dice_kvsall_fused", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
           float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas), _ptr(out_table),
           int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta),

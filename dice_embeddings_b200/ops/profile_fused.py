@@ -41,8 +41,11 @@ def main():
     pk = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.isfile(pk):
         peak, tag = float(json.load(open(pk))["bf16_tflops"]), "of measured"
-    roles = [("X=entities (loss)", lambda: K.kvsall_fused(x, y, out_x, loss, status, 0.0, 1.0, True, mask=mx, pos_delta=1.0)),
-             ("X=queries", lambda: K.kvsall_fused(y, x, out_y, None, status, 0.0, 1.0, False, mask=my, pos_delta=1.0))]
+    tr = {"buf": None}
+    roles = [("X=entities (loss)", lambda: K.kvsall_fused(x, y, out_x, loss, status, 0.0, 1.0, True, mask=mx, pos_delta=1.0,
+                                                         trace=tr["buf"])),
+             ("X=queries", lambda: K.kvsall_fused(y, x, out_y, None, status, 0.0, 1.0, False, mask=my, pos_delta=1.0,
+                                                  trace=tr["buf"]))]
     flop = 2 * 2.0 * a.nx * a.ny * a.d
     for name, fn in roles:
         for _ in range(a.warmup):
@@ -63,17 +66,23 @@ def main():
               f"{tf / peak:.2f} {tag} ({peak:.0f})")
         if a.trace:
             buf = torch.zeros(64, 8, dtype=torch.int64, device=dev)
-            K.kvsall_set_trace(buf)
+            pair = a.d == 256 and K.pair_kernel_enabled()
+            if pair:
+                tr["buf"] = buf
+            else:
+                K.kvsall_set_trace(buf)
             fn()
             torch.cuda.synchronize()
+            tr["buf"] = None
             K.kvsall_set_trace(None)
             t = buf.cpu()
             t0 = int(t[0, 0])
-            print("  tile | Y load issued | S gemm issued | 2nd gemm issued | epi sees S | epi wrote dS | out drained")
+            print("  tile | Y load issued | S gemm issued | 2nd gemm issued | epi sees S | epi wrote dS | out drained"
+                  " | 2nd-half load issued")
             for g in range(64):
                 if int(t[g, 0]) == 0:
                     break
-                print("  %4d | %s" % (g, " | ".join("%8d" % (int(v) - t0) if int(v) else "       -" for v in t[g, :6])))
+                print("  %4d | %s" % (g, " | ".join("%8d" % (int(v) - t0) if int(v) else "       -" for v in t[g, :7])))
     K.check_status(status)
 
 

@@ -41,6 +41,62 @@ def test_kvsall_fused_matches_reference(nx, ny, D, with_loss):
         assert abs(loss.item() - ref_loss.item()) / abs(ref_loss.item()) < 2e-3
 
 
+def _masked_reference(x, y, mask_bits, base, pos, scale):
+    """fp32 statement of the masked step: labels = pos where the bit is set, base elsewhere."""
+    s = x.float() @ y.float().t()
+    labels = torch.where(mask_bits, torch.full_like(s, pos), torch.full_like(s, base))
+    loss = (torch.nn.functional.softplus(s) - labels * s).double().sum()
+    ds = torch.sigmoid(s) - labels
+    return loss, scale * (ds @ y.float())
+
+
+def _pack_mask(bits):
+    """[nx, ny] bool -> int32 words, one bit per column, rows padded as the kernels expect."""
+    nx, ny = bits.shape
+    stride = K.mask_stride(ny)
+    padded = torch.zeros(nx, stride * 32, dtype=torch.bool, device=bits.device)
+    padded[:, :ny] = bits
+    w = padded.view(nx, stride, 32).to(torch.int64)
+    weights = (2 ** torch.arange(32, device=bits.device, dtype=torch.int64))
+    words = (w * weights).sum(-1)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words)
+    return words.to(torch.int32).contiguous()
+
+
+@pytest.mark.parametrize("nx,ny,ctas", [(256, 128, 0), (1000, 777, 0), (3000, 1500, 4), (2049, 4100, 6), (130, 260, 2),
+                                        (4096, 14541, 0)])
+@pytest.mark.parametrize("with_loss,masked", [(True, True), (False, True), (True, False)])
+def test_pair_kernel_matches_reference_and_one_cta_kernel(nx, ny, ctas, with_loss, masked, monkeypatch):
+    """The CTA-pair kernel (d = 256) against the fp32 reference, with label masks, ragged edges in both dimensions
+    and few CTA pairs, so that one pair walks many segments (x super-tiles); and against the one-CTA kernel."""
+    torch.manual_seed(nx * 7 + ny)
+    D = 256
+    x = (torch.randn(nx, D, device=DEV) * 0.25).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.25).to(torch.bfloat16)
+    base, pos, scale = 0.002, 0.9, 1.0 / 128
+    bits = torch.rand(nx, ny, device=DEV) < 0.03
+    mask = _pack_mask(bits) if masked else None
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    res = {}
+    for flavour in ("1", "0"):
+        monkeypatch.setenv("DICE_B200_PAIR", flavour)
+        out = torch.zeros(nx, D, device=DEV)
+        loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+        K.kvsall_fused(x, y, out, loss if with_loss else None, status, base, scale, with_loss, num_ctas=ctas,
+                       mask=mask, pos_delta=pos - base)
+        torch.cuda.synchronize()
+        K.check_status(status)
+        res[flavour] = (out, loss.item())
+    ref_loss, ref_out = _masked_reference(x, y, bits if masked else torch.zeros_like(bits), base, pos, scale)
+    denom = ref_out.abs().max().clamp_min(1e-6)
+    for flavour in ("1", "0"):
+        out, loss = res[flavour]
+        assert (out - ref_out).abs().max() / denom < 2e-2, flavour
+        if with_loss:
+            assert abs(loss - ref_loss.item()) / abs(ref_loss.item()) < 2e-3, flavour
+    assert (res["1"][0] - res["0"][0]).abs().max() / denom < 1e-2
+
+
 def test_kvsall_fused_accumulates_and_splits_work():
     """Two launches add up; any CTA count gives the same sums (work ranges are arbitrary cuts of the tile grid)."""
     torch.manual_seed(0)
