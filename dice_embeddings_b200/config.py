@@ -117,6 +117,90 @@ _SCORING_WITH_RECIPROCALS = ("AllvsAll", "1vsSample", "KvsAll", "1vsAll", "KvsSa
 _EVAL_CHOICES = (None, "None", "train", "val", "test", "train_val", "train_test", "val_test", "train_val_test")
 
 
+def is_sparql_endpoint_alive(sparql_endpoint: str = None) -> bool:
+    """One tiny COUNT query; ``False`` without an endpoint, an ``AssertionError`` when the endpoint does not answer
+    (reference ``dicee/sanity_checkers.py:7-15``)."""
+    if not sparql_endpoint:
+        return False
+    import requests
+    query = "SELECT (COUNT(*) as ?num_triples) WHERE {  ?s ?p ?o .} "
+    response = requests.post(sparql_endpoint, data={"query": query})
+    assert response.ok, f"SPARQL endpoint {sparql_endpoint} answered {getattr(response, 'status_code', '?')}"
+    return True
+
+
+def validate_knowledge_graph(args) -> None:
+    """Exactly one source of triples is kept, in the reference's order of precedence: a live SPARQL endpoint, then a
+    single file, then a dataset folder, which must exist and contain a ``train*`` file
+    (reference ``dicee/sanity_checkers.py:18-80``)."""
+    import glob
+    import os
+    endpoint = getattr(args, "sparql_endpoint", None)
+    single = getattr(args, "path_single_kg", None)
+    folder = getattr(args, "dataset_dir", None)
+    if is_sparql_endpoint_alive(endpoint):
+        args.dataset_dir = None
+        args.path_single_kg = None
+    elif single is not None:
+        if not os.path.isfile(single):
+            raise ValueError(f"--path_single_kg **{single}** does not lead to a file")
+        args.dataset_dir = None
+        args.sparql_endpoint = None
+    elif folder:
+        if not isinstance(folder, str):
+            raise AssertionError(f"The dataset_dir must be a string. ***{folder}***")
+        if not (os.path.isdir(folder) or os.path.isfile(folder)):
+            raise AssertionError(f"The dataset_dir does not lead to a directory ***{folder}***")
+        if not glob.glob(folder + "/train*"):
+            raise ValueError(f"---dataset_dir **{folder}** must lead to a **folder** containing at least train.txt**. "
+                             f"Use --path_single_kg **folder/dataset.format**, if you have a single file.")
+        args.sparql_endpoint = None
+        args.path_single_kg = None
+    else:
+        raise RuntimeError("One of the following arguments must be given: "
+                           f"--dataset_dir:{folder},\t--path_single_kg:{single},\t--sparql_endpoint:{endpoint}.")
+
+
+def sanity_check_callback_args(args) -> None:
+    """Trainer / callback combinations (reference ``dicee/sanity_checkers.py:92-116``): training on several GPUs needs
+    an explicit run folder (every rank must agree on it) and excludes the LR-schedule / TWA / SWAG callbacks."""
+    import os
+    gpu_count = 0
+    try:
+        import torch
+        gpu_count = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    except Exception:   # noqa: BLE001 - the checks must not depend on a working CUDA runtime
+        pass
+    launched = int(os.environ.get("WORLD_SIZE", "1")) > 1
+    multi = args.trainer in ("torchDDP", "Sharded") or (args.trainer == "PL" and gpu_count >= 2 and launched)
+    if multi and launched and getattr(args, "path_to_store_single_run", None) is None:
+        raise NotImplementedError("Path to store experiments must be provided for Multi-GPU training "
+                                  "(--path_to_store_single_run).")
+    if any([getattr(args, "swa", False), getattr(args, "swag", False), getattr(args, "ema", False),
+            getattr(args, "twa", False)]):
+        args.swa_start_epoch = getattr(args, "swa_start_epoch", None) or 1
+        assert args.swa_start_epoch > 0, "SWA Start Epoch must be greater than 0"
+
+
+def dataset_sanity_checking(train_set, num_entities: int, num_relations: int) -> None:
+    """Indexed triples must be a non-empty ``[n, 3]`` integer array whose ids fit the vocabularies
+    (reference ``dicee/read_preprocess_save_load_kg/util.py:515-545``)."""
+    import numpy as np
+    assert isinstance(train_set, np.ndarray), "the training set must be a numpy array"
+    assert train_set.ndim == 2 and train_set.shape[1] == 3, f"expected [n, 3] triples, got {train_set.shape}"
+    if train_set.shape[0] == 0:
+        raise AssertionError("Size of the training dataset must be greater than 0.")
+    max_e = int(max(train_set[:, 0].max(), train_set[:, 2].max()))
+    if max_e >= num_entities:
+        raise AssertionError(f"Entity Indexing Error:\nMax ID of a subject or object entity in train set: {max_e} "
+                             f"is not below num_entities: {num_entities}")
+    max_r = int(train_set[:, 1].max())
+    if max_r >= num_relations:
+        raise AssertionError(f"Relation Indexing Error:\nMax ID of a relation in train set: {max_r} "
+                             f"is not below num_relations: {num_relations}")
+    assert np.issubdtype(train_set.dtype, np.integer), "triples must be stored as integers"
+
+
 def sanity_check_args(args) -> None:
     """Range / combination checks (reference ``dicee/sanity_checkers.py:83-116``)."""
     assert args.embedding_dim > 0, "embedding_dim must be positive"
@@ -134,6 +218,9 @@ def sanity_check_args(args) -> None:
         raise ValueError("adaptive_lr (LR scheduling with snapshot ensembles) is not available with multi-GPU trainers")
     if multi_gpu_trainer and (getattr(args, "twa", False) or getattr(args, "swag", False)):
         raise ValueError("TWA/SWAG are not available with the TP/torchDDP trainers")
+    if getattr(args, "continual_learning", None) is None and not getattr(args, "_allow_no_source", False):
+        validate_knowledge_graph(args)
+    sanity_check_callback_args(args)
 
 
 def preprocess_args(args):

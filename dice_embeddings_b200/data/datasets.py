@@ -54,10 +54,12 @@ class BatchedDataset(torch.utils.data.Dataset):
         return tuple(b[0] for b in batch)
 
     def batches(self, batch_size: int, shuffle: bool = True, generator: Optional[torch.Generator] = None,
-                rank: int = 0, world_size: int = 1, drop_last: bool = False) -> Iterator[tuple]:
+                rank: int = 0, world_size: int = 1, drop_last: bool = False, pad_last: bool = False) -> Iterator[tuple]:
         """Yield batches; with ``world_size > 1`` every rank takes a strided slice of one
         shared permutation (same ``generator`` seed on every rank), padded by wrap-around so
-        that all ranks see the same number of batches."""
+        that all ranks see the same number of batches.  ``pad_last`` fills a short final batch up to ``batch_size``
+        by wrapping around to the start of the rank's slice (for engines that need full batches; no item is
+        dropped); ``drop_last`` skips it instead."""
         n = len(self)
         if shuffle:
             perm = torch.randperm(n, generator=generator)
@@ -72,8 +74,12 @@ class BatchedDataset(torch.utils.data.Dataset):
         perm = perm.to(self.device)
         for s in range(0, perm.numel(), batch_size):
             idx = perm[s:s + batch_size]
-            if drop_last and idx.numel() < batch_size:
-                break
+            if idx.numel() < batch_size:
+                if pad_last:
+                    reps = -(-(batch_size - idx.numel()) // max(perm.numel(), 1))
+                    idx = torch.cat([idx] + [perm] * reps)[:batch_size]
+                elif drop_last:
+                    break
             yield self.make_batch(idx, generator)
 
     def dense_batch(self, idx: torch.Tensor, generator: Optional[torch.Generator] = None):
@@ -85,9 +91,9 @@ class BatchedDataset(torch.utils.data.Dataset):
         finally:
             self.sparse_labels = sparse
 
-    def num_batches(self, batch_size: int, world_size: int = 1) -> int:
+    def num_batches(self, batch_size: int, world_size: int = 1, drop_last: bool = False) -> int:
         per = -(-len(self) // world_size)
-        return -(-per // batch_size)
+        return per // batch_size if drop_last else -(-per // batch_size)
 
 
 def multihot_from_csr(rows: torch.Tensor, cols: torch.Tensor, batch: int, width: int,

@@ -85,15 +85,60 @@ def _read_table(path: str, read_only_few=None, sample_triples_ratio=None, backen
     return df.reset_index(drop=True)
 
 
-def _read_sparql(endpoint: str) -> pd.DataFrame:
-    """Fetch all (s, p, o) with IRI objects from a triple store (reference ``util.py:244-352``)."""
+_SPARQL_HEADERS = {"Content-Type": "application/x-www-form-urlencoded", "Accept": "application/sparql-results+json"}
+
+
+def count_triples(endpoint: str) -> int:
+    """Total number of triples in the store behind ``endpoint`` (reference ``util.py:244-258``)."""
     import requests
-    query = "SELECT ?subject ?predicate ?object WHERE { ?subject ?predicate ?object . FILTER(isIRI(?object)) }"
-    resp = requests.post(endpoint, data={"query": query}, headers={"Accept": "application/sparql-results+json"})
+    resp = requests.post(endpoint, data={"query": "SELECT (COUNT(*) AS ?count) WHERE { ?s ?p ?o . }"},
+                         headers=_SPARQL_HEADERS)
     resp.raise_for_status()
-    rows = [(f"<{b['subject']['value']}>", f"<{b['predicate']['value']}>", f"<{b['object']['value']}>")
+    return int(resp.json()["results"]["bindings"][0]["count"]["value"])
+
+
+def _fetch_page(endpoint: str, offset: int, chunk_size: int) -> pd.DataFrame:
+    import requests
+    query = f"SELECT ?subject ?predicate ?object WHERE {{ ?subject ?predicate ?object . }} LIMIT {chunk_size} OFFSET {offset}"
+    resp = requests.post(endpoint, data={"query": query}, headers=_SPARQL_HEADERS)
+    if not resp.ok:   # the reference skips a failed page with a message; so does this reader
+        print(f"SPARQL page at offset {offset} failed: {getattr(resp, 'status_code', '?')}")
+        return pd.DataFrame(columns=["subject", "relation", "object"], dtype=str)
+    rows = [(b["subject"]["value"], b["predicate"]["value"], b["object"]["value"])
             for b in resp.json()["results"]["bindings"]]
     return pd.DataFrame(rows, columns=["subject", "relation", "object"], dtype=str)
+
+
+def _read_sparql(endpoint: str, chunk_size: int = 500_000, num_workers: Optional[int] = None,
+                 cache_dir: Optional[str] = None) -> pd.DataFrame:
+    """All (s, p, o) of a triple store, fetched in pages of ``chunk_size`` rows with ``LIMIT / OFFSET`` queries that
+    run concurrently (a thread per page in flight: the work is waiting for the endpoint), in offset order.
+
+    The reference counts the triples, deals the page offsets to one worker *process* per core, parks every page as a
+    parquet file and re-reads the folder (``dicee/read_preprocess_save_load_kg/util.py:244-328``).  ``cache_dir`` keeps
+    that behaviour: pages are written there as ``chunk_<offset>.parquet`` and an existing folder is read back instead
+    of querying again."""
+    from concurrent.futures import ThreadPoolExecutor
+    if cache_dir and os.path.isdir(cache_dir):
+        files = sorted(glob.glob(os.path.join(cache_dir, "chunk_*.parquet")),
+                       key=lambda f: int(os.path.basename(f)[6:-8]))
+        if files:
+            print(f"*** Found parquet files in `{cache_dir}`, reading from those; delete the folder to query again ***")
+            return pd.concat([pd.read_parquet(f) for f in files], ignore_index=True).astype(str)
+    total = count_triples(endpoint)
+    offsets = list(range(0, total, chunk_size))
+    workers = max(1, min(num_workers or (os.cpu_count() or 1), len(offsets) or 1))
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        pages = list(pool.map(lambda off: _fetch_page(endpoint, off, chunk_size), offsets))
+    if cache_dir:
+        os.makedirs(cache_dir, exist_ok=True)
+        for off, page in zip(offsets, pages):
+            if len(page):
+                page.to_parquet(os.path.join(cache_dir, f"chunk_{off}.parquet"), index=False)
+    pages = [pg for pg in pages if len(pg)]
+    if not pages:
+        return pd.DataFrame(columns=["subject", "relation", "object"], dtype=str)
+    return pd.concat(pages, ignore_index=True)
 
 
 def add_reciprocals(df: Optional[pd.DataFrame]) -> Optional[pd.DataFrame]:
@@ -240,6 +285,8 @@ class KG:
         self.train_set = index(self.raw_train_set)
         self.valid_set = index(self.raw_valid_set)
         self.test_set = index(self.raw_test_set)
+        from ..config import dataset_sanity_checking
+        dataset_sanity_checking(self.train_set, self.num_entities, self.num_relations)
 
     def _preprocess_bpe(self) -> None:
         """Token-id triples, optionally padded to a common length

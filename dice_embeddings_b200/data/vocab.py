@@ -169,3 +169,29 @@ def create_constraints(triples: np.ndarray):
     dom_c = {r: np.setdiff1d(ents, d).tolist() for r, d in dom.items()}
     rng_c = {r: np.setdiff1d(ents, d).tolist() for r, d in rng.items()}
     return dom_c, rng_c, {r: d.tolist() for r, d in dom.items()}, {r: d.tolist() for r, d in rng.items()}
+
+
+def create_constraints(triples: np.ndarray):
+    """Domain and range of every relation, and their complements.
+
+    Returns ``(domain_constraints_per_rel, range_constraints_per_rel, domain_per_rel, range_per_rel)`` keyed by relation
+    id: ``domain_per_rel[r]`` / ``range_per_rel[r]`` are the sets of entities seen as head / tail of ``r``; the
+    ``*_constraints`` entries list the entities of the graph that were *never* seen there, i.e. the candidates a
+    type-constrained ranking removes (reference ``dicee/static_preprocess_funcs.py:76-108``, which fills the same four
+    dictionaries with one Python loop over the triples; here: one sort per side)."""
+    assert isinstance(triples, np.ndarray) and triples.ndim == 2 and triples.shape[1] == 3
+    t = triples.astype(np.int64, copy=False)
+    entities = np.union1d(t[:, 0], t[:, 2])
+    domain_per_rel, range_per_rel = {}, {}
+    domain_constraints_per_rel, range_constraints_per_rel = {}, {}
+    order = np.argsort(t[:, 1], kind="stable")
+    rel_sorted = t[order, 1]
+    rels, starts = np.unique(rel_sorted, return_index=True)
+    ends = np.append(starts[1:], rel_sorted.shape[0])
+    for r, a, b in zip(rels.tolist(), starts.tolist(), ends.tolist()):
+        rows = order[a:b]
+        dom, rng = np.unique(t[rows, 0]), np.unique(t[rows, 2])
+        domain_per_rel[r], range_per_rel[r] = set(dom.tolist()), set(rng.tolist())
+        domain_constraints_per_rel[r] = np.setdiff1d(entities, dom, assume_unique=True).tolist()
+        range_constraints_per_rel[r] = np.setdiff1d(entities, rng, assume_unique=True).tolist()
+    return domain_constraints_per_rel, range_constraints_per_rel, domain_per_rel, range_per_rel

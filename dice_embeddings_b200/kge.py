@@ -425,10 +425,27 @@ class KGE:
             x = torch.hstack(self.index_triple(h, r, t))
         else:
             x = torch.hstack(self.index_triple([h], [r], [t]))
-        if self.apply_semantic_constraint:
-            raise NotImplementedError()
         out = self.model(x.to(self.model.device))
+        if self.apply_semantic_constraint:
+            # a triple whose head lies outside the relation's domain or whose tail lies outside its range (as seen in
+            # the training graph) cannot hold: logit -inf, probability 0.  The reference names the switch but raises
+            # NotImplementedError here (dicee/knowledge_graph_embeddings.py:642-643).
+            ok = self._semantic_mask(x)
+            out = torch.where(ok.to(out.device), out, torch.full_like(out, float("-inf")))
         return out if logits else torch.sigmoid(out)
+
+    def semantic_constraints(self):
+        """``(domain_constraints_per_rel, range_constraints_per_rel, domain_per_rel, range_per_rel)`` of the stored
+        training triples, computed once (reference ``dicee/static_preprocess_funcs.py:76-108``)."""
+        if getattr(self, "_constraints", None) is None:
+            from .data.vocab import create_constraints
+            self._constraints = create_constraints(np.asarray(self.train_set))
+        return self._constraints
+
+    def _semantic_mask(self, x: torch.Tensor) -> torch.Tensor:
+        _, _, dom, rng = self.semantic_constraints()
+        rows = x.view(-1, 3).tolist()
+        return torch.tensor([h in dom.get(r, ()) and t in rng.get(r, ()) for h, r, t in rows], dtype=torch.bool)
 
     # ------------------------------------------------------------------ multi-hop queries
     @staticmethod

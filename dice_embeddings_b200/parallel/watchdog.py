@@ -54,7 +54,11 @@ class Heartbeat:
     # ------------------------------------------------------------------ checking
     def _read(self, peer: int) -> int:
         try:
-            raw = self.store.get(f"hb/{peer}")
+            key = f"hb/{peer}"
+            check = getattr(self.store, "check", None)   # c10d stores block in get() until the key exists
+            if check is not None and not check([key]):
+                return 0
+            raw = self.store.get(key)
             return int(raw.decode() or 0) if raw else 0
         except Exception:
             return 0

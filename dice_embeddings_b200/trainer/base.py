@@ -44,12 +44,14 @@ class BatchLoader:
     instead of collating Python items in worker processes."""
 
     def __init__(self, dataset, batch_size: int, shuffle: bool = True, seed: int = 0, rank: int = 0,
-                 world_size: int = 1, drop_last: bool = False):
+                 world_size: int = 1, drop_last: bool = False, pad_last: bool = False, num_workers: int = 0):
         self.dataset = dataset
         self.batch_size = int(batch_size)
         self.shuffle = shuffle
         self.rank, self.world_size = rank, world_size
         self.drop_last = drop_last
+        self.pad_last = pad_last          # full final batch by wrap-around (engines with a fixed batch size)
+        self.num_workers = max(int(num_workers or 0), 0)   # ``--num_core``: batches are built ahead by a thread
         self.generator = torch.Generator()
         self.seed = int(seed)
         self.epoch = 0
@@ -59,14 +61,58 @@ class BatchLoader:
         self.epoch = int(epoch)
 
     def __len__(self) -> int:
-        return self.dataset.num_batches(self.batch_size, self.world_size)
+        return self.dataset.num_batches(self.batch_size, self.world_size, self.drop_last and not self.pad_last)
+
+    def _batches(self) -> Iterator[tuple]:
+        return self.dataset.batches(self.batch_size, self.shuffle, self.generator, self.rank, self.world_size,
+                                    self.drop_last, self.pad_last)
 
     def __iter__(self) -> Iterator[tuple]:
         # same permutation on every rank: seed depends on (seed, epoch) only
         self.generator.manual_seed(self.seed * 1_000_003 + self.epoch)
-        yield from self.dataset.batches(self.batch_size, self.shuffle, self.generator, self.rank, self.world_size,
-                                        self.drop_last)
+        if self.num_workers > 0:
+            yield from _prefetch(self._batches(), depth=2 * self.num_workers)
+        else:
+            yield from self._batches()
         self.epoch += 1
+
+
+def _prefetch(it: Iterator[tuple], depth: int) -> Iterator[tuple]:
+    """Run ``it`` in a background thread, ``depth`` batches ahead of the consumer (the role of the reference's
+    DataLoader workers, ``dicee/trainer/dice_trainer.py:262-264``; batch construction here is tensor code that
+    releases the interpreter lock, so a thread is enough).  Batches arrive in the same order as without it."""
+    import queue
+    import threading
+    q: "queue.Queue" = queue.Queue(maxsize=max(depth, 1))
+    end, stop = object(), threading.Event()
+
+    def work():
+        try:
+            for item in it:
+                while not stop.is_set():
+                    try:
+                        q.put(item, timeout=0.1)
+                        break
+                    except queue.Full:
+                        continue
+                if stop.is_set():
+                    return
+            q.put(end)
+        except BaseException as exc:   # noqa: BLE001 - re-raised in the consumer
+            q.put(exc)
+
+    t = threading.Thread(target=work, daemon=True)
+    t.start()
+    try:
+        while True:
+            item = q.get()
+            if item is end:
+                return
+            if isinstance(item, BaseException):
+                raise item
+            yield item
+    finally:
+        stop.set()
 
 
 class AbstractTrainer:

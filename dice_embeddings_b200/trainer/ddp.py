@@ -10,8 +10,11 @@ table.  Here the name selects, in this order:
    gradients are averaged with one flat all-reduce per step.  This path also runs on CPU ranks (Gloo), which is
    how it is tested without GPUs.
 
-Callbacks fire on global rank 0 at epoch end, as in the reference (``:188-191``); the process group is left alive
-for the executor to tear down.
+Callbacks fire on global rank 0 at epoch end, as in the reference (``:188-191``); every rank then meets in a host-side
+barrier, so that long callbacks (evaluation, checkpoints, weight averaging) never eat into the bounded waits of the
+device-side barriers of the next step.  Ranks publish heartbeats through the process group's store and check their
+peers between steps; a silent peer raises :class:`~dice_embeddings_b200.parallel.watchdog.RankFailure` before the next
+launch instead of a device barrier time-out.  The process group is left alive for the executor to tear down.
 """
 from __future__ import annotations
 
@@ -52,7 +55,7 @@ class TorchDDPTrainer(AbstractTrainer):
                     raise RuntimeError("kernel_backend=cuda requested but the model / scoring technique is not covered")
                 return None
             from ..parallel.sharded_engine import ShardedKvsAllEngine
-            return ShardedKvsAllEngine(model, loader.dataset, batch_size=self.attributes.batch_size, lr=self.attributes.lr,
+            return ShardedKvsAllEngine(model, loader.dataset, batch_size=loader.batch_size, lr=self.attributes.lr,
                                        weight_decay=getattr(self.attributes, "weight_decay", 0.0) or 0.0,
                                        device=self.device, comm=getattr(self.attributes, "comm", "p2p"))
         except ImportError:
@@ -102,9 +105,18 @@ class TorchDDPTrainer(AbstractTrainer):
         if self.world_size > 1:  # identical start on every rank
             for p in model.parameters():
                 dist.broadcast(p.data, src=0)
+        if isinstance(loader, BatchLoader) and self.world_size > 1:
+            # engines with a fixed batch size: never more than a rank's share of the data (the same number on every
+            # rank), and the short final batch is filled by wrap-around instead of being dropped
+            per_rank = -(-len(loader.dataset) // self.world_size)
+            if per_rank < loader.batch_size:
+                if self.is_global_zero:
+                    print(f"batch_size {loader.batch_size} exceeds the {per_rank} data points per rank: using {per_rank}")
+                loader.batch_size = per_rank
         self.engine = self._maybe_sharded_engine(model, loader)
         if self.engine is not None:
-            loader.drop_last = True
+            loader.drop_last, loader.pad_last = False, True
+            assert len(loader) >= 1, "no training step per epoch: the dataset is empty"
         self.peer_optimizer = None
         if self.engine is not None:
             self.optimizer = self.engine.optimizer_view()
@@ -113,8 +125,10 @@ class TorchDDPTrainer(AbstractTrainer):
             self.optimizer = self.peer_optimizer if self.peer_optimizer is not None else model.configure_optimizers()
         params = [p for p in model.parameters() if p.requires_grad]
         use_bf16 = getattr(self.attributes, "compute_dtype", "fp32") == "bf16" and self.device.type == "cuda"
+        heartbeat = self._start_heartbeat()
         if self.is_global_zero:
             self.on_fit_start(self, model)
+        self._host_barrier()
         for epoch in range(self.attributes.num_epochs):
             self.current_epoch = epoch
             if hasattr(loader, "set_epoch"):
@@ -124,6 +138,8 @@ class TorchDDPTrainer(AbstractTrainer):
             nb = 0
             t0 = time.time()
             for i, batch in enumerate(loader):
+                if heartbeat is not None:
+                    heartbeat.raise_if_failed()   # a peer went silent: stop before the next launch
                 batch = tuple(b.to(self.device, non_blocking=True) if isinstance(b, torch.Tensor) else b for b in batch)
                 if self.engine is not None:
                     loss = self.engine.step(batch)
@@ -149,5 +165,29 @@ class TorchDDPTrainer(AbstractTrainer):
             if self.is_global_zero:
                 print(f"Epoch:{epoch + 1} | Loss:{epoch_loss:.8f} | Runtime:{(time.time() - t0) / 60:.3f}mins")
                 self.on_train_epoch_end(self, model)
+            self._host_barrier()      # the other ranks wait here, on the host, while rank 0 runs its callbacks
         if self.is_global_zero:
             self.on_fit_end(self, model)
+        self._host_barrier()
+        if heartbeat is not None:
+            heartbeat.stop()
+
+    def _host_barrier(self) -> None:
+        if self.world_size > 1 and dist.is_initialized():
+            dist.barrier()
+
+    def _start_heartbeat(self):
+        """Background heartbeats through the default process group's store (``None`` for a single rank or when the
+        store cannot be reached).  ``DICE_B200_HEARTBEAT_TIMEOUT`` (seconds, default 120; 0 switches it off) bounds how
+        long a peer may stay silent; rank-0 callbacks may run longer than that only while the others sit in the host
+        barrier, where heartbeats keep flowing from the background thread."""
+        timeout = float(os.environ.get("DICE_B200_HEARTBEAT_TIMEOUT", "120"))
+        if self.world_size < 2 or timeout <= 0 or not dist.is_initialized():
+            return None
+        try:
+            from torch.distributed.distributed_c10d import _get_default_store
+            from ..parallel.watchdog import Heartbeat
+            return Heartbeat(_get_default_store(), self.global_rank, self.world_size, timeout=timeout,
+                             interval=min(1.0, timeout / 4)).start()
+        except Exception:   # noqa: BLE001 - the store is an implementation detail of the backend
+            return None

@@ -119,7 +119,8 @@ class DICE_Trainer:
         rank = getattr(self.trainer, "global_rank", 0)
         world = getattr(self.trainer, "world_size", 1)
         return BatchLoader(dataset, batch_size=self.args.batch_size, shuffle=True,
-                           seed=getattr(self.args, "random_seed", 0) or 0, rank=rank, world_size=world)
+                           seed=getattr(self.args, "random_seed", 0) or 0, rank=rank, world_size=world,
+                           num_workers=getattr(self.args, "num_core", 0) or 0)
 
     def init_dataset(self):
         ds = self.trainer.dataset

@@ -31,7 +31,7 @@ class ShardedTrainer(TorchDDPTrainer):
             if st == "NegSample" and hasattr(ds, "defer_sampling"):
                 ds.defer_sampling = True   # the engine draws the corruptions on the device
             a = self.attributes
-            return ShardedSampledEngine(model, st, batch_size=a.batch_size, lr=a.lr, neg_ratio=getattr(a, "neg_ratio", 0) or 0,
+            return ShardedSampledEngine(model, st, batch_size=loader.batch_size, lr=a.lr, neg_ratio=getattr(a, "neg_ratio", 0) or 0,
                                         label_smoothing=getattr(a, "label_smoothing_rate", 0.0) or 0.0,
                                         weight_decay=getattr(a, "weight_decay", 0.0) or 0.0, device=self.device,
                                         seed=getattr(a, "random_seed", 0) or 0)
