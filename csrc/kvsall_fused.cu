@@ -333,15 +333,15 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       bool ok = true;
       while (!c2.done() && ok && !*s_abort) {
         bool progressed = false;
-        if (g2 < g1 && mbar_try_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
-            (!c2.first() || mbar_try_wait(dx_empty, (c2.seg & 1) ^ 1))) {
+        if (g2 < g1 && mbar_test_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
+            (!c2.first() || mbar_test_wait(dx_empty, (c2.seg & 1) ^ 1))) {
           issue_g2(g2, c2.first(), c2.last());
           ++g2;
           c2.advance();
           progressed = true;
         }
-        if (!progressed && !c1.done() && g1 - g2 < 2 && (!c1.first() || mbar_try_wait(x_full, c1.seg & 1)) &&
-            mbar_try_wait(y_full + (g1 % C::NSTAGE) * 4, (g1 / C::NSTAGE) & 1)) {
+        if (!progressed && !c1.done() && g1 - g2 < 2 && (!c1.first() || mbar_test_wait(x_full, c1.seg & 1)) &&
+            mbar_test_wait(y_full + (g1 % C::NSTAGE) * 4, (g1 / C::NSTAGE) & 1)) {
           if (!issue_g1(g1)) { ok = false; break; }
           if (c1.last()) tc_commit(x_empty);  // last S GEMM of the segment: the X buffer may be refilled
           ++g1;

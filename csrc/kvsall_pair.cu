@@ -28,7 +28,6 @@
 #include "tma_host.cuh"
 
 #include <stdio.h>
-#include <stdlib.h>
 
 namespace dice {
 namespace pair {
@@ -58,7 +57,8 @@ struct Params {
   const uint32_t* mask;
   int mask_stride;
   float pos_delta;
-  int debug;            // experiments only
+  int loss_share;       // -1: every tile adds its loss terms; 0 / 1: only tiles whose 256 x 256 block of the (x, y)
+                        // plane has that parity do (the other launch of the step takes the rest)
   long long* trace;     // optional [64 tiles][8] clock64 stamps written by the leader CTA of pair 0, else null
 };
 
@@ -81,6 +81,20 @@ template <bool LOSS, bool MASK, bool FULL>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t mword, float base, float label_pos,
                                                int y_valid, uint32_t (&packed)[16], float& loss) {
   constexpr float LOG2E = 1.4426950408889634f;
+  if constexpr (!LOSS && !MASK) {
+    // uniform label: sigmoid(s) - base = 0.5 tanh(s / 2) + (0.5 - base), three instructions per logit
+    const float c0 = 0.5f - base;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float d0 = fmaf(tanhf_fast(0.5f * __uint_as_float(r[i])), 0.5f, c0);
+      float d1 = fmaf(tanhf_fast(0.5f * __uint_as_float(r[i + 1])), 0.5f, c0);
+      if (!FULL && i >= y_valid) d0 = 0.f;
+      if (!FULL && i + 1 >= y_valid) d1 = 0.f;
+      __nv_bfloat162 v = __floats2bfloat162_rn(d0, d1);
+      packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float ds2[2];
@@ -187,38 +201,81 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
 
   if (warp == 0) {
     // =========================================================================== TMA producer (one per CTA)
+    // Two independent load streams (row halves + X tiles for the first GEMM, column halves for the second) are
+    // issued by one thread in whichever order their buffers become free: a stream never waits behind the other.
     if (lane == 0) {
       const uint32_t xf = map_to_cta(smem_u32(x_full), 0);
-      uint32_t rcount = 0, seg = 0;
-      bool ok = true;
-      for (long long w = w_begin; w < w_end && ok && !*s_abort;) {
-        int x, y0, run;
+      // cursor of the row-half stream (X tile once per segment, then one row half per tile)
+      long long wr = w_begin;
+      int nr = 0, tr = 0, xr = 0, yr0 = 0;
+      uint32_t rcount = 0, segr = 0;
+      bool x_issued = false;
+      // cursor of the column-half stream
+      long long wc = w_begin;
+      int nc = 0, tcur = 0, xc = 0, yc0 = 0;
+      uint32_t ccount = 0;
+      auto locate = [&](long long w, int& x, int& y0, int& n) {
+        int run;
         p.map.locate(w, x, y0, run);
-        const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
-        if (!mbar_wait_bounded(x_empty, (seg & 1) ^ 1, s_abort)) { ok = false; break; }
-        if (leader) mbar_arrive_expect_tx(x_full, 2 * X_BYTES);
-        const int x_row = x * 2 * ROWS_CTA + static_cast<int>(cta) * ROWS_CTA;
-        for (int s = 0; s < 4; ++s) tma_load_2d_pair(sX + s * XSLAB, &tmap_x, s * 64, x_row, xf);
-        for (int t = 0; t < n; ++t, ++rcount) {
-          const uint32_t rs = rcount % NR, cs = rcount % NC;
-          const int y_row = (y0 + t) * BLOCK_Y;
-          if (!mbar_wait_bounded(r_empty + rs, ((rcount / NR) & 1) ^ 1, s_abort)) { ok = false; break; }
-          stamp(rcount, 0);
-          if (leader) mbar_arrive_expect_tx(r_full + rs, 2 * R_BYTES);
-          const uint32_t rf = map_to_cta(smem_u32(r_full + rs), 0);
-          uint8_t* rdst = sR + rs * R_BYTES;
-          for (int s = 0; s < 4; ++s)   // rows [64 cta, 64 cta + 64) of the tile, all four K slabs
-            tma_load_2d_pair(rdst + s * RSLAB, &tmap_yr, s * 64, y_row + static_cast<int>(cta) * 64, rf);
-          if (!mbar_wait_bounded(c_empty + cs, ((rcount / NC) & 1) ^ 1, s_abort)) { ok = false; break; }
-          stamp(rcount, 6);
-          if (leader) mbar_arrive_expect_tx(c_full + cs, 2 * C_BYTES);
-          const uint32_t cf = map_to_cta(smem_u32(c_full + cs), 0);
-          uint8_t* cdst = sC + cs * C_BYTES;
-          for (int s = 0; s < 2; ++s)   // all 128 rows, columns [128 cta, 128 cta + 128)
-            tma_load_2d_pair(cdst + s * CSLAB, &tmap_yc, static_cast<int>(cta) * 128 + s * 64, y_row, cf);
+        n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
+      };
+      if (wr < w_end) locate(wr, xr, yr0, nr);
+      if (wc < w_end) locate(wc, xc, yc0, nc);
+      uint32_t idle = 0;
+      bool ok = true;
+      while ((wr < w_end || wc < w_end) && ok && !*s_abort) {
+        bool progressed = false;
+        if (wr < w_end) {
+          if (!x_issued && mbar_test_wait(x_empty, (segr & 1) ^ 1)) {
+            if (leader) mbar_arrive_expect_tx(x_full, 2 * X_BYTES);
+            const int x_row = xr * 2 * ROWS_CTA + static_cast<int>(cta) * ROWS_CTA;
+            for (int s = 0; s < 4; ++s) tma_load_2d_pair(sX + s * XSLAB, &tmap_x, s * 64, x_row, xf);
+            x_issued = true;
+            progressed = true;
+          }
+          if (tr < nr && mbar_test_wait(r_empty + (rcount % NR), ((rcount / NR) & 1) ^ 1)) {
+            const uint32_t rs = rcount % NR;
+            stamp(rcount, 0);
+            if (leader) mbar_arrive_expect_tx(r_full + rs, 2 * R_BYTES);
+            const uint32_t rf = map_to_cta(smem_u32(r_full + rs), 0);
+            uint8_t* rdst = sR + rs * R_BYTES;
+            const int y_row = (yr0 + tr) * BLOCK_Y + static_cast<int>(cta) * 64;
+            for (int s = 0; s < 4; ++s)   // rows [64 cta, 64 cta + 64) of the tile, all four K slabs
+              tma_load_2d_pair(rdst + s * RSLAB, &tmap_yr, s * 64, y_row, rf);
+            ++rcount;
+            ++tr;
+            progressed = true;
+          }
+          if (tr == nr && x_issued) {   // segment complete on the load side: move on
+            wr += nr;
+            ++segr;
+            tr = 0;
+            x_issued = false;
+            if (wr < w_end) locate(wr, xr, yr0, nr);
+          }
         }
-        w += n;
-        ++seg;
+        if (wc < w_end) {
+          const uint32_t cs = ccount % NC;
+          if (mbar_test_wait(c_empty + cs, ((ccount / NC) & 1) ^ 1)) {
+            stamp(ccount, 6);
+            if (leader) mbar_arrive_expect_tx(c_full + cs, 2 * C_BYTES);
+            const uint32_t cf = map_to_cta(smem_u32(c_full + cs), 0);
+            uint8_t* cdst = sC + cs * C_BYTES;
+            const int y_row = (yc0 + tcur) * BLOCK_Y;
+            for (int s = 0; s < 2; ++s)   // all 128 rows, columns [128 cta, 128 cta + 128)
+              tma_load_2d_pair(cdst + s * CSLAB, &tmap_yc, static_cast<int>(cta) * 128 + s * 64, y_row, cf);
+            ++ccount;
+            progressed = true;
+            if (++tcur == nc) { wc += nc; tcur = 0; if (wc < w_end) locate(wc, xc, yc0, nc); }
+          }
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > DICE_WAIT_LIMIT) {
+          ok = false;
+        } else if (idle > 64) {
+          __nanosleep(32);
+        }
       }
       if (!ok) fail(ST_TIMEOUT_PRODUCER);
       if (*s_abort) {
@@ -242,7 +299,6 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         tc_fence_after();
         const uint64_t rd = rdesc + rs * (R_BYTES >> 4);
         const uint32_t d_tmem = tmem_s0 + (gi & 1) * BLOCK_Y;
-        if (!(p.debug & 4)) {
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
 #pragma unroll
@@ -251,7 +307,6 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             const uint32_t b_off = sl * (RSLAB >> 4) + kk * 2;
             mma_ss_pair(d_tmem, xdesc + a_off, rd + b_off, IDESC_G1, (sl | kk) ? 1u : 0u);
           }
-        }
         }
         tc_commit_pair(s_full + (gi & 1), 3);
         tc_commit_pair(r_empty + rs, 3);       // the row halves of this tile may be refilled in both CTAs
@@ -262,12 +317,10 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         tc_fence_after();
         const uint64_t cd = cdesc + cs * (C_BYTES >> 4);
         const uint32_t a_base = tmem_s0 + (gi & 1) * BLOCK_Y;
-        if (!(p.debug & 8)) {
 #pragma unroll
         for (int k = 0; k < BLOCK_Y / 16; ++k) {
           const uint32_t a_tmem = a_base + 32 * (k >> 1) + 8 * (k & 1);
           mma_ts_pair(tmem_out, a_tmem, cd + k * 128, IDESC_G2, (k == 0 && first) ? 0u : 1u);
-        }
         }
         tc_commit_pair(c_empty + cs, 3);
         if (last) tc_commit_pair(dx_full, 3);
@@ -287,16 +340,16 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       bool ok = true;
       while (w2 < w_end && ok && !*s_abort) {
         bool progressed = false;
-        if (g2 < g1 && mbar_try_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
-            mbar_try_wait(c_full + (g2 % NC), (g2 / NC) & 1) &&
-            (t2 != 0 || mbar_try_wait(dx_empty, (seg2 & 1) ^ 1))) {
+        if (g2 < g1 && mbar_test_wait(ds_full + (g2 & 1), (g2 >> 1) & 1) &&
+            mbar_test_wait(c_full + (g2 % NC), (g2 / NC) & 1) &&
+            (t2 != 0 || mbar_test_wait(dx_empty, (seg2 & 1) ^ 1))) {
           issue_g2(g2, t2 == 0, t2 + 1 == n2);
           ++g2;
           if (++t2 == n2) { w2 += n2; ++seg2; t2 = 0; if (w2 < w_end) load(w2, n2); }
           progressed = true;
         }
-        if (!progressed && w1 < w_end && g1 - g2 < 2 && (t1 != 0 || mbar_try_wait(x_full, seg1 & 1)) &&
-            mbar_try_wait(r_full + (g1 % NR), (g1 / NR) & 1)) {
+        if (!progressed && w1 < w_end && g1 - g2 < 2 && (t1 != 0 || mbar_test_wait(x_full, seg1 & 1)) &&
+            mbar_test_wait(r_full + (g1 % NR), (g1 / NR) & 1)) {
           issue_g1(g1);
           if (t1 + 1 == n1) tc_commit_pair(x_empty, 3);   // last S GEMM of the segment: X may be refilled
           ++g1;
@@ -354,23 +407,19 @@ kvsall_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const uint32_t s_addr = tmem_s0 + b * BLOCK_Y + lane_sel + cg * 32;
         uint32_t r[32];
         uint32_t packed[16];
-        if (p.debug & 2) {
-          // nothing: no TMEM traffic, no math
-        } else if (p.debug & 1) {
-          tmem_ld32(s_addr, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) packed[i] = r[2 * i] & 0x3f803f80u;
-          tmem_st16(s_addr, packed);
-          tc_wait_st();
-        } else {
         tmem_ld32(s_addr, r);
         tc_wait_ld();
-        if (y_valid >= 32) epilogue_chunk<LOSS, MASK, true>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
-        else epilogue_chunk<LOSS, MASK, false>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+        bool with_loss = LOSS;
+        if constexpr (LOSS) with_loss = p.loss_share < 0 || ((x + ((y0 + t) >> 1)) & 1) == p.loss_share;
+        if (with_loss) {
+          if (y_valid >= 32) epilogue_chunk<LOSS, MASK, true>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+          else epilogue_chunk<LOSS, MASK, false>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+        } else {
+          if (y_valid >= 32) epilogue_chunk<false, MASK, true>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+          else epilogue_chunk<false, MASK, false>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+        }
         tmem_st16(s_addr, packed);
         tc_wait_st();
-        }
         tc_fence_before();
         __syncwarp();
         if (warp == 2 && lane == 0) stamp(g, 4);
@@ -453,12 +502,14 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& tyr, const CUtensorM
 }  // namespace dice
 
 // CTA-pair variant of dice_kvsall_fused for D = 256 (returns -6 for other widths: use dice_kvsall_fused there).
-// num_pairs <= 0 selects one pair per two SMs.  trace (optional, device int64 [64][8]): per-tile clock stamps of the
+// num_pairs <= 0 selects one pair per two SMs.  loss_share (with_loss only): -1 = the loss of every (x, y) pair is
+// added; 0 or 1 = only of the pairs whose 256 x 256 block has that parity, so that the two launches of a training
+// step (roles of x and y swapped) can each take half of the loss arithmetic.  trace (optional, device int64 [64][8]): per-tile clock stamps of the
 // leader CTA of pair 0 for pipeline diagnostics.
 extern "C" int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss,
                                 float base, float scale, int with_loss, int* status, int num_pairs,
-                                const unsigned int* mask, int mask_stride, float pos_delta, long long* trace,
-                                void* stream) {
+                                const unsigned int* mask, int mask_stride, float pos_delta, int loss_share,
+                                long long* trace, void* stream) {
   using namespace dice;
   using namespace dice::pair;
   if (x_rows <= 0 || y_rows <= 0) return 0;
@@ -489,7 +540,7 @@ extern "C" int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_
   p.mask_stride = mask_stride;
   p.pos_delta = pos_delta;
   p.trace = trace;
-  p.debug = getenv("DICE_B200_PAIR_DEBUG") ? atoi(getenv("DICE_B200_PAIR_DEBUG")) : 0;
+  p.loss_share = loss_share;
   if (num_pairs <= 0) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);

@@ -54,6 +54,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe.  try_wait may suspend the thread for a hardware-defined time when the phase is not complete;
+// a thread that polls several barriers and acts on whichever is ready first must use this one instead.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false after `limit` unsuccessful probes or as soon as *abort becomes non-zero;
 // the caller then records a status code and unwinds.  Nothing in these kernels spins forever.
 #ifndef DICE_WAIT_LIMIT

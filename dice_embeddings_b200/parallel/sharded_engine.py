@@ -177,16 +177,20 @@ class ShardedKvsAllEngine:
         self.r = torch.zeros(B, dtype=torch.int64, device=dev)
         self.dp = torch.zeros(B, dtype=torch.int64, device=dev)
         self.x_in = torch.zeros(B, 2, dtype=torch.int64, device=dev)
-        # labels: bit masks of the positives in both orientations while they fit a modest budget, else the sparse
-        # correction kernels driven by the CSR (tables of millions of rows)
+        # labels: "mask" (default while the masks fit 1 GiB) feeds bit masks of the positives to the scoring epilogues;
+        # "sparse" applies the known tails by a correction kernel driven by the owner-partitioned CSR, beside the dense
+        # scoring launches (tables of millions of rows)
         mask_bytes = 2.0 * W * B * self.rows_pad / 8
-        self.label_mode = label_mode or ("mask" if mask_bytes <= (1 << 30) else "sparse")
+        self.label_mode = label_mode or os.environ.get("DICE_B200_LABELS") or \
+            ("mask" if mask_bytes <= (1 << 30) else "sparse")
         assert self.label_mode in ("mask", "sparse")
+        assert self.label_mode == "sparse" or mask_bytes <= (1 << 30), "label masks would exceed 1 GiB"
+        if comm == "nccl":
+            self.label_mode = "mask"   # the comparison pipeline keeps the mask flavour
         if self.label_mode == "mask":
             self.mask_q = torch.zeros(W * B, K.mask_stride(self.rows_pad), dtype=torch.int32, device=dev)
             self.mask_e = torch.zeros(self.rows_pad, K.mask_stride(W * B), dtype=torch.int32, device=dev)
         else:
-            assert comm == "p2p", "the sparse label path is implemented for the peer-memory flavour"
             self.mask_q = self.mask_e = None
         self.first = torch.zeros(W * B + 1, dtype=torch.int32, device=dev)
         if comm == "nccl":
@@ -262,18 +266,23 @@ class ShardedKvsAllEngine:
                                 status=self.status)
             self._mark("masks")
         e_loc = self.E_bf16[: self.rows]
+        if not masks:
+            # label term of the positives whose tail lives in this shard (loss, dE rows here, partial dQ rows here; all
+            # added atomically) on a parallel branch beside the two dense scoring launches
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                K.positive_scan(self.dp_all, self.offsets_loc, n, self.first)
+                K.positive_correction(self.dp_all, self.offsets_loc, self.values_loc, self.first, self.Q, self.E_bf16,
+                                      self.dQ, self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, 1, 0)
+        # both launches add half of the loss terms each (the epilogue with loss costs several times the one without)
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
-                       mask=self.mask_e, pos_delta=self.pos_weight)
+                       mask=self.mask_e, pos_delta=self.pos_weight, loss_share=0)
         self._mark("fused_E")
-        K.kvsall_fused(self.Q, e_loc, self.dQ, None, self.status, self.base, scale, False,
-                       mask=self.mask_q, pos_delta=self.pos_weight)
+        K.kvsall_fused(self.Q, e_loc, self.dQ, self.loss_acc[:1], self.status, self.base, scale, True,
+                       mask=self.mask_q, pos_delta=self.pos_weight, loss_share=1)
         self._mark("fused_Q")
         if not masks:
-            # label term of the positives whose tail lives in this shard: loss, dE rows here, partial dQ rows here
-            K.positive_scan(self.dp_all, self.offsets_loc, n, self.first)
-            K.positive_correction(self.dp_all, self.offsets_loc, self.values_loc, self.first, self.Q, self.E_bf16,
-                                  self.dQ, self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, 1, 0)
-            self._mark("positives")
+            main.wait_stream(self._side)
         self._barrier()                                   # S2: every rank's partial dQ is complete
         self._mark("S2")
         # owner-side backward: dQ rows summed over the ranks inside the switch (or by peer loads), row gradients local

@@ -48,7 +48,7 @@ def main():
         ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(dev)
         model = make()
         eng = ShardedKvsAllEngine(model, ds, batch_size=B, lr=lr, device=dev, comm=comm.split("-")[0],
-                                  label_mode="sparse" if comm.endswith("sparse") else "mask",
+                                  label_mode="sparse" if comm.endswith("sparse") else None,
                                   multimem=False if comm.endswith("unicast") else None)
         if comm == "p2p":
             mm_used = eng.multimem
@@ -85,7 +85,7 @@ def main():
     d_e = (esp - ep).abs().max().item() / ep.abs().max().item()
     d_r = (rsp - rp).abs().max().item() / rp.abs().max().item()
     ok &= d_e < 2e-2 and d_r < 2e-2
-    msg.append(f"sparse labels vs masks: losses {lsp} / {lp}; rel diff E {d_e:.2e} R {d_r:.2e}")
+    msg.append(f"sparse labels vs label masks: losses {lsp} / {lp}; rel diff E {d_e:.2e} R {d_r:.2e}")
     if rank == 0:
         ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(dev)
         model = make()

@@ -97,6 +97,28 @@ def test_pair_kernel_matches_reference_and_one_cta_kernel(nx, ny, ctas, with_los
     assert (res["1"][0] - res["0"][0]).abs().max() / denom < 1e-2
 
 
+def test_pair_kernel_loss_split_between_the_two_roles_adds_up():
+    """The two launches of a step (roles of x and y swapped) each add the loss of one half of the (x, y) plane."""
+    torch.manual_seed(5)
+    nx, ny, D = 1500, 700, 256
+    x = (torch.randn(nx, D, device=DEV) * 0.25).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.25).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    full = torch.zeros(1, dtype=torch.float64, device=DEV)
+    halves = torch.zeros(1, dtype=torch.float64, device=DEV)
+    ox, oy = torch.zeros(nx, D, device=DEV), torch.zeros(ny, D, device=DEV)
+    K.kvsall_fused(x, y, ox, full, status, 0.01, 1.0, True)
+    ox2, oy2 = torch.zeros(nx, D, device=DEV), torch.zeros(ny, D, device=DEV)
+    K.kvsall_fused(x, y, ox2, halves, status, 0.01, 1.0, True, loss_share=0)
+    part = halves.item()
+    K.kvsall_fused(y, x, oy2, halves, status, 0.01, 1.0, True, loss_share=1)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    assert 0.2 * full.item() < part < 0.8 * full.item()
+    assert abs(halves.item() - full.item()) < 1e-6 * abs(full.item())
+    assert (ox - ox2).abs().max() <= 2e-2 * ox.abs().max()
+
+
 def test_kvsall_fused_accumulates_and_splits_work():
     """Two launches add up; any CTA count gives the same sums (work ranges are arbitrary cuts of the tile grid)."""
     torch.manual_seed(0)
