@@ -97,8 +97,9 @@ def test_pair_kernel_matches_reference_and_one_cta_kernel(nx, ny, ctas, with_los
     assert (res["1"][0] - res["0"][0]).abs().max() / denom < 1e-2
 
 
-def test_pair_kernel_loss_split_between_the_two_roles_adds_up():
+def test_pair_kernel_loss_split_between_the_two_roles_adds_up(monkeypatch):
     """The two launches of a step (roles of x and y swapped) each add the loss of one half of the (x, y) plane."""
+    monkeypatch.setenv("DICE_B200_PAIR", "1")
     torch.manual_seed(5)
     nx, ny, D = 1500, 700, 256
     x = (torch.randn(nx, D, device=DEV) * 0.25).to(torch.bfloat16)
