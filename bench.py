@@ -232,7 +232,7 @@ def run_ours(args) -> dict:
     clocks = sampler.stop() if sampler is not None else None
     ms_dev, ms_e2e = statistics.median(blocks_dev), statistics.median(blocks_e2e)
     engine.sync_to_model()
-    if getattr(engine, "_phase_events", None) is not None:
+    if getattr(engine, "_phase_events", None) is not None or getattr(engine, "_phase_names", None) is not None:
         pt = engine.phase_times()
         if rank == 0:
             print("phase_ms " + json.dumps({k: round(v, 4) for k, v in pt.items()}), file=sys.stderr, flush=True)

@@ -444,6 +444,66 @@ __global__ void build_label_masks_flat_kernel(const long long* __restrict__ dp_i
   }
 }
 
+// Same result in ONE launch and without a global prefix sum: a block takes MASK_ITEMS consecutive batch items, scans
+// their positive counts in shared memory and then deals the block's positives to its threads one by one (binary search
+// in the shared prefix array).  Work is balanced inside a block; an item with thousands of known tails makes its block
+// loop a few more times, which costs microseconds, while the three dependent launches of the scan-based variant cost
+// about 20 us on the critical path of a training step.
+constexpr int MASK_ITEMS = 64;
+__global__ void __launch_bounds__(256) build_label_masks_block_kernel(
+    const long long* __restrict__ dp_idx, const long long* __restrict__ offsets, const long long* __restrict__ values,
+    int n, int W, int rank, unsigned int* __restrict__ mask_q, int stride_q, unsigned int* __restrict__ mask_e,
+    int stride_e, long long num_data_points, long long num_local_rows, int* status) {
+  __shared__ int pre[MASK_ITEMS + 1];
+  __shared__ long long beg[MASK_ITEMS];
+  const int i0 = blockIdx.x * MASK_ITEMS;
+  const int items = min(MASK_ITEMS, n - i0);
+  if (threadIdx.x < MASK_ITEMS) {
+    int c = 0;
+    long long b = 0;
+    if (threadIdx.x < items) {
+      const long long d = dp_idx[i0 + threadIdx.x];
+      if (num_data_points > 0 && (d < 0 || d >= num_data_points)) {
+        if (status != nullptr) atomicCAS(status, 0, ST_BAD_INDEX);
+      } else {
+        b = offsets[d];
+        c = static_cast<int>(offsets[d + 1] - b);
+      }
+    }
+    beg[threadIdx.x] = b;
+    // inclusive scan over the 64 counts: two warps, then the second adds the first warp's total
+    int v = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, v, o);
+      if ((threadIdx.x & 31) >= o) v += t;
+    }
+    pre[threadIdx.x + 1] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32 && threadIdx.x < MASK_ITEMS) pre[threadIdx.x + 1] += pre[32];
+  if (threadIdx.x == 0) pre[0] = 0;
+  __syncthreads();
+  const int total = pre[MASK_ITEMS];
+  for (int t = threadIdx.x; t < total; t += blockDim.x) {
+    int lo = 0, hi = MASK_ITEMS - 1;   // largest k with pre[k] <= t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (pre[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    const int i = i0 + lo;
+    const long long j = values[beg[lo] + (t - pre[lo])];
+    if (j % W != rank) continue;
+    const long long jl = j / W;
+    if (num_local_rows > 0 && (j < 0 || jl >= num_local_rows)) {
+      if (status != nullptr) atomicCAS(status, 0, ST_BAD_INDEX);
+      continue;
+    }
+    atomicOr(mask_q + static_cast<long long>(i) * stride_q + (jl >> 5), 1u << (jl & 31));
+    atomicOr(mask_e + jl * stride_e + (i >> 5), 1u << (i & 31));
+  }
+}
+
 // ------------------------------------------------------------------------------------ optimisers
 struct OptParams {
   float* param;
@@ -593,6 +653,129 @@ __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------ end of a step in one launch
+// Up to three parameter segments (entity shard, relation table, coefficient) are updated by one grid, and the block
+// that finishes last closes the step: loss = accumulator / count, accumulator = 0, step += 1.  Every block reads the
+// step counter when it starts, and the last block to finish is by construction behind all of those reads, so the
+// increment cannot race with them.
+struct StepTailParams {
+  OptParams seg[3];
+  int n_seg;
+  double* acc;
+  float* loss_out;
+  double inv_count;
+  long long* step_rw;
+  const double* const* acc_table;
+  int n_acc;
+  unsigned int* done;          // zero-initialised counter, reset by the closing block
+  const int* status;
+};
+
+__device__ __forceinline__ void optimizer_segment(const OptParams& p, long long t) {
+  float inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
+  if (p.kind <= 1) {
+    inv_bc1 = 1.f / (1.f - exp2f(static_cast<float>(t) * log2f(p.beta1)));
+    inv_sqrt_bc2 = rsqrtf(1.f - exp2f(static_cast<float>(t) * log2f(p.beta2)));
+  }
+  const float clip = sqrtf(sqrtf(static_cast<float>(t - 1)));
+  const bool first_step = (t == 1);
+  const bool remote = p.grad_table != nullptr || p.grad_mc != nullptr;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  bool vec = ((reinterpret_cast<uintptr_t>(p.param) | reinterpret_cast<uintptr_t>(p.grad) |
+               reinterpret_cast<uintptr_t>(p.m) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(p.shadow) & 7) == 0;
+  if (p.grad_mc != nullptr) vec &= (reinterpret_cast<uintptr_t>(p.grad_mc) & 15) == 0;
+  else if (p.grad_table != nullptr)
+    for (int k = 0; k < p.n_grad; ++k) vec &= (reinterpret_cast<uintptr_t>(p.grad_table[k]) & 15) == 0;
+  long long done = 0;
+  if (vec) {
+    const long long n4 = p.n >> 2;
+    for (long long i = tid; i < n4; i += stride) {
+      float4 w = reinterpret_cast<float4*>(p.param)[i];
+      float4 g;
+      if (p.grad_mc != nullptr) {
+        g = opt_multimem_sum4(p.grad_mc + (i << 2));
+      } else if (p.grad_table != nullptr) {
+        g = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < p.n_grad; ++k) {
+          const float4 x = reinterpret_cast<const float4*>(p.grad_table[k])[i];
+          g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+        }
+      } else {
+        g = reinterpret_cast<float4*>(p.grad)[i];
+      }
+      float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+      if (p.kind != 2) {
+        m = reinterpret_cast<float4*>(p.m)[i];
+        v = reinterpret_cast<float4*>(p.v)[i];
+      }
+      w.x = opt_update(p.kind, w.x, g.x, m.x, v.x, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.y = opt_update(p.kind, w.y, g.y, m.y, v.y, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.z = opt_update(p.kind, w.z, g.z, m.z, v.z, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      w.w = opt_update(p.kind, w.w, g.w, m.w, v.w, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+      reinterpret_cast<float4*>(p.param)[i] = w;
+      if (!remote) reinterpret_cast<float4*>(p.grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.kind != 2) {
+        reinterpret_cast<float4*>(p.m)[i] = m;
+        reinterpret_cast<float4*>(p.v)[i] = v;
+      }
+      if (p.shadow != nullptr) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(p.shadow)[i] = pk;
+      }
+    }
+    done = n4 << 2;
+  }
+  for (long long i = done + tid; i < p.n; i += stride) {
+    float w = p.param[i];
+    float g;
+    if (p.grad_mc != nullptr) {
+      g = opt_multimem_sum1(p.grad_mc + i);
+    } else if (p.grad_table != nullptr) {
+      g = 0.f;
+      for (int k = 0; k < p.n_grad; ++k) g += p.grad_table[k][i];
+    } else {
+      g = p.grad[i];
+      p.grad[i] = 0.f;
+    }
+    float m = 0.f, v = 0.f;
+    if (p.kind != 2) { m = p.m[i]; v = p.v[i]; }
+    w = opt_update(p.kind, w, g, m, v, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, inv_bc1, inv_sqrt_bc2, clip, first_step);
+    p.param[i] = w;
+    if (p.kind != 2) { p.m[i] = m; p.v[i] = v; }
+    if (p.shadow != nullptr) p.shadow[i] = __float2bfloat16_rn(w);
+  }
+}
+
+__global__ void __launch_bounds__(256) step_tail_kernel(const StepTailParams p) {
+  if (p.status != nullptr && *p.status != 0) return;
+  const long long t = *p.step_rw + 1;
+  for (int s = 0; s < p.n_seg; ++s) optimizer_segment(p.seg[s], t);
+  if (p.done == nullptr) return;
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(p.done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    if (p.acc_table != nullptr) {
+      double sum = 0.0;
+      for (int k = 0; k < p.n_acc; ++k) sum += *p.acc_table[k];
+      *p.loss_out = static_cast<float>(sum * p.inv_count);
+    } else {
+      *p.loss_out = static_cast<float>(*p.acc * p.inv_count);
+      *p.acc = 0.0;
+    }
+    *p.step_rw = t;
+    *p.done = 0u;
+  }
+}
+
 __global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
@@ -718,7 +901,8 @@ extern "C" int dice_build_label_masks(const long long* dp_idx, const long long* 
 }
 
 // first: int[n + 1] scratch for the prefix sums of positives per data point.
-// num_data_points / num_local_rows > 0 (with status) switch on range checks of the data-point ids and of the CSR
+// first == null selects the one-launch variant (block-local prefix sums); otherwise first is int[n + 1] scratch for the
+// count / scan / spread variant.  num_data_points / num_local_rows > 0 (with status) switch on range checks of the data-point ids and of the CSR
 // values; offending entries are reported through *status and skipped.
 extern "C" int dice_build_label_masks_flat(const long long* dp_idx, const long long* offsets, const long long* values,
                                            int* first, int n, int W, int rank, unsigned int* mask_q, int stride_q,
@@ -726,6 +910,12 @@ extern "C" int dice_build_label_masks_flat(const long long* dp_idx, const long l
                                            long long num_local_rows, int* status, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (first == nullptr) {   // one launch, block-local prefix sums
+    build_label_masks_block_kernel<<<(n + MASK_ITEMS - 1) / MASK_ITEMS, 256, 0, s>>>(
+        dp_idx, offsets, values, n, W, rank, mask_q, stride_q, mask_e, stride_e, num_data_points, num_local_rows,
+        status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   positive_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(dp_idx, offsets, n, first, num_data_points, status);
   positive_scan_kernel<<<1, 1024, 0, s>>>(n, first);
   build_label_masks_flat_kernel<<<148 * 4, 256, 0, s>>>(dp_idx, offsets, values, first, n, W, rank, mask_q, stride_q,
@@ -771,6 +961,36 @@ extern "C" int dice_optimizer_step(int kind, float* param, float* grad, float* m
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   optimizer_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// One launch for the end of a training step: optimiser sweeps over n_seg <= 3 parameter segments and, when `done`
+// (a zero-initialised device counter) is given, the closing of the step by the last block.  Per segment s the arrays
+// hold: param, grad, m, v, shadow (bf16 or null), n, grad_table (or null), grad_mc (or null); the optimiser kind and
+// hyper-parameters are shared.  n_grad: number of buffers behind every non-null grad_table.
+extern "C" int dice_step_tail(int kind, int n_seg, float* const* param, float* const* grad, float* const* m,
+                              float* const* v, void* const* shadow, const long long* n,
+                              const float* const* const* grad_table, const float* const* grad_mc, int n_grad,
+                              long long* step, float lr, float beta1, float beta2, float eps, float weight_decay,
+                              double* acc, float* loss_out, double inv_count, const double* const* acc_table, int n_acc,
+                              unsigned int* done, const int* status, void* stream) {
+  if (n_seg < 1 || n_seg > 3) return -6;
+  StepTailParams p{};
+  long long total = 0;
+  for (int s = 0; s < n_seg; ++s) {
+    p.seg[s] = OptParams{param[s], grad[s], m[s], v[s], static_cast<__nv_bfloat16*>(shadow[s]), step, n[s], lr, beta1,
+                         beta2, eps, weight_decay, kind, grad_table ? grad_table[s] : nullptr, n_grad,
+                         grad_mc ? grad_mc[s] : nullptr, status};
+    total += n[s];
+  }
+  p.n_seg = n_seg;
+  p.acc = acc; p.loss_out = loss_out; p.inv_count = inv_count; p.step_rw = step; p.acc_table = acc_table;
+  p.n_acc = n_acc; p.done = done; p.status = status;
+  const int threads = 256;
+  long long blocks = (total / 4 + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  step_tail_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

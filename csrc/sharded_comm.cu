@@ -82,8 +82,9 @@ __device__ __forceinline__ void normalize_rel8(int mode, const float (&r)[K][8],
 }
 
 struct LookupVecParams {
-  const long long* idx_h;        // [B] global entity ids of this rank's queries
-  const long long* idx_r;        // [B]
+  const long long* idx_h;        // [B] global entity ids of this rank's queries (entry i at idx_h[i * idx_stride])
+  const long long* idx_r;        // [B] relation ids, same stride: a [B, 2] batch of (h, r) pairs is read in place
+  int idx_stride;
   const long long* dp_src;       // [B] data-point ids (optional)
   const float* const* ent;       // [W] fp32 shard bases (peer pointers allowed)
   const float* rel;              // [R, D] replicated
@@ -109,8 +110,8 @@ __global__ void __launch_bounds__(256) lookup_compose_vec_kernel(const LookupVec
   if (tid >= static_cast<long long>(p.B) * per_row) return;
   const int i = static_cast<int>(tid / per_row);
   const int j0 = static_cast<int>(tid % per_row) << 3;
-  const long long h = p.idx_h[i];
-  const long long r_id = p.idx_r[i];
+  const long long h = p.idx_h[static_cast<long long>(i) * p.idx_stride];
+  const long long r_id = p.idx_r[static_cast<long long>(i) * p.idx_stride];
   if (h < 0 || h >= p.num_entities || r_id < 0 || r_id >= p.num_relations) {
     atomicCAS(p.status, 0, ST_BAD_INDEX);
     return;
@@ -168,8 +169,9 @@ __global__ void __launch_bounds__(256) lookup_compose_vec_kernel(const LookupVec
 }
 
 struct BwdOwnerParams {
-  const long long* idx_h;        // [n] global entity ids of the whole (global) batch
+  const long long* idx_h;        // [n] global entity ids of the whole (global) batch (entry i at [i * idx_stride])
   const long long* idx_r;        // [n]
+  int idx_stride;
   const float* ent_local;        // this rank's fp32 shard
   const float* rel;
   const float* coeff;
@@ -198,8 +200,8 @@ __global__ void __launch_bounds__(256) compose_backward_owner_kernel(const BwdOw
   if (active) {
     i = static_cast<int>(tid / per_row);
     j0 = static_cast<int>(tid % per_row) << 3;
-    h = p.idx_h[i];
-    r_id = p.idx_r[i];
+    h = p.idx_h[static_cast<long long>(i) * p.idx_stride];
+    r_id = p.idx_r[static_cast<long long>(i) * p.idx_stride];
     if (h < 0 || h >= p.num_entities || r_id < 0 || r_id >= p.num_relations) {
       atomicCAS(p.status, 0, ST_BAD_INDEX);
       active = false;
@@ -348,12 +350,13 @@ extern "C" int dice_lookup_vec_supported(int model, int D) {
   return (K > 0 && D % (8 * K) == 0) ? 1 : 0;
 }
 
-// model codes as in dice_lookup_compose.  q_mc != null publishes the bf16 rows through the multicast mapping (all
+// model codes as in dice_lookup_compose.  idx_h / idx_r are read with stride idx_stride (1 for separate arrays; 2 with
+// idx_r = idx_h + 1 reads a row-major [B, 2] batch of (h, r) pairs in place).  q_mc != null publishes the bf16 rows through the multicast mapping (all
 // bound GPUs receive them at the same offset); otherwise they are stored to each of the n_dst buffers of q_dst.
 // ids_dst (optional): n_dst index buffers receiving h, r and the data-point id of every row (three arrays, each
 // ids_stride long).  ent / q_dst / ids_dst are device arrays of base pointers.
 extern "C" int dice_lookup_compose_vec(int model, int normalize, const long long* idx_h, const long long* idx_r,
-                                       const long long* dp_src, const float* const* ent, int W,
+                                       int idx_stride, const long long* dp_src, const float* const* ent, int W,
                                        long long num_entities, int num_relations, const float* rel,
                                        const float* coeff, __nv_bfloat16* const* q_dst, int n_dst, void* q_mc,
                                        long long q_row_offset, float* q_f32, long long* const* ids_dst,
@@ -364,7 +367,8 @@ extern "C" int dice_lookup_compose_vec(int model, int normalize, const long long
       (reinterpret_cast<uintptr_t>(q_f32) & 15))
     return -5;
   LookupVecParams p{};
-  p.idx_h = idx_h; p.idx_r = idx_r; p.dp_src = dp_src; p.ent = ent; p.rel = rel; p.coeff = nullptr;
+  p.idx_h = idx_h; p.idx_r = idx_r; p.idx_stride = idx_stride > 0 ? idx_stride : 1; p.dp_src = dp_src; p.ent = ent;
+  p.rel = rel; p.coeff = nullptr;
   p.q_dst = q_dst; p.q_mc = static_cast<__nv_bfloat16*>(q_mc); p.q_f32 = q_f32; p.ids_dst = ids_dst;
   p.ids_stride = ids_stride; p.q_row_offset = q_row_offset; p.num_entities = num_entities;
   p.num_relations = num_relations; p.n_dst = n_dst; p.B = B; p.D = D; p.W = W; p.norm_mode = NORM_NONE;
@@ -386,7 +390,7 @@ extern "C" int dice_lookup_compose_vec(int model, int normalize, const long long
 // the n_dq buffers of dq_table, else from dq.  Row gradients are added to g_ent_local (this rank's shard), relation
 // gradients to g_rel (this rank's partial sum).
 extern "C" int dice_compose_backward_owner(int model, int normalize, const long long* idx_h, const long long* idx_r,
-                                           const float* ent_local, int W, int rank, long long num_entities,
+                                           int idx_stride, const float* ent_local, int W, int rank, long long num_entities,
                                            int num_relations, const float* rel, const float* coeff, const float* dq,
                                            const float* const* dq_table, int n_dq, const void* dq_mc,
                                            float* g_ent_local, float* g_rel, float* g_coeff, int n, int D,
@@ -398,7 +402,8 @@ extern "C" int dice_compose_backward_owner(int model, int normalize, const long 
       (reinterpret_cast<uintptr_t>(g_ent_local) & 15) || (reinterpret_cast<uintptr_t>(g_rel) & 15))
     return -5;
   BwdOwnerParams p{};
-  p.idx_h = idx_h; p.idx_r = idx_r; p.ent_local = ent_local; p.rel = rel; p.coeff = nullptr; p.dq = dq;
+  p.idx_h = idx_h; p.idx_r = idx_r; p.idx_stride = idx_stride > 0 ? idx_stride : 1; p.ent_local = ent_local;
+  p.rel = rel; p.coeff = nullptr; p.dq = dq;
   p.dq_table = dq_table; p.dq_mc = static_cast<const float*>(dq_mc); p.g_ent_local = g_ent_local; p.g_rel = g_rel;
   p.g_coeff = nullptr; p.num_entities = num_entities; p.num_relations = num_relations; p.n = n; p.n_dq = n_dq;
   p.D = D; p.W = W; p.rank = rank; p.norm_mode = NORM_NONE; p.additive = 0; p.status = status;

@@ -38,21 +38,36 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile ``csrc/*.cu`` for sm_100a into ``libdice_b200.so`` (no-op when up to date)."""
+    """Compile ``csrc/*.cu`` for sm_100a into ``libdice_b200.so`` (no-op when up to date).
+
+    Several processes may call this at once (every rank of a ``torchrun`` job on a fresh checkout): the build runs
+    under an exclusive file lock, into a file of the process's own, and is published with an atomic rename; a process
+    that waited for the lock finds the library up to date and does not compile again."""
     if not force and not needs_build():
         return LIB_PATH
-    nvcc = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
-    if not os.path.isfile(nvcc):
-        nvcc = "nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, *sources(), "-o", LIB_PATH + ".tmp"]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        print(res.stderr)
-    os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    import fcntl
+    with open(LIB_PATH + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():   # another process built it while this one waited
+                return LIB_PATH
+            nvcc = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
+            if not os.path.isfile(nvcc):
+                nvcc = "nvcc"
+            tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+            cmd = [nvcc, *NVCC_FLAGS, *sources(), "-o", tmp]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+            if verbose:
+                print(res.stderr)
+            os.replace(tmp, LIB_PATH)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 
@@ -93,8 +108,9 @@ class _Sigs:
     dice_build_label_masks = [_p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
     dice_build_label_masks_flat = [_p, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _l, _l, _p, _p]
     dice_lookup_vec_supported = [_i, _i]
-    dice_lookup_compose_vec = [_i, _i, _p, _p, _p, _p, _i, _l, _i, _p, _p, _p, _i, _p, _l, _p, _p, _l, _i, _i, _p, _p]
-    dice_compose_backward_owner = [_i, _i, _p, _p, _p, _i, _i, _l, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p, _p]
+    dice_lookup_compose_vec = [_i, _i, _p, _p, _i, _p, _p, _i, _l, _i, _p, _p, _p, _i, _p, _l, _p, _p, _l, _i, _i, _p, _p]
+    dice_compose_backward_owner = [_i, _i, _p, _p, _i, _p, _i, _i, _l, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p, _p]
+    dice_step_tail = [_i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _f, _f, _f, _f, _f, _p, _p, _d, _p, _i, _p, _p, _p]
     dice_positive_correction_noalloc = [_p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p]
     dice_lookup_compose = [_i, _i, _p, _p, _p, _i, _l, _p, _p, _p, _i, _l, _p, _i, _i, _p, _p, _p, _p]
     dice_compose_backward = [_i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _i, _l, _p]

@@ -9,8 +9,8 @@ One step is a short fixed sequence of kernel launches replayed from a CUDA graph
    read by the scoring epilogue) or, for tables too large for masks, ``positive_scan`` + ``positive_correction``
    after them (sparse label term from the CSR)
 5. ``compose_backward_owner``  chain rule of the composition, row gradients added into ``dE`` / ``dR``
-6. ``optimizer_step`` ×k   Adam / AdamW / SGD / ADOPT over E (refreshing the bf16 shadow), R and the coefficient
-7. ``finish_step``         loss = accumulator / (B·|E|), accumulator = 0, step += 1
+6. ``step_tail``           Adam / AdamW / SGD / ADOPT over E (refreshing the bf16 shadow), R and the coefficient in one
+   launch whose last block closes the step: loss = accumulator / (B·|E|), accumulator = 0, step += 1
 
 The ``[B, |E|]`` logit and label matrices of the reference's step (``dicee/models/base_model.py:25-46``:
 forward, ``BCEWithLogitsLoss``, backward, optimiser) never exist; labels are the resident CSR.  The model's own
@@ -135,6 +135,14 @@ class FusedKvsAllEngine:
         self._bufs = {}
         self._graphs = {}
         self._side = torch.cuda.Stream(device=dev)
+        self._phase_names = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
+        self._phase_slots = torch.zeros(32, dtype=torch.int64, device=dev)
+        segs = [dict(param=self.E, grad=self.gE, m=self.mE, v=self.vE, shadow=self.E_bf16),
+                dict(param=self.R, grad=self.gR, m=self.mR, v=self.vR)]
+        if self.coeff_trainable:
+            segs.append(dict(param=self.coeff, grad=self.gC, m=self.mC, v=self.vC))
+        self._tail = K.StepTail(self.opt_kind, segs, self.step_count, self.status, finish=True, acc=self.loss_acc,
+                                loss_out=self.loss_out)
 
     # ------------------------------------------------------------------ buffers per batch size
     def _buffers(self, n: int):
@@ -142,8 +150,7 @@ class FusedKvsAllEngine:
             dev = self.device
             b = SimpleNamespace()
             b.x_in = torch.zeros(n, 2, dtype=torch.int64, device=dev)   # the batch's (h, r) pairs as they arrive
-            b.h = torch.zeros(n, dtype=torch.int64, device=dev)
-            b.r = torch.zeros(n, dtype=torch.int64, device=dev)
+            b.h, b.r = b.x_in.view(-1), b.x_in.view(-1)[1:]             # read in place with stride 2 by the kernels
             b.dp = torch.zeros(n, dtype=torch.int64, device=dev)
             b.Q = torch.zeros(n, self.D, dtype=torch.bfloat16, device=dev)
             b.dQ = torch.zeros(n, self.D, dtype=torch.float32, device=dev)
@@ -157,9 +164,23 @@ class FusedKvsAllEngine:
             self._bufs[n] = b
         return self._bufs[n]
 
+    def _mark(self, name: str) -> None:
+        """Phase timing (``DICE_B200_PHASE_TIMING=1``): a one-thread kernel stores the GPU timer after each phase, also
+        under graph replay; :meth:`phase_times` returns milliseconds per phase of the last step."""
+        if self._phase_names is not None:
+            if name not in self._phase_names:
+                self._phase_names.append(name)
+            K.timestamp(self._phase_slots, self._phase_names.index(name))
+
+    def phase_times(self):
+        torch.cuda.synchronize(self.device)
+        t = self._phase_slots.cpu().tolist()
+        return {self._phase_names[i]: (t[i] - t[i - 1]) / 1e6 for i in range(1, len(self._phase_names))}
+
     def _launch_all(self, b, n: int) -> None:
         scale = 1.0 / (float(n) * float(self.NE))
         main = torch.cuda.current_stream(self.device)
+        self._mark("start")
         if self.label_mode == "mask":
             # the label masks depend on the data-point ids only: they are built on a side stream (a parallel branch
             # of the captured graph) while the main stream gathers and composes the queries
@@ -168,17 +189,19 @@ class FusedKvsAllEngine:
                 b.mask_q.zero_()
                 b.mask_e.zero_()
                 K.build_label_masks(b.dp, self.offsets, self.values, n, 1, 0, b.mask_q, b.mask_e, first=b.first)
-        b.h.copy_(b.x_in[:, 0])   # inside the captured sequence: callers only fill x_in and dp
-        b.r.copy_(b.x_in[:, 1])
         K.lookup_compose_vec(self.code, self.normalize, b.h, b.r, None, b.ent_tab, 1, self.NE, self.NR, self.R,
-                             self.coeff, b.q_tab, 1, 0, 0, None, None, 0, n, self.D, self.status)
+                             self.coeff, b.q_tab, 1, 0, 0, None, None, 0, n, self.D, self.status, idx_stride=2)
+        self._mark("lookup")
         if self.label_mode == "mask":
             main.wait_stream(self._side)
+            self._mark("masks_join")
             # both launches add half of the loss terms each (the epilogue with loss costs several times the one without)
             K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True,
                            mask=b.mask_e, pos_delta=self.pos_weight, loss_share=0)
+            self._mark("fused_E")
             K.kvsall_fused(b.Q, self.E_bf16, b.dQ, self.loss_acc, self.status, self.base, scale, True,
                            mask=b.mask_q, pos_delta=self.pos_weight, loss_share=1)
+            self._mark("fused_Q")
         else:
             # the label term of the known tails (loss, dE rows, dQ rows; all added atomically) runs on a parallel
             # branch next to the two dense scoring launches: it needs the queries and the entity table only
@@ -193,25 +216,21 @@ class FusedKvsAllEngine:
             main.wait_stream(self._side)
         K.compose_backward_owner(self.code, self.normalize, b.h, b.r, self.E, 1, 0, self.NE, self.NR, self.R,
                                  self.coeff, b.dQ, None, 0, 0, self.gE, self.gR,
-                                 self.gC if self.coeff_trainable else None, n, self.D, self.status)
+                                 self.gC if self.coeff_trainable else None, n, self.D, self.status, idx_stride=2)
+        self._mark("backward")
         b1, b2 = self.betas
-        # the small updates (relations, coefficient, clearing dQ) run beside the sweep over the entity table
         self._side.wait_stream(main)
         with torch.cuda.stream(self._side):
             b.dQ.zero_()
-            K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, self.lr, b1, b2,
-                             self.eps, self.weight_decay)
-            if self.coeff_trainable:
-                K.optimizer_step(self.opt_kind, self.coeff, self.gC, self.mC, self.vC, None, self.step_count, self.lr,
-                                 b1, b2, self.eps, self.weight_decay)
-        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, self.lr, b1,
-                         b2, self.eps, self.weight_decay)
+        # one launch: Adam / ADOPT / SGD over entities (refreshing the bf16 shadow), relations and the coefficient; its
+        # last block turns the loss accumulator into the step's loss and advances the step counter
+        self._tail.launch(self.lr, b1, b2, self.eps, self.weight_decay, scale)
         main.wait_stream(self._side)
-        K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count)
+        self._mark("tail")
 
     #: number of kernels of this library launched per step (for launch accounting)
     def launches_per_step(self) -> int:
-        return (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)   # kernels of this library
+        return 8 if self.label_mode == "mask" else 7   # kernels of this library
 
     def _run(self, b, n: int) -> None:
         key = (n, self.lr)

@@ -125,12 +125,14 @@ def lookup_compose_vec(model: int, normalize: bool, idx_h, idx_r, dp_src: Option
                        ent_table: torch.Tensor, W: int, num_entities: int, num_relations: int, rel: torch.Tensor,
                        coeff: Optional[torch.Tensor], q_dst_table: Optional[torch.Tensor], n_dst: int, q_mc: int,
                        q_row_offset: int, q_f32: Optional[torch.Tensor], ids_dst_table: Optional[torch.Tensor],
-                       ids_stride: int, B: int, D: int, status: torch.Tensor) -> None:
+                       ids_stride: int, B: int, D: int, status: torch.Tensor, idx_stride: int = 1) -> None:
     """Head rows are pulled from their owners, composed with the relation rows, and the bf16 query rows are published
     either through the multicast address ``q_mc`` (one ``multimem.st`` per 16 bytes reaches every rank) or to the
     ``n_dst`` buffers of ``q_dst_table``.  ``ids_dst_table``: per-destination index buffers receiving ``h | r | dp``
-    (three arrays of ``ids_stride`` entries each)."""
-    _call("dice_lookup_compose_vec", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(dp_src),
+    (three arrays of ``ids_stride`` entries each).  ``idx_stride``: distance between consecutive entries of ``idx_h`` /
+    ``idx_r`` (2 with ``idx_r = idx_h[1:]`` views of a ``[B, 2]`` batch reads the pairs in place)."""
+    _call("dice_lookup_compose_vec", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), int(idx_stride),
+          _ptr(dp_src),
           _ptr(ent_table), int(W), int(num_entities), int(num_relations), _ptr(rel), _ptr(coeff), _ptr(q_dst_table),
           int(n_dst), int(q_mc) or None, int(q_row_offset), _ptr(q_f32), _ptr(ids_dst_table), int(ids_stride), int(B),
           int(D), _ptr(status), others=(idx_h, idx_r, dp_src, ent_table, status, q_f32))
@@ -150,14 +152,15 @@ def compose_backward(model: int, normalize: bool, idx_h, idx_r, ent_table, W: in
 def compose_backward_owner(model: int, normalize: bool, idx_h, idx_r, ent_local: torch.Tensor, W: int, rank: int,
                            num_entities: int, num_relations: int, rel: torch.Tensor, coeff, dq, dq_table, n_dq: int,
                            dq_mc: int, g_ent_local: torch.Tensor, g_rel: torch.Tensor, g_coeff, n: int, D: int,
-                           status: torch.Tensor) -> None:
+                           status: torch.Tensor, idx_stride: int = 1) -> None:
     """Backward of the composition for the queries whose head row this rank owns.  The query gradient is read through
     the multicast address ``dq_mc`` (``multimem.ld_reduce``: the sum over all ranks is formed inside the switch), else
     as the sum of the ``n_dq`` buffers of ``dq_table`` (peer loads), else from ``dq``.  Row gradients stay local."""
     _req(ent_local, torch.float32, "ent_local")
     _req(g_ent_local, torch.float32, "g_ent_local")
     _req(g_rel, torch.float32, "g_rel")
-    _call("dice_compose_backward_owner", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), _ptr(ent_local),
+    _call("dice_compose_backward_owner", rel, int(model), int(normalize), _ptr(idx_h), _ptr(idx_r), int(idx_stride),
+          _ptr(ent_local),
           int(W), int(rank), int(num_entities), int(num_relations), _ptr(rel), _ptr(coeff), _ptr(dq), _ptr(dq_table),
           int(n_dq), int(dq_mc) or None, _ptr(g_ent_local), _ptr(g_rel), _ptr(g_coeff), int(n), int(D), _ptr(status),
           others=(idx_h, idx_r, ent_local, dq, g_ent_local, g_rel, status))
@@ -171,19 +174,26 @@ def mask_stride(n_bits: int) -> int:
 def build_label_masks(dp_idx, offsets, values, n: int, W: int, rank: int, mask_q: torch.Tensor,
                       mask_e: torch.Tensor, first: Optional[torch.Tensor] = None,
                       num_data_points: int = 0, num_local_rows: int = 0,
-                      status: Optional[torch.Tensor] = None) -> None:
+                      status: Optional[torch.Tensor] = None, variant: str = "block") -> None:
     """Set the positive-label bits of a batch in both mask orientations (masks must be zeroed by the caller).
-    With ``first`` (int32 ``[n + 1]`` scratch) the work is spread one thread per positive label instead of one warp
-    per data point, which is faster when a few data points own most of the positives.  ``num_data_points`` /
-    ``num_local_rows`` (with ``status``) switch on range checks of the data-point ids and of the CSR values."""
+
+    ``variant``: ``"block"`` (default) is one launch in which every block scans the positive counts of 64 consecutive
+    batch items in shared memory and deals their positives to its threads; ``"scan"`` (needs ``first``, int32
+    ``[n + 1]`` scratch) counts, scans globally and spreads one thread per positive in three launches; ``"warp"`` walks
+    one data point per warp.  ``num_data_points`` / ``num_local_rows`` (with ``status``) switch on range checks of the
+    data-point ids and of the CSR values."""
     _req(mask_q, torch.int32, "mask_q")
     _req(mask_e, torch.int32, "mask_e")
-    if first is not None:
-        _req(first, torch.int32, "first")
-        assert first.numel() >= n + 1
-        _call("dice_build_label_masks_flat", mask_q, _ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(first), n, W,
+    if variant == "scan":
+        assert first is not None
+    if variant in ("block", "scan"):
+        use_first = first if variant == "scan" else None
+        if use_first is not None:
+            _req(use_first, torch.int32, "first")
+            assert use_first.numel() >= n + 1
+        _call("dice_build_label_masks_flat", mask_q, _ptr(dp_idx), _ptr(offsets), _ptr(values), _ptr(use_first), n, W,
               rank, _ptr(mask_q), mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], int(num_data_points),
-              int(num_local_rows), _ptr(status), others=(dp_idx, offsets, values, first, mask_e, status))
+              int(num_local_rows), _ptr(status), others=(dp_idx, offsets, values, use_first, mask_e, status))
         return
     _call("dice_build_label_masks", mask_q, _ptr(dp_idx), _ptr(offsets), _ptr(values), n, W, rank, _ptr(mask_q),
           mask_q.shape[1], _ptr(mask_e), mask_e.shape[1], others=(dp_idx, offsets, values, mask_e))
@@ -210,6 +220,41 @@ def optimizer_step(kind: int, param, grad, m, v, shadow, step, lr, beta1, beta2,
     _call("dice_optimizer_step", param, kind, _ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(shadow), _ptr(step),
           param.numel(), float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), _ptr(grad_table),
           int(n_grad), int(grad_mc) or None, _ptr(status), others=(grad, m, v, shadow, step, status))
+
+
+class StepTail:
+    """End of a training step as ONE launch: optimiser sweeps over up to three parameter segments and, with
+    ``finish=True``, the closing of the step (loss = accumulator / count, accumulator cleared, step counter advanced)
+    by the block that finishes last.  The pointer arrays are built once; :meth:`launch` only passes scalars."""
+
+    def __init__(self, kind: int, segments, step: torch.Tensor, status: Optional[torch.Tensor], finish: bool,
+                 acc: Optional[torch.Tensor] = None, loss_out: Optional[torch.Tensor] = None,
+                 acc_table: Optional[torch.Tensor] = None, n_acc: int = 0, n_grad: int = 0):
+        """``segments``: list of dicts with ``param, grad, m, v`` and optional ``shadow`` (bf16), ``grad_table``
+        (device pointer table of ``n_grad`` gradient buffers) and ``grad_mc`` (multicast address)."""
+        import ctypes
+        assert 1 <= len(segments) <= 3
+        self.kind, self.n_seg, self.n_grad = int(kind), len(segments), int(n_grad)
+        self.step, self.status, self.acc, self.loss_out = step, status, acc, loss_out
+        self.acc_table, self.n_acc = acc_table, int(n_acc)
+        self.anchor = segments[0]["param"]
+        self._keep = segments
+        P = ctypes.c_void_p * self.n_seg
+        self.param = P(*[s["param"].data_ptr() for s in segments])
+        self.grad = P(*[_ptr(s.get("grad")) for s in segments])
+        self.m = P(*[_ptr(s.get("m")) for s in segments])
+        self.v = P(*[_ptr(s.get("v")) for s in segments])
+        self.shadow = P(*[_ptr(s.get("shadow")) for s in segments])
+        self.n = (ctypes.c_longlong * self.n_seg)(*[s["param"].numel() for s in segments])
+        self.grad_table = P(*[_ptr(s.get("grad_table")) for s in segments])
+        self.grad_mc = P(*[(int(s.get("grad_mc") or 0) or None) for s in segments])
+        self.done = torch.zeros(1, dtype=torch.int32, device=self.anchor.device) if finish else None
+
+    def launch(self, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, inv_count: float = 1.0):
+        _call("dice_step_tail", self.anchor, self.kind, self.n_seg, self.param, self.grad, self.m, self.v, self.shadow,
+              self.n, self.grad_table, self.grad_mc, self.n_grad, _ptr(self.step), float(lr), float(beta1),
+              float(beta2), float(eps), float(weight_decay), _ptr(self.acc), _ptr(self.loss_out), float(inv_count),
+              _ptr(self.acc_table), self.n_acc, _ptr(self.done), _ptr(self.status))
 
 
 def cast_bf16(src: torch.Tensor, dst: torch.Tensor) -> None:

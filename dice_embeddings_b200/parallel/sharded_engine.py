@@ -173,10 +173,9 @@ class ShardedKvsAllEngine:
         else:
             self.offsets_loc, self.values_loc = self.offsets, self.values
 
-        self.h = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.r = torch.zeros(B, dtype=torch.int64, device=dev)
         self.dp = torch.zeros(B, dtype=torch.int64, device=dev)
         self.x_in = torch.zeros(B, 2, dtype=torch.int64, device=dev)
+        self.h, self.r = self.x_in.view(-1), self.x_in.view(-1)[1:]   # read in place with stride 2 by the lookup
         # labels: "mask" (default while the masks fit 1 GiB) feeds bit masks of the positives to the scoring epilogues;
         # "sparse" applies the known tails by a correction kernel driven by the owner-partitioned CSR, beside the dense
         # scoring launches (tables of millions of rows)
@@ -198,6 +197,12 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._side = torch.cuda.Stream(device=dev)
+        if comm == "p2p":
+            segs = [dict(param=self.R, grad=self.gR, m=self.mR, v=self.vR, grad_table=self.tab.gR, grad_mc=self.mc.gR)]
+            if self.coeff_trainable:
+                segs.append(dict(param=self.coeff, grad=self.gC[:1], m=self.mC, v=self.vC, grad_table=self.tab.gC))
+            self._tail = K.StepTail(self.opt_kind, segs, self.step_count, self.status, finish=True,
+                                    loss_out=self.loss_out, acc_table=self.tab.loss, n_acc=W, n_grad=W)
         self._phase_events = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
         self._phase_names = []
         self._phase_slots = torch.zeros(32, dtype=torch.int64, device=dev)
@@ -240,8 +245,6 @@ class ShardedKvsAllEngine:
         b1, b2 = self.betas
         a = (self.lr, b1, b2, self.eps, self.weight_decay)
         self._mark("start")
-        self.h.copy_(self.x_in[:, 0])                     # callers only fill x_in and dp
-        self.r.copy_(self.x_in[:, 1])
         masks = self.label_mode == "mask"
         main = torch.cuda.current_stream(self.device)
         if masks:   # cleared on a parallel branch; joined before the masks are built
@@ -252,7 +255,7 @@ class ShardedKvsAllEngine:
         # head rows by peer loads, query rows and batch indices to every rank (multimem.st or one store per rank)
         K.lookup_compose_vec(self.code, self.normalize, self.h, self.r, self.dp, self.tab.E, W, self.NE, self.NR,
                              self.R, self.coeff, self.tab.Q, W, self.mc.Q, self.rank * B, None, self.tab.ids, n, B, D,
-                             self.status)
+                             self.status, idx_stride=2 if self.comm == "p2p" else 1)
         self._mark("lookup+allgather")
         self._barrier()                                   # S1: all query rows have landed everywhere
         self._mark("S1")
@@ -298,20 +301,16 @@ class ShardedKvsAllEngine:
         self._side.wait_stream(main)
         with torch.cuda.stream(self._side):
             self.dQ.zero_()
-        K.optimizer_step(self.opt_kind, self.R, self.gR, self.mR, self.vR, None, self.step_count, *a,
-                         grad_table=self.tab.gR, n_grad=W, grad_mc=self.mc.gR, status=self.status)
-        if self.coeff_trainable:
-            K.optimizer_step(self.opt_kind, self.coeff, self.gC[:1], self.mC, self.vC, None, self.step_count, *a,
-                             grad_table=self.tab.gC, n_grad=W, status=self.status)
-        K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=W,
-                      status=self.status)
+        # one launch: the replicated tables are updated from the sum of all ranks' gradient buffers (multimem.ld_reduce
+        # or peer loads: the all-reduce folded into the update) and the last block sums the loss partials
+        self._tail.launch(*a, scale)
         main.wait_stream(self._side)
         self._mark("optim_R")
 
     def launches_per_step(self) -> int:
         if self.comm != "p2p":
             return 9
-        return 3 + (9 if self.label_mode == "mask" else 10) + (1 if self.coeff_trainable else 0)
+        return 3 + (9 if self.label_mode == "mask" else 8)
 
     # ------------------------------------------------------------------ the step, collective flavour
     def _init_nccl_buffers(self) -> None:
@@ -327,6 +326,8 @@ class ShardedKvsAllEngine:
         self.n_dh = torch.zeros(B, D, dtype=torch.float32, device=dev)
         self.n_dh_all = torch.zeros(W * B, D, dtype=torch.float32, device=dev)
         self.n_arange = torch.arange(B, dtype=torch.int64, device=dev)
+        self.n_h = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.n_r = torch.zeros(B, dtype=torch.int64, device=dev)
         self.n_tab_h = K.pointer_table([self.n_hrows], dev)
         self.n_tab_q = K.pointer_table([self.n_Q], dev)
         self.n_tab_dh = K.pointer_table([self.n_dh], dev)
@@ -334,16 +335,16 @@ class ShardedKvsAllEngine:
     def _launch_nccl(self) -> None:
         W, B, D, n, g = self.W, self.B, self.D, self.W * self.B, self.group
         scale = 1.0 / (float(n) * float(self.NE))
-        self.h.copy_(self.x_in[:, 0])
-        self.r.copy_(self.x_in[:, 1])
+        self.n_h.copy_(self.x_in[:, 0])
+        self.n_r.copy_(self.x_in[:, 1])
         # lookup: all-gather the head ids, every owner contributes its rows, reduce-scatter back
-        dist.all_gather_into_tensor(self.n_h_all, self.h, group=g)
+        dist.all_gather_into_tensor(self.n_h_all, self.n_h, group=g)
         dist.all_gather_into_tensor(self.n_dp_all, self.dp, group=g)
         mine = (self.n_h_all % W) == self.rank
         self.n_rows_all.zero_()
         self.n_rows_all[mine] = self.E[torch.div(self.n_h_all[mine], W, rounding_mode="floor")]
         dist.reduce_scatter_tensor(self.n_hrows, self.n_rows_all, group=g)
-        K.lookup_compose(self.code, self.normalize, self.n_arange, self.r, self.n_tab_h, 1, B, self.R, self.coeff,
+        K.lookup_compose(self.code, self.normalize, self.n_arange, self.n_r, self.n_tab_h, 1, B, self.R, self.coeff,
                          self.n_tab_q, 1, 0, None, B, D, self.status)
         dist.all_gather_into_tensor(self.n_Qall, self.n_Q, group=g)
         self.mask_q.zero_()
@@ -357,7 +358,7 @@ class ShardedKvsAllEngine:
                        mask=self.mask_q, pos_delta=self.pos_weight)
         dist.reduce_scatter_tensor(self.n_dQ, self.n_dQall, group=g)
         self.n_dh.zero_()
-        K.compose_backward(self.code, self.normalize, self.n_arange, self.r, self.n_tab_h, 1, self.R, self.coeff,
+        K.compose_backward(self.code, self.normalize, self.n_arange, self.n_r, self.n_tab_h, 1, self.R, self.coeff,
                            self.n_dQ, self.n_tab_dh, self.gR, self.gC if self.coeff_trainable else None, B, D)
         dist.all_gather_into_tensor(self.n_dh_all, self.n_dh, group=g)
         self.gE.index_add_(0, torch.div(self.n_h_all[mine], W, rounding_mode="floor"), self.n_dh_all[mine])

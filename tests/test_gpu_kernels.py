@@ -343,7 +343,8 @@ def test_p2p_barrier_wait_is_bounded():
 
 
 def test_label_mask_kernels_agree():
-    """One warp per data point and one thread per positive label build the same masks (two shards)."""
+    """The three mask builders (one warp per data point; count / scan / one thread per positive; one launch with
+    block-local prefix sums) build the same masks (two shards; a graph with a few very heavy data points)."""
     from dice_embeddings_b200.data.datasets import KvsAll
     from dice_embeddings_b200.data.synthetic import zipf_kg
     NE, NR = 900, 9
@@ -354,13 +355,14 @@ def test_label_mask_kernels_agree():
     for W, rank in ((1, 0), (2, 1)):
         rows = (NE - rank + W - 1) // W
         masks = []
-        for flat in (False, True):
+        for variant in ("warp", "scan", "block"):
             mq = torch.zeros(n, K.mask_stride(rows), dtype=torch.int32, device=DEV)
             me = torch.zeros(rows, K.mask_stride(n), dtype=torch.int32, device=DEV)
-            first = torch.zeros(n + 1, dtype=torch.int32, device=DEV) if flat else None
-            K.build_label_masks(dp, offsets, values, n, W, rank, mq, me, first=first)
+            first = torch.zeros(n + 1, dtype=torch.int32, device=DEV)
+            K.build_label_masks(dp, offsets, values, n, W, rank, mq, me, first=first, variant=variant)
             masks.append((mq, me))
-        assert torch.equal(masks[0][0], masks[1][0]) and torch.equal(masks[0][1], masks[1][1])
+        for k in (1, 2):
+            assert torch.equal(masks[0][0], masks[k][0]) and torch.equal(masks[0][1], masks[k][1])
         assert int(masks[0][0].ne(0).sum()) > 0
 
 
