@@ -104,16 +104,18 @@ def fused_tail_ranks(model, triples: torch.Tensor, er_vocab, batch_size: int = 4
         q, _ = eval_rank.model_queries(model, b[:, :2])
         ptr, cols = filter_csr(er_vocab, b[:, 0], b[:, 1])
         try:
-            r = ranker.ranks(q, b[:, 2], ptr, cols)
+            r = ranker.ranks(q, b[:, 2], ptr, cols).cpu()
+            ranker.check()          # the ranks are on the host already: reading the status words costs nothing more
         except KernelError:
             if not ranker.exact:
                 raise
             ranker.exact = False
             try:
-                r = ranker.ranks(q, b[:, 2], ptr, cols)
+                r = ranker.ranks(q, b[:, 2], ptr, cols).cpu()
+                ranker.check()
             finally:
                 ranker.exact = True
-        out.append(r.cpu())
+        out.append(r)
     return torch.cat(out) if out else torch.zeros(0, dtype=torch.long)
 
 

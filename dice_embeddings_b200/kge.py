@@ -315,6 +315,7 @@ class KGE:
             s, ix = ranker.topk(q, topk)
             scores.append((s if bias is None else s + bias.reshape(-1, 1)).cpu())
             indices.append(ix.cpu())
+        ranker.check()
         return torch.cat(scores).flatten(), torch.cat(indices).flatten()
 
     def predict_missing_head_entity(self, relation: StrOrList, tail_entity: StrOrList, within=None,

@@ -131,5 +131,8 @@ class _Sigs:
     dice_conv_gate_supported = [_i, _i, _i, _i]
     dice_conv_gate_forward = [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _f, _f, _p, _p, _p, _p]
     dice_conv_gate_backward = [_i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]
+    dice_peer_sum_f32 = [_p, _i, _p, _i, _p, _p]
+    dice_merge_ranks = [_p, _p, _i, _p, _i, _p, _p]
+    dice_merge_topk = [_p, _p, _i, _i, _l, _p, _p, _i, _p, _p]
     dice_eval_sparse = [_p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _p]
     dice_eval_band_exact = [_p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _l, _p, _p, _p]

@@ -443,6 +443,29 @@ def eval_sparse(q: torch.Tensor, y: torch.Tensor, target_idx: torch.Tensor, targ
           others=(y, target_idx, col_bias, target_in, filt_ptr, filt_cols, target_score, filtered_greater))
 
 
+def peer_sum_f32(table: torch.Tensor, W: int, out: torch.Tensor, n: int, status: Optional[torch.Tensor] = None) -> None:
+    """``out[i] = Σ_k table[k][i]`` over the ``W`` buffers (peer memory) whose base addresses ``table`` holds."""
+    _req(out, torch.float32, "out")
+    _call("dice_peer_sum_f32", out, _ptr(table), int(W), _ptr(out), int(n), _ptr(status), others=(table, status))
+
+
+def merge_ranks(greater_table: torch.Tensor, filtered_table: torch.Tensor, W: int, ranks: torch.Tensor, n: int,
+                status: Optional[torch.Tensor] = None) -> None:
+    """``ranks[i] = 1 + Σ_k greater_k[i] − Σ_k filtered_k[i]`` from every rank's int32 count buffers (peer loads)."""
+    _req(ranks, torch.int64, "ranks")
+    _call("dice_merge_ranks", ranks, _ptr(greater_table), _ptr(filtered_table), int(W), _ptr(ranks), int(n),
+          _ptr(status), others=(greater_table, filtered_table, status))
+
+
+def merge_topk(score_table: torch.Tensor, idx_table: torch.Tensor, W: int, k: int, stride: int, out_s: torch.Tensor,
+               out_i: torch.Tensor, n: int, status: Optional[torch.Tensor] = None) -> None:
+    """Best ``k`` of the ``W · k`` candidates per query held in every rank's candidate buffers (peer loads)."""
+    _req(out_s, torch.float32, "out_s")
+    _req(out_i, torch.int64, "out_i")
+    _call("dice_merge_topk", out_s, _ptr(score_table), _ptr(idx_table), int(W), int(k), int(stride), _ptr(out_s),
+          _ptr(out_i), int(n), _ptr(status), others=(score_table, idx_table, out_i, status))
+
+
 def check_status(status: torch.Tensor, where: str = "") -> None:
     """Read the device status word (synchronises) and raise if a kernel reported a failure."""
     code = int(status.item())

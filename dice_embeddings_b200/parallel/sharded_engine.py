@@ -149,8 +149,14 @@ class ShardedKvsAllEngine:
                                    Q=heap.table("Q"), dQ=heap.table("dQ"), ids=heap.table("ids"),
                                    loss=heap.table("loss"), sig=heap.table("sig"))
         mm = self.multimem
-        self.mc = SimpleNamespace(Q=heap.mc_address("Q") if mm else 0, dQ=heap.mc_address("dQ") if mm else 0,
-                                  gR=heap.mc_address("gR") if mm else 0, gC=heap.mc_address("gC") if mm else 0)
+        # The in-switch reduction pays off from four ranks on: measured on two B200s the owner-side backward takes
+        # 30 us with multimem.ld_reduce against 17 us with one peer load per element (the round trip through the
+        # switch's reduction unit is longer than a plain peer read), while with W ranks the peer-load variant moves
+        # W - 1 times the bytes.  DICE_B200_MULTIMEM_REDUCE=0/1 overrides the choice.
+        red = os.environ.get("DICE_B200_MULTIMEM_REDUCE")
+        mm_red = mm and (W >= 4 if red is None else red == "1")
+        self.mc = SimpleNamespace(Q=heap.mc_address("Q") if mm else 0, dQ=heap.mc_address("dQ") if mm_red else 0,
+                                  gR=heap.mc_address("gR") if mm_red else 0, gC=0)
 
         # dataset (replicated): pairs and CSR of known tails
         self.dataset = dataset

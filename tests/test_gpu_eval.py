@@ -164,8 +164,8 @@ def test_exact_mode_reproduces_fp32_ranks(nx, ny, D):
 
 @pytest.mark.parametrize("adversarial", [False, True])
 def test_two_stage_topk_over_a_large_table(adversarial):
-    """Tables above the two-stage limit: threshold from a prefix, one collecting pass; with rows sorted by norm the
-    prefix is not representative, the candidate lists overflow and the pass is repeated with the exact size."""
+    """Tables above the two-stage limit: threshold from a strided sample of the rows, then one collecting pass; the
+    sample stays representative when the rows are sorted by norm, and nothing in the call waits for the GPU."""
     nx, ny, D, k = 70, 300000, 128, 10
     x, y = _operands(nx, ny, D, 9)
     if adversarial:
