@@ -5,7 +5,9 @@ differences that matter on a B200: batches are built on the device from resident
 host→device copy of ``B × |E|`` labels), the loss stays on the device and is read back once per epoch instead
 of once per step (the reference calls ``loss.item()`` every batch, ``:146-149``), and when the model is one of
 the bilinear families trained with KvsAll / 1vsAll on a CUDA device the whole step is handed to the fused
-sm_100a engine (:mod:`dice_embeddings_b200.ops.fused_step`).
+sm_100a engine (:mod:`dice_embeddings_b200.ops.fused_step`); bilinear models whose query vector is produced by
+PyTorch modules (convolutional gates, normalisers, dropout) keep those in autograd and score against the entity
+table on the tensor cores through :mod:`dice_embeddings_b200.ops.hybrid_step`.
 
 Gradient accumulation follows the reference literally: with ``gradient_accumulation_steps = k > 1`` the
 gradients are only *zeroed* every ``k`` batches while the optimiser still steps every batch (``:50-58, 148``).
@@ -51,6 +53,14 @@ class TorchTrainer(AbstractTrainer):
         ds = getattr(loader, "dataset", None)
         if getattr(self.attributes, "scoring_technique", None) in SAMPLED:
             return build_sampled_engine(model, ds, self.attributes, self.device, strict=(backend == "cuda"))
+        # models whose query vector comes out of PyTorch modules (convolutional gates, normalisers, dropout, dual
+        # quaternions) keep those in autograd and hand only the scoring against the table to the tensor-core kernels
+        from ..ops.fused_step import fused_model_code
+        from ..ops.hybrid_step import build_hybrid_engine
+        if fused_model_code(model) is None:
+            hybrid = build_hybrid_engine(model, ds, self.attributes, self.device)
+            if hybrid is not None:
+                return hybrid
         return build_fused_engine(model, ds, self.attributes, self.device, strict=(backend == "cuda"))
 
     def fit(self, *args, train_dataloaders, **kwargs) -> None:

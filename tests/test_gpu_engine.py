@@ -61,6 +61,55 @@ def test_one_sgd_step_matches_autograd(name, label_mode, D):
         assert (d - d_ref).abs().max() / scale < 5e-2, n
 
 
+@pytest.mark.parametrize("name,extra", [("ConEx", {}), ("AConEx", {}), ("ConvQ", {}), ("AConvO", {}), ("DualE", {}),
+                                        ("ComplEx", {"normalization": "LayerNorm"}),
+                                        ("QMult", {"normalization": "BatchNorm1d"})])
+@pytest.mark.parametrize("D", [64, 256])
+def test_external_query_engine_matches_autograd(name, extra, D):
+    """Models whose query vector comes out of PyTorch modules (convolutional gates, normalisers, dual quaternions):
+    one SGD step through the tensor-core scoring function against the same step in plain autograd on dense labels."""
+    from dice_embeddings_b200.ops.hybrid_step import ExternalQueryEngine, build_hybrid_engine, hybrid_supported
+    lr = 50.0
+    NE, NR = 700, 15
+    tr = zipf_kg(NE, NR, 4000, seed=0)
+    ds = KvsAll(tr, NE, NR, label_smoothing_rate=0.1).to(DEV)
+    torch.manual_seed(0)
+    args = dict(model=name, embedding_dim=D, num_entities=NE, num_relations=NR, optim="SGD", learning_rate=lr,
+                scoring_technique="KvsAll", num_of_output_channels=2, kernel_size=3, **extra)
+    ref, _ = initialize_model(dict(args))
+    hyb, _ = initialize_model(dict(args))
+    hyb.load_state_dict(ref.state_dict())
+    for m in (ref, hyb):
+        m.to(DEV)
+        with torch.no_grad():
+            m.entity_embeddings.weight.mul_(0.3)
+            m.relation_embeddings.weight.mul_(0.3)
+        m.train()
+    assert hybrid_supported(hyb)
+    B = 384
+    idx = torch.randperm(len(ds), device=DEV)[:B]
+    x, y = ds.make_batch(idx)
+    start = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    opt = ref.configure_optimizers()
+    loss_ref = ref.training_step((x, y))
+    loss_ref.backward()
+    opt.step()
+    eng = build_hybrid_engine(hyb, ds, type("A", (), dict(scoring_technique="KvsAll", batch_size=B, lr=lr))(), DEV)
+    assert isinstance(eng, ExternalQueryEngine)
+    loss = eng.step((x, idx))
+    eng.sync_to_model()
+    assert abs(float(loss) - float(loss_ref.detach())) < 1e-2 * abs(float(loss_ref.detach()))
+    moved = 0
+    for (n, p_ref), (_, p) in zip(ref.named_parameters(), hyb.named_parameters()):
+        d_ref, d = p_ref.detach() - start[n], p.detach() - start[n]
+        scale = d_ref.abs().max()
+        if n == "conv2d.bias" or scale < 1e-5 * start[n].abs().max().clamp_min(1e-3):
+            continue   # the batch norm behind the convolution removes its bias: that gradient is rounding noise
+        moved += 1
+        assert (d - d_ref).abs().max() < 6e-2 * scale + 1e-6, n
+    assert moved >= 2
+
+
 @pytest.mark.parametrize("optim", ["Adam", "Adopt"])
 def test_loss_trajectory_with_graph_replay(optim):
     ds, ref, fused = _make("ComplEx", 128, optim, 0.02)
