@@ -317,6 +317,97 @@ __global__ void __launch_bounds__(256) compose_backward_owner_kernel(const BwdOw
   }
 }
 
+// ------------------------------------------------------------------------------------ two-shot all-reduce + update
+// Dense, replicated parameters (relation tables of models outside the sharded engines, convolution / linear / norm
+// weights): the flat gradient buffers of all ranks live in the symmetric heap.  For one bucket [lo, hi) of the flat
+// parameter vector every rank owns the slice lo + rank * len / W .. and, in ONE kernel,
+//   1. reduce-scatter: sums that slice of every rank's gradient (multimem.ld_reduce through the switch, or W peer loads),
+//   2. applies Adam / AdamW / SGD / ADOPT to its slice (moments are only ever touched for the slices a rank owns),
+//   3. all-gather: stores the updated parameters into every rank's copy (multimem.st, or W peer stores).
+// A rank therefore moves 1 / W of what a one-shot all-reduce would make it read.
+struct BucketParams {
+  float* const* p_dst;          // [W] flat parameter buffers of all ranks (peer pointers), used without multicast
+  float* p_mc;                  // multicast address of the parameter buffer, or null
+  const float* p_local;         // this rank's parameter buffer (read side)
+  const float* const* g_src;    // [W] gradient buffers of all ranks, used without multicast
+  const float* g_mc;            // multicast address of the gradient buffer, or null
+  float* m;
+  float* v;
+  const long long* step;
+  long long lo, hi;             // this rank's slice of the flat vector (multiples of 4)
+  int W, kind;
+  float lr, beta1, beta2, eps, weight_decay, grad_scale;
+  const int* status;
+};
+
+__global__ void __launch_bounds__(256) bucket_reduce_update_kernel(const BucketParams p) {
+  if (p.status != nullptr && *p.status != 0) return;
+  const long long t = *p.step + 1;
+  float inv_bc1 = 1.f, inv_sqrt_bc2 = 1.f;
+  if (p.kind <= 1) {
+    inv_bc1 = 1.f / (1.f - exp2f(static_cast<float>(t) * log2f(p.beta1)));
+    inv_sqrt_bc2 = rsqrtf(1.f - exp2f(static_cast<float>(t) * log2f(p.beta2)));
+  }
+  const float clip = sqrtf(sqrtf(static_cast<float>(t - 1)));
+  const bool first_step = (t == 1);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = p.lo + (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < p.hi; i += stride) {
+    float4 g;
+    if (p.g_mc != nullptr) {
+      g = multimem_ld_reduce_f32x4(p.g_mc + i);
+    } else {
+      g = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < p.W; ++k) {
+        const float4 x = *reinterpret_cast<const float4*>(p.g_src[k] + i);
+        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      }
+    }
+    g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
+    float4 w = *reinterpret_cast<const float4*>(p.p_local + i);
+    float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+    if (p.kind != 2) {
+      m = *reinterpret_cast<const float4*>(p.m + i);
+      v = *reinterpret_cast<const float4*>(p.v + i);
+    }
+    float gg[4] = {g.x, g.y, g.z, g.w}, ww[4] = {w.x, w.y, w.z, w.w}, mm[4] = {m.x, m.y, m.z, m.w},
+          vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float wd_g = (p.kind == 1) ? gg[u] : fmaf(p.weight_decay, ww[u], gg[u]);
+      float wq = ww[u];
+      if (p.kind == 1) wq *= 1.f - p.lr * p.weight_decay;
+      if (p.kind == 0 || p.kind == 1) {
+        mm[u] = fmaf(p.beta1, mm[u], (1.f - p.beta1) * wd_g);
+        vv[u] = fmaf(p.beta2, vv[u], (1.f - p.beta2) * wd_g * wd_g);
+        wq -= p.lr * inv_bc1 * mm[u] / (sqrtf(vv[u]) * inv_sqrt_bc2 + p.eps);
+      } else if (p.kind == 2) {
+        wq -= p.lr * wd_g;
+      } else if (first_step) {   // ADOPT: the first step only seeds the second moment
+        vv[u] = wd_g * wd_g;
+      } else {
+        float ng = wd_g / fmaxf(sqrtf(vv[u]), p.eps);
+        ng = fminf(fmaxf(ng, -clip), clip);
+        mm[u] += (1.f - p.beta1) * (ng - mm[u]);
+        vv[u] = fmaf(p.beta2, vv[u], (1.f - p.beta2) * wd_g * wd_g);
+        wq -= p.lr * mm[u];
+      }
+      ww[u] = wq;
+    }
+    if (p.kind != 2) {
+      *reinterpret_cast<float4*>(p.m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(p.v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    }
+    uint4 out;
+    out.x = __float_as_uint(ww[0]); out.y = __float_as_uint(ww[1]);
+    out.z = __float_as_uint(ww[2]); out.w = __float_as_uint(ww[3]);
+    if (p.p_mc != nullptr) {
+      multimem_st_16(p.p_mc + i, out);
+    } else {
+      for (int k = 0; k < p.W; ++k) *reinterpret_cast<uint4*>(p.p_dst[k] + i) = out;
+    }
+  }
+}
+
 template <int K>
 static int launch_lookup_vec(const LookupVecParams& p, cudaStream_t s) {
   const long long n = static_cast<long long>(p.B) * (p.D / K / 8);
@@ -417,4 +508,30 @@ extern "C" int dice_compose_backward_owner(int model, int normalize, const long 
     case 5: p.additive = 1; return launch_bwd_owner<1>(p, s);
     default: return -6;
   }
+}
+
+// Two-shot all-reduce of one slice [lo, hi) of a flat gradient vector fused with the optimiser update of that slice
+// and the broadcast of the updated parameters (see bucket_reduce_update_kernel).  lo, hi and every buffer must be
+// 16-byte aligned.  g_mc / p_mc != null select the NVSwitch multicast path, otherwise g_src / p_dst (device arrays of
+// W base pointers) are used.  grad_scale multiplies the summed gradient (1 / W for a mean over ranks).
+extern "C" int dice_bucket_reduce_update(int kind, float* const* p_dst, void* p_mc, const float* p_local,
+                                         const float* const* g_src, const void* g_mc, float* m, float* v,
+                                         const long long* step, long long lo, long long hi, int W, float lr,
+                                         float beta1, float beta2, float eps, float weight_decay, float grad_scale,
+                                         const int* status, void* stream) {
+  if (hi <= lo) return 0;
+  if ((lo & 3) || (hi & 3)) return -5;
+  if ((reinterpret_cast<uintptr_t>(p_mc) | reinterpret_cast<uintptr_t>(g_mc) | reinterpret_cast<uintptr_t>(p_local) |
+       reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15)
+    return -5;
+  BucketParams p{};
+  p.p_dst = p_dst; p.p_mc = static_cast<float*>(p_mc); p.p_local = p_local; p.g_src = g_src;
+  p.g_mc = static_cast<const float*>(g_mc); p.m = m; p.v = v; p.step = step; p.lo = lo; p.hi = hi; p.W = W;
+  p.kind = kind; p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = weight_decay;
+  p.grad_scale = grad_scale; p.status = status;
+  const long long n4 = (hi - lo) >> 2;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  bucket_reduce_update_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -222,6 +222,22 @@ def optimizer_step(kind: int, param, grad, m, v, shadow, step, lr, beta1, beta2,
           int(n_grad), int(grad_mc) or None, _ptr(status), others=(grad, m, v, shadow, step, status))
 
 
+def bucket_reduce_update(kind: int, p_table: torch.Tensor, p_mc: int, p_local: torch.Tensor, g_table: torch.Tensor,
+                         g_mc: int, m: torch.Tensor, v: torch.Tensor, step: torch.Tensor, lo: int, hi: int, W: int,
+                         lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, grad_scale: float,
+                         status: Optional[torch.Tensor] = None) -> None:
+    """Two-shot all-reduce of the slice ``[lo, hi)`` of a flat gradient vector fused with its optimiser update and the
+    broadcast of the updated parameters: the gradient slice is summed over the ``W`` ranks (``g_mc``:
+    ``multimem.ld_reduce``; else peer loads through ``g_table``), the optimiser is applied to ``p_local[lo:hi]`` with
+    the moments ``m`` / ``v``, and the result is stored into every rank's parameter buffer (``p_mc``: ``multimem.st``;
+    else peer stores through ``p_table``)."""
+    _req(p_local, torch.float32, "p_local")
+    _call("dice_bucket_reduce_update", p_local, int(kind), _ptr(p_table), int(p_mc) or None, _ptr(p_local),
+          _ptr(g_table), int(g_mc) or None, _ptr(m), _ptr(v), _ptr(step), int(lo), int(hi), int(W), float(lr),
+          float(beta1), float(beta2), float(eps), float(weight_decay), float(grad_scale), _ptr(status),
+          others=(p_table, g_table, m, v, step, status))
+
+
 class StepTail:
     """End of a training step as ONE launch: optimiser sweeps over up to three parameter segments and, with
     ``finish=True``, the closing of the step (loss = accumulator / count, accumulator cleared, step counter advanced)

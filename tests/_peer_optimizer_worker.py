@@ -19,10 +19,15 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     W = dist.get_world_size()
     ok, msg = True, []
-    for name, optim, lr in (("DistMult", "Adam", 0.01), ("DualE", "SGD", 0.5), ("Shallom", "Adopt", 0.01)):
+    # small buckets: several bucket launches per step, queued from the autograd hooks while backward still runs;
+    # ConEx has more than a dozen parameter tensors; the last case runs without the overlap (everything at step())
+    for name, optim, lr, bucket, overlap in (("DistMult", "Adam", 0.01, 4 << 20, True), ("DualE", "SGD", 0.5, 2048, True),
+                                             ("Shallom", "Adopt", 0.01, 4096, True), ("ConEx", "AdamW", 0.01, 8192, True),
+                                             ("ConEx", "Adam", 0.01, 1 << 20, False)):
         torch.manual_seed(0)
         args = dict(model=name, embedding_dim=32, num_entities=300, num_relations=7, optim=optim, learning_rate=lr,
-                    scoring_technique="NegSample" if name != "Shallom" else "KvsAll")
+                    scoring_technique="NegSample" if name != "Shallom" else "KvsAll", num_of_output_channels=2,
+                    kernel_size=3)
         ref, _ = initialize_model(dict(args))
         mdl, _ = initialize_model(dict(args))
         mdl.load_state_dict(ref.state_dict())
@@ -30,7 +35,11 @@ def main():
         g = torch.Generator().manual_seed(1)
         B = 64 * W
         opt_ref = ref.configure_optimizers()
-        popt = PeerAllReduceOptimizer(mdl, lr=lr, device=dev)
+        popt = PeerAllReduceOptimizer(mdl, lr=lr, device=dev, bucket_bytes=bucket, overlap=overlap)
+        if name == "ConEx":   # batch statistics differ between a whole batch and its slices: compare without them
+            for mod in list(ref.modules()) + list(mdl.modules()):
+                if isinstance(mod, torch.nn.modules.batchnorm._BatchNorm):
+                    mod.eval()
         for _ in range(4):
             if name == "Shallom":
                 x = torch.stack((torch.randint(0, 300, (B,), generator=g), torch.randint(0, 300, (B,), generator=g)), 1).to(dev)
@@ -52,7 +61,8 @@ def main():
             worst = max(worst, float((a - b).abs().max() / a.abs().max().clamp_min(1e-9)))
         good = worst < 2e-4
         ok &= good
-        msg.append(f"{name}/{optim}: max relative parameter difference {worst:.2e}")
+        msg.append(f"{name}/{optim}: {len(popt.buckets)} buckets, overlap {overlap}, multimem {popt.multimem}: "
+                   f"max relative parameter difference {worst:.2e}")
         del popt
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
