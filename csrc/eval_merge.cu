@@ -4,6 +4,7 @@
 // tiny next to the scoring GEMM that produced them.  The reference ranks on one device with a dense sort
 // (dicee/evaluation/evaluator.py:473-510) and takes torch.topk over all scores
 // (dicee/knowledge_graph_embeddings.py:390-403).
+#include "dice_b200.h"
 #include "ptx_sm100.cuh"
 
 namespace dice {

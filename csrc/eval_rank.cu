@@ -10,6 +10,7 @@
 // The same CTA structure as the training kernel is used (warp 0 TMA producer, warp 1 MMA issuer, warps 2..9
 // epilogue, one persistent CTA per SM over a contiguous range of (x-tile, y-tile) pairs) but there is no second
 // GEMM, so all 512 TMEM columns hold four S buffers.  Every wait is bounded and reports through the status word.
+#include "dice_b200.h"
 #include "ptx_sm100.cuh"
 #include "tile_map.cuh"
 #include "tma_host.cuh"

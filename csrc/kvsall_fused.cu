@@ -24,6 +24,7 @@
 // epilogue of the loss variant took 1.7x the time of the two GEMMs of a tile.
 // Every mbarrier wait is bounded; on a time-out the kernel records a status code, drains its TMA copies, frees
 // TMEM and returns.
+#include "dice_b200.h"
 #include "ptx_sm100.cuh"
 #include "tile_map.cuh"
 #include "tma_host.cuh"

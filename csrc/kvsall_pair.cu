@@ -23,6 +23,7 @@
 //
 // Reference math being replaced: the 4 `torch.mm` of ComplEx.forward_k_vs_all plus BCEWithLogitsLoss and their
 // autograd backward (dicee/models/complex.py:254-264, dicee/models/base_model.py:138).
+#include "dice_b200.h"
 #include "ptx_sm100.cuh"
 #include "tile_map.cuh"
 #include "tma_host.cuh"

@@ -15,6 +15,7 @@
 // holds an error (a timed-out barrier, a bad index), so that a rank whose peers are gone stops touching their memory.
 // The reference has no counterpart: its lookups are `nn.Embedding` gathers on one device and its only collective is
 // DDP's gradient all-reduce (dicee/models/base_model.py:371-383, dicee/trainer/torch_trainer_ddp.py:88).
+#include "dice_b200.h"
 #include "algebra.cuh"
 #include "ptx_sm100.cuh"
 

@@ -7,6 +7,7 @@
 //
 // The query vectors come from dice_lookup_compose (any of its algebras) and their gradient goes back through
 // dice_compose_backward, so one scoring kernel serves every model of the bilinear family plus the translation model.
+#include "dice_b200.h"
 #include "ptx_sm100.cuh"
 
 namespace dice {

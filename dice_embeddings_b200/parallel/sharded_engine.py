@@ -16,15 +16,15 @@ S1    ``p2p_barrier``
 3     ``kvsall_fused`` (query-stationary): partial ``dQ``      none (the partials of the whole batch stay local)
       of the local shard for all queries
 S2    ``p2p_barrier``
-4     ``compose_backward_owner``: the *owner of the head       ``multimem.ld_reduce.add`` of the query-gradient rows
-      row* sums that query's partial ``dQ`` over all ranks,     (summed inside the switch: the reduce-scatter of
-      applies the chain rule and adds the row gradient to       dQ); without multicast, W peer loads per element.
-      its own gradient shard                                    No row gradient crosses the fabric.
+4     ``compose_backward_owner``: the *owner of the head       peer loads of the query-gradient rows of all ranks
+      row* sums that query's partial ``dQ`` over all ranks,     (the reduce-scatter of dQ, done by its consumer);
+      applies the chain rule and adds the row gradient to       ``multimem.ld_reduce.add`` on request (slower for
+      its own gradient shard                                    scattered rows).  No row gradient crosses the fabric.
 5     ``optimizer_step`` over the local entity shard           none
 S3    ``p2p_barrier``
-6     ``optimizer_step`` of the replicated tables from the     ``multimem.ld_reduce`` (or peer loads) of every
-      sum of all ranks' gradient buffers; ``finish_step``       rank's buffer: the all-reduce folded into the update
-      sums the loss partials
+6     ``step_tail``: the replicated tables are updated from    peer loads (or ``multimem.ld_reduce``) of every
+      the sum of all ranks' gradient buffers and the last       rank's buffer: the all-reduce folded into the update
+      block sums the loss partials
 ====  =====================================================  ==================================================
 
 ``S3`` also orders the next step's peer reads of the updated entity rows, so a step needs three barriers.  Buffers
@@ -149,12 +149,12 @@ class ShardedKvsAllEngine:
                                    Q=heap.table("Q"), dQ=heap.table("dQ"), ids=heap.table("ids"),
                                    loss=heap.table("loss"), sig=heap.table("sig"))
         mm = self.multimem
-        # The in-switch reduction pays off from four ranks on: measured on two B200s the owner-side backward takes
-        # 30 us with multimem.ld_reduce against 17 us with one peer load per element (the round trip through the
-        # switch's reduction unit is longer than a plain peer read), while with W ranks the peer-load variant moves
-        # W - 1 times the bytes.  DICE_B200_MULTIMEM_REDUCE=0/1 overrides the choice.
-        red = os.environ.get("DICE_B200_MULTIMEM_REDUCE")
-        mm_red = mm and (W >= 4 if red is None else red == "1")
+        # Measured on B200s (owner-side backward of 4096 owned queries, d = 256): multimem.ld_reduce 30 us against 17 us
+        # with peer loads at two ranks, 52 us against 25 us at four.  The 16-byte in-switch reductions of scattered
+        # rows cost more than reading W - 1 peer copies, so the reduce-scatter of dQ and the all-reduce of the
+        # replicated gradients use peer loads unless DICE_B200_MULTIMEM_REDUCE=1; the all-gather of Q keeps
+        # multimem.st (one store instead of W).
+        mm_red = mm and os.environ.get("DICE_B200_MULTIMEM_REDUCE") == "1"
         self.mc = SimpleNamespace(Q=heap.mc_address("Q") if mm else 0, dQ=heap.mc_address("dQ") if mm_red else 0,
                                   gR=heap.mc_address("gR") if mm_red else 0, gC=0)
 
