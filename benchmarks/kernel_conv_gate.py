@@ -1,17 +1,21 @@
 """Time the fused convolution + batch normalisation + ReLU (forward and backward) against the PyTorch layers.
 
-    python -m dice_embeddings_b200.ops.profile_conv_gate --batch 16384 --rows 4 --cols 128 --channels 8
+    python benchmarks/kernel_conv_gate.py --batch 16384 --rows 4 --cols 128 --channels 8
 
 Times are CUDA-event times after warm-up.  ``--fused_only`` skips the layers (for hardware-counter captures).
 """
 from __future__ import annotations
 
 import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 
 import torch
 from torch import nn
 
-from . import conv_gate
+from dice_embeddings_b200.ops import conv_gate
 
 
 def _time(fn, iters: int) -> float:

@@ -1,4 +1,4 @@
-"""Stand-alone timing of the ranking kernel: ``python -m dice_embeddings_b200.ops.profile_eval``.
+"""Stand-alone timing of the ranking kernel: ``python benchmarks/kernel_eval.py``.
 
 Times ``eval_rank`` (counting mode and top-k mode) with CUDA events after warm-up, flushing L2 between launches, and
 reports the achieved tensor throughput (one GEMM of ``2·B·|E|·D`` FLOP per launch) as a fraction of the cuBLAS bf16
@@ -8,12 +8,16 @@ captures of this kernel."""
 from __future__ import annotations
 
 import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
 
 import torch
 
-from ..utils.profiling import measured_peaks
-from . import kernels as K
-from .eval_rank import FusedRanker
+from dice_embeddings_b200.utils.profiling import measured_peaks
+from dice_embeddings_b200.ops import kernels as K
+from dice_embeddings_b200.ops.eval_rank import FusedRanker
 
 
 def main():

@@ -1,4 +1,4 @@
-"""Stand-alone timing of the fused scoring kernel: ``python -m dice_embeddings_b200.ops.profile_fused``.
+"""Stand-alone timing of the fused scoring kernel: ``python benchmarks/kernel_fused.py``.
 
 Times both roles of ``kvsall_fused`` (entity-stationary with loss, query-stationary) with CUDA events after
 warm-up, flushing L2 between launches, and reports the achieved tensor throughput (two GEMMs of
@@ -11,9 +11,13 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
 
-from . import kernels as K
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a source checkout
+
+from dice_embeddings_b200.ops import kernels as K
 
 
 def main():
@@ -36,7 +40,7 @@ def main():
     mx = torch.zeros(a.nx, K.mask_stride(a.ny), dtype=torch.int32, device=dev) if a.mask else None
     my = torch.zeros(a.ny, K.mask_stride(a.nx), dtype=torch.int32, device=dev) if a.mask else None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     peak, tag = 1590.0, "of fallback"
     pk = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.isfile(pk):
@@ -66,15 +70,10 @@ def main():
               f"{tf / peak:.2f} {tag} ({peak:.0f})")
         if a.trace:
             buf = torch.zeros(64, 8, dtype=torch.int64, device=dev)
-            pair = a.d == 256 and K.pair_kernel_enabled()
-            if pair:
-                tr["buf"] = buf
-            else:
-                K.kvsall_set_trace(buf)
+            tr["buf"] = buf
             fn()
             torch.cuda.synchronize()
             tr["buf"] = None
-            K.kvsall_set_trace(None)
             t = buf.cpu()
             t0 = int(t[0, 0])
             print("  tile | Y load issued | S gemm issued | 2nd gemm issued | epi sees S | epi wrote dS | out drained"

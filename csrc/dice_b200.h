@@ -27,17 +27,17 @@ extern "C" {
 // ---------------------------------------------------------------------------------------- tensor-core scoring
 // out[x_rows, D] += scale * (sigmoid(X Yᵀ) - label) * Y and, with_loss, *loss += sum softplus(s) - label * s; x, y bf16
 // row-major, D in {64, 128, 256}.  Labels: `base` everywhere, base + pos_delta where the bit mask (row stride
-// mask_stride words, a multiple of 4) is set.  out_table (optional) scatters result rows to per-block owners.
+// mask_stride words, a multiple of 4) is set.  out_table (optional) scatters result rows to per-block owners; trace
+// (optional) receives int64[64][8] pipeline stamps of CTA 0.
 int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss,
                       float base, float scale, int with_loss, int* status, int num_ctas, float* const* out_table,
-                      int out_block_rows, const unsigned int* mask, int mask_stride, float pos_delta, void* stream);
+                      int out_block_rows, const unsigned int* mask, int mask_stride, float pos_delta,
+                      long long* trace, void* stream);
 // CTA-pair variant (tcgen05.mma.cta_group::2), D = 256.  loss_share -1 / 0 / 1: all / even / odd 256 x 256 blocks add
 // their loss terms in this launch.  trace: optional int64[64][8] pipeline stamps.
 int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss, float base,
                      float scale, int with_loss, int* status, int num_pairs, const unsigned int* mask,
                      int mask_stride, float pos_delta, int loss_share, long long* trace, void* stream);
-// Registers (or clears, with null) an int64[64][8] buffer for per-tile stamps of CTA 0 of dice_kvsall_fused launches.
-int dice_kvsall_set_trace(long long* buffer);
 
 // Filtered-rank counting / running top-k over X Yᵀ without storing it (see csrc/eval_rank.cu).
 int dice_eval_rank(const void* x, int x_rows, const void* y, int y_rows, int D, const float* target,

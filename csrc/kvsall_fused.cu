@@ -497,23 +497,16 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 
 }  // namespace dice
 
-// Pipeline diagnostics: when a device buffer of 64 * 8 int64 is registered here, CTA 0 of every following launch
-// writes clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
-// 4 epilogue wrote dS, 5 out tile drained).  Pass null to switch it off again.
-static long long* g_trace_buffer = nullptr;
-extern "C" int dice_kvsall_set_trace(long long* buffer) {
-  g_trace_buffer = buffer;
-  return 0;
-}
-
 // x, y: bf16 row-major with 16-byte aligned base; D in {64, 128, 256}.  out must be zero-initialised (or hold a
 // running sum) by the caller; *loss likewise.  With out_table != null (a device array of base pointers, one per
 // block of out_block_rows rows, possibly in peer memory) the result rows are scattered to their owners instead.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
-// launch; device-side failures are reported through *status.
+// launch; device-side failures are reported through *status.  trace (optional, device int64 [64][8]): CTA 0 writes
+// clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
+// 4 epilogue wrote dS, 5 out tile drained) for pipeline diagnostics.
 extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out,
                                  double* loss, float base, float scale, int with_loss, int* status, int num_ctas,
                                  float* const* out_table, int out_block_rows, const unsigned int* mask,
-                                 int mask_stride, float pos_delta, void* stream) {
+                                 int mask_stride, float pos_delta, long long* trace, void* stream) {
   using namespace dice;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
@@ -540,7 +533,7 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.mask = mask;
   p.mask_stride = mask_stride;
   p.pos_delta = pos_delta;
-  p.trace = g_trace_buffer;
+  p.trace = trace;
   if (mask != nullptr && ((mask_stride & 3) || (reinterpret_cast<uintptr_t>(mask) & 7))) return -5;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;

@@ -8,6 +8,7 @@ three flags are additions of this framework (``--compute_dtype``, ``--kernel_bac
 from __future__ import annotations
 
 import argparse
+from typing import Optional
 import json
 
 MODEL_CHOICES = [
@@ -104,9 +105,56 @@ def get_default_arguments(description=None):
     return parser.parse_args(description)
 
 
+def _relaunch_on_all_gpus(args, argv) -> Optional[int]:
+    """``--trainer PL`` is the reference's command-line default and means "all visible GPUs, data parallel" there
+    (Lightning starts one process per device; ``dicee/trainer/dice_trainer.py:75-92``).  The counterpart here: when
+    several GPUs are visible and the process was not started by ``torchrun``, the command re-launches itself under
+    ``torch.distributed.run`` with one rank per GPU and the data-parallel trainer (``torchDDP``, which picks the
+    row-sharded engine when the model is covered).  ``DICE_B200_SINGLE_PROCESS=1`` keeps the single-device run."""
+    import os
+    import subprocess
+    import sys
+    if args.trainer != "PL" or "RANK" in os.environ or os.environ.get("DICE_B200_SINGLE_PROCESS") == "1":
+        return None
+    try:
+        import torch
+        n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    except Exception:   # noqa: BLE001
+        n = 0
+    if n < 2:
+        return None
+    if args.path_to_store_single_run is None:   # every rank has to agree on the run folder
+        import datetime
+        args_dir = os.path.join(args.storage_path, datetime.datetime.now().strftime("%Y-%m-%d %H-%M-%S.%f"))
+        extra = ["--path_to_store_single_run", args_dir]
+    else:
+        extra = []
+    raw = list(sys.argv[1:] if argv is None else argv)
+    out, skip = [], False
+    for tok in raw:                              # replace the trainer flag
+        if skip:
+            skip = False
+            continue
+        if tok == "--trainer":
+            skip = True
+            continue
+        if tok.startswith("--trainer="):
+            continue
+        out.append(tok)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
+           f"--nproc-per-node={n}", "-m", "dice_embeddings_b200", *out, "--trainer", "torchDDP", *extra]
+    print(f"--trainer PL with {n} visible GPUs: starting one rank per GPU\n  " + " ".join(cmd))
+    return subprocess.call(cmd)
+
+
 def main(argv=None):
     from .executor import ContinuousExecute, Execute
     args = get_default_arguments(argv)
+    rc = _relaunch_on_all_gpus(args, argv)
+    if rc is not None:
+        if rc != 0:
+            raise SystemExit(rc)
+        return None
     if args.continual_learning:
         return ContinuousExecute(args).continual_start()
     return Execute(args).start()

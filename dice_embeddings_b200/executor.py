@@ -52,8 +52,11 @@ def read_or_load_kg(args, cls=KG):
 
 class Execute:
     def __init__(self, args, continuous_training: bool = False):
-        self.distributed = getattr(args, "trainer", None) in _DISTRIBUTED_TRAINERS and \
-            ("RANK" in os.environ or dist.is_initialized())
+        trainer = getattr(args, "trainer", None)
+        launched = "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1
+        # "PL" started under torchrun with several ranks is data parallel, as with the reference's Lightning trainer
+        self.distributed = (trainer in _DISTRIBUTED_TRAINERS and ("RANK" in os.environ or dist.is_initialized())) \
+            or (trainer == "PL" and launched)
         self._setup_distributed_training()
         self.args = preprocess_args(args)
         seed_everything(args.random_seed)

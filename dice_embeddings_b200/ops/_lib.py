@@ -103,7 +103,7 @@ _d = ctypes.c_double
 
 
 class _Sigs:
-    dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _p, _i, _f, _p]
+    dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _p, _i, _f, _p, _p]
     dice_kvsall_pair = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _f, _i, _p, _p]
     dice_build_label_masks = [_p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
     dice_build_label_masks_flat = [_p, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _l, _l, _p, _p]
@@ -121,7 +121,6 @@ class _Sigs:
     dice_cast_bf16 = [_p, _p, _l, _p]
     dice_finish_step = [_p, _p, _d, _p, _p, _i, _p, _p]
     dice_p2p_barrier = [_p, _i, _i, _p, _p, ctypes.c_uint, _p]
-    dice_kvsall_set_trace = [_p]
     dice_timestamp = [_p, _p]
     dice_uniform_int = [_p, _l, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _l, _l, _p]
     dice_neg_sample = [_p, _i, _i, _l, ctypes.c_ulonglong, ctypes.c_ulonglong, _p, _i, _f, _f, _p, _p, _p, _p, _p, _p]

@@ -103,8 +103,8 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
         return
     _call("dice_kvsall_fused", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
           float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas), _ptr(out_table),
-          int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta),
-          others=(y, out, loss_acc, status, mask))
+          int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
+          others=(y, out, loss_acc, status, mask, trace))
 
 
 def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.Tensor, W: int, num_entities: int,
@@ -294,15 +294,6 @@ def timestamp(slots: torch.Tensor, index: int) -> None:
     """Write the GPU nanosecond timer into ``slots[index]`` (int64) in stream order; capturable in a CUDA graph."""
     _req(slots, torch.int64, "slots")
     _call("dice_timestamp", slots, slots.data_ptr() + 8 * int(index))
-
-
-def kvsall_set_trace(buffer: Optional[torch.Tensor]) -> None:
-    """Register (or clear with ``None``) a ``[64, 8]`` int64 device buffer receiving per-tile clock stamps of CTA 0 of
-    every following ``kvsall_fused`` launch (pipeline diagnostics)."""
-    if buffer is not None:
-        _req(buffer, torch.int64, "trace buffer")
-        assert buffer.numel() >= 512
-    _lib.lib().dice_kvsall_set_trace(_ptr(buffer))
 
 
 def uniform_int(out: torch.Tensor, high: int, seed: int, offset: int = 0, step: Optional[torch.Tensor] = None) -> None:

@@ -6,8 +6,11 @@ Trainer names map as follows:
 
 ========================  ==========================================================================
 ``torchCPUTrainer``       :class:`TorchTrainer` on CPU (or on ``cuda:<gpus>`` when ``args.gpus`` is set)
-``PL``                    :class:`TorchTrainer` on ``cuda:0`` when a GPU exists, else CPU.  The reference
-                          delegates to PyTorch-Lightning (``:75-92``); Lightning is not a dependency here
+``PL``                    one GPU or none: :class:`TorchTrainer` (``cuda:0`` / CPU).  Several GPUs: the command line
+                          re-launches itself with one rank per GPU under ``torch.distributed.run`` and the
+                          ``torchDDP`` trainer (``cli._relaunch_on_all_gpus``); under ``torchrun`` the name is
+                          an alias of ``torchDDP``.  The reference delegates to PyTorch-Lightning, which starts
+                          DDP on several GPUs (``:75-92``); Lightning is not a dependency here
 ``torchDDP``              :class:`TorchDDPTrainer` — one process per device under ``torchrun``
 ``TP``                    :class:`TensorParallel` — embedding-dimension split over the local devices
 ``Sharded``               :class:`ShardedTrainer` — row-sharded entity table with fused kernels
@@ -37,7 +40,7 @@ def initialize_trainer(args, callbacks: List):
     if name == "TP":
         from .tensor_parallel import TensorParallel
         return TensorParallel(args, callbacks=callbacks)
-    if name == "torchDDP":
+    if name == "torchDDP" or (name == "PL" and int(os.environ.get("WORLD_SIZE", "1")) > 1):
         from .ddp import TorchDDPTrainer
         return TorchDDPTrainer(args, callbacks=callbacks)
     if name == "Sharded":

@@ -150,3 +150,16 @@ def test_heartbeat_over_the_process_group_store_reports_a_silent_rank(tmp_path):
     script.write_text(HB_WORKER)
     res = _torchrun(2, [str(script)], 29673, timeout=120, env_extra={"DICE_ROOT": ROOT})
     assert "RANK_FAILURE_SEEN 1" in res.stdout and "NO_FAILURE" not in res.stdout, res.stdout[-1500:] + res.stderr[-1500:]
+
+
+def test_pl_trainer_under_torchrun_is_data_parallel(umls_like_dir, tmp_path):
+    """The reference's default trainer name means "all devices, data parallel": started with two ranks it must train
+    as the data-parallel trainer does (one run folder, rank 0 writes it)."""
+    out = tmp_path / "pl"
+    res = _torchrun(2, ["-m", "dice_embeddings_b200", "--dataset_dir", umls_like_dir, "--path_to_store_single_run",
+                        str(out), "--model", "DistMult", "--scoring_technique", "KvsAll", "--trainer", "PL",
+                        "--num_epochs", "30", "--batch_size", "128", "--optim", "Adam", "--embedding_dim", "32",
+                        "--lr", "0.1"], 29674)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    rep = json.load(open(out / "eval_report.json"))
+    assert rep["Train"]["MRR"] > 0.5 and os.path.isfile(out / "model.pt")
