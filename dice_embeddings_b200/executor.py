@@ -173,6 +173,11 @@ class Execute:
         self.write_report()
         if self.args.eval_model is None or self.knowledge_graph is None or isinstance(self.knowledge_graph, np.memmap):
             return {**self.report}
+        # the model was stored from the host; the evaluation goes back to the device it was trained on, where the
+        # ranking runs on the tensor cores (the reference evaluates on the CPU, dicee/executer.py:256-257)
+        dev = getattr(getattr(self.trainer, "trainer", None), "device", None)
+        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+            self.trained_model.to(dev)
         self.evaluator.eval(dataset=self.knowledge_graph, trained_model=self.trained_model,
                             form_of_labelling=form_of_labelling)
         self.write_report()
