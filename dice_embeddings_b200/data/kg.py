@@ -23,6 +23,7 @@ reference's pickled dictionaries on demand.
 from __future__ import annotations
 
 import glob
+import atexit
 import os
 import pickle
 import sys
@@ -416,10 +417,23 @@ class KG:
         if self.test_set is not None:
             np.save(os.path.join(p, "test_set.npy"), self.test_set)
 
-    def save_filter_vocab_pickles(self, path: Optional[str] = None) -> None:
-        """Write ``er_vocab.p`` / ``re_vocab.p`` / ``ee_vocab.p`` (reference ``preprocess.py:58-60``)."""
+    def save_filter_vocab_pickles(self, path: Optional[str] = None, background: bool = False) -> None:
+        """Write ``er_vocab.p`` / ``re_vocab.p`` / ``ee_vocab.p`` (reference ``preprocess.py:58-60``).
+
+        ``background=True`` hands the job to a helper process (``data/vocab_writer.py`` run as a script on a copy of
+        the filter triples) and returns at once; :meth:`wait_for_vocab_pickles` joins it.  Nothing in this framework
+        reads the dictionaries while a run is in progress: filtering uses the CSR form."""
         path = path or self.path_for_serialization
         if path is None or not self.eval_model:
+            return
+        if background and self.er_vocab is None and getattr(self, "_filter_data", None) is not None:
+            import subprocess
+            import sys
+            from . import vocab_writer
+            tmp = os.path.join(path, f".filter_triples.{os.getpid()}.npy")
+            np.save(tmp, np.asarray(self._filter_data))
+            self._vocab_writer = subprocess.Popen([sys.executable, os.path.abspath(vocab_writer.__file__), tmp, path])
+            atexit.register(self.wait_for_vocab_pickles)
             return
         self.materialize_dict_vocab()
         for name in ("er_vocab", "re_vocab", "ee_vocab"):
@@ -427,6 +441,15 @@ class KG:
             if obj is not None:
                 with open(os.path.join(path, name + ".p"), "wb") as f:
                     pickle.dump(obj, f)
+
+    def wait_for_vocab_pickles(self) -> None:
+        """Join the helper process of :meth:`save_filter_vocab_pickles`; falls back to writing them here if it failed."""
+        proc = getattr(self, "_vocab_writer", None)
+        if proc is None:
+            return
+        self._vocab_writer = None
+        if proc.wait() != 0:
+            self.save_filter_vocab_pickles(proc.args[3])
 
     def load(self) -> None:
         p = self.path_for_deserialization

@@ -127,11 +127,7 @@ def ee_csr(triples: np.ndarray, num_entities: int) -> PairCSR:
     return PairCSR.build(triples[:, 0], triples[:, 2], triples[:, 1], num_entities)
 
 
-def _dict_vocab(a, b, v) -> Dict[Tuple[int, int], List[int]]:
-    out: Dict[Tuple[int, int], List[int]] = defaultdict(list)
-    for x, y, z in zip(a.tolist(), b.tolist(), v.tolist()):
-        out[(x, y)].append(z)
-    return out
+from .vocab_writer import dict_vocab as _dict_vocab  # noqa: E402  (pure NumPy, shared with the helper process)
 
 
 def get_er_vocab(data: np.ndarray) -> Dict[Tuple[int, int], List[int]]:
@@ -150,25 +146,6 @@ def get_ee_vocab(data: np.ndarray) -> Dict[Tuple[int, int], List[int]]:
     """(head, tail) → list of relations (reference ``static_funcs.py:111-126``)."""
     data = np.asarray(data)
     return _dict_vocab(data[:, 0], data[:, 2], data[:, 1])
-
-
-def create_constraints(triples: np.ndarray):
-    """Domain / range of every relation and their complements.
-
-    Returns ``(domain_constraints, range_constraints, domain, range)`` as dicts
-    relation → list of entity ids, where the *constraints* are the entities that never
-    occur in that slot (reference ``dicee/static_preprocess_funcs.py:76-108``).
-    """
-    triples = np.asarray(triples)
-    ents = np.unique(np.concatenate([triples[:, 0], triples[:, 2]]))
-    dom, rng = {}, {}
-    for r in np.unique(triples[:, 1]).tolist():
-        sel = triples[triples[:, 1] == r]
-        dom[r] = np.unique(sel[:, 0])
-        rng[r] = np.unique(sel[:, 2])
-    dom_c = {r: np.setdiff1d(ents, d).tolist() for r, d in dom.items()}
-    rng_c = {r: np.setdiff1d(ents, d).tolist() for r, d in rng.items()}
-    return dom_c, rng_c, {r: d.tolist() for r, d in dom.items()}, {r: d.tolist() for r, d in rng.items()}
 
 
 def create_constraints(triples: np.ndarray):

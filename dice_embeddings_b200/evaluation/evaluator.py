@@ -53,7 +53,9 @@ class Evaluator:
         path = getattr(self.args, "full_storage_path", None)
         if path and not self._pickles_written and not self.during_training and hasattr(dataset, "save_filter_vocab_pickles"):
             if (dataset.num_entities or 0) <= 2_000_000:  # dict export is a convenience for small graphs
-                dataset.save_filter_vocab_pickles(path)
+                # a helper process writes them while the ranking runs; ``dataset.wait_for_vocab_pickles()`` joins it
+                # (the executor does so before it returns, and the dataset does at interpreter exit)
+                dataset.save_filter_vocab_pickles(path, background=True)
             self._pickles_written = True
 
     def _ee(self):

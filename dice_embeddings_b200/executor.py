@@ -180,6 +180,8 @@ class Execute:
             self.trained_model.to(dev)
         self.evaluator.eval(dataset=self.knowledge_graph, trained_model=self.trained_model,
                             form_of_labelling=form_of_labelling)
+        if hasattr(self.knowledge_graph, "wait_for_vocab_pickles"):
+            self.knowledge_graph.wait_for_vocab_pickles()   # the run folder is complete when start() returns
         self.write_report()
         return {**self.report, **self.evaluator.report}
 
