@@ -32,7 +32,8 @@ extern "C" {
 int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss,
                       float base, float scale, int with_loss, int* status, int num_ctas, float* const* out_table,
                       int out_block_rows, const unsigned int* mask, int mask_stride, float pos_delta,
-                      long long* trace, void* stream);
+                      long long* trace, int score_mode, const float* x_bias, const float* y_bias, float* x_dsum,
+                      float margin, void* stream);
 // CTA-pair variant (tcgen05.mma.cta_group::2), D = 256.  loss_share -1 / 0 / 1: all / even / odd 256 x 256 blocks add
 // their loss terms in this launch.  trace: optional int64[64][8] pipeline stamps.
 int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss, float base,

@@ -54,6 +54,11 @@ struct KvsAllParams {
   int mask_stride;      // (a multiple of 4, so the two words a thread needs per tile are one aligned 8-byte load)
   float pos_delta;      // label(positive) - base
   long long* trace;     // optional [64 tiles][8] clock64 stamps written by CTA 0 (pipeline diagnostics), else null
+  // SCORE != 0: the logit is a function of the dot product and one scalar per row of X and of Y
+  const float* x_bias;  // [nx_tiles * 128] or null (= 0): SCORE 1 bias of row x; SCORE 2 squared norm of row x
+  const float* y_bias;  // [ny_tiles * 128] or null (= 0), padded to whole tiles: the same for the rows of Y
+  float* x_dsum;        // optional [x_rows]: += scale * sum over y of the value fed to the second GEMM
+  float margin;         // SCORE 2: logit = margin - sqrt(|x|^2 + |y|^2 - 2 x.y)
 };
 
 template <int D>
@@ -129,16 +134,31 @@ __device__ __forceinline__ float log1p_over_e(float e) {
 
 // One thread's 32 logits of a tile: dS = sigmoid(s) - label packed as bf16 pairs (low half = even column) and, with
 // LOSS, the BCE-with-logits terms added to loss.  FULL: all 32 columns are valid entries of Y.
-template <bool LOSS, bool MASK, bool FULL>
+// SCORE selects how the logit follows from the dot product a = x.y of the tensor cores:
+//   0  s = a
+//   1  s = a + xb + yb[col]                     (per-query scalar terms of the Clifford models)
+//   2  s = margin - sqrt(xb + yb[col] - 2 a)    (translational distance; xb, yb are squared norms).  The value handed
+//      to the second GEMM is then dS / distance, and the caller subtracts (sum of those values) * x from the result:
+//      d s / d x = (y - x) / distance.
+// dsum accumulates the values handed to the second GEMM (SCORE != 0 only).
+template <bool LOSS, bool MASK, bool FULL, int SCORE>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t mword, float base, float label_pos,
-                                               int y_valid, uint32_t (&packed)[16], float& loss) {
+                                               int y_valid, uint32_t (&packed)[16], float& loss, float xb,
+                                               const float* __restrict__ yb, float margin, float& dsum) {
   constexpr float LOG2E = 1.4426950408889634f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float ds2[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const float s = __uint_as_float(r[i + u]);
+      float s = __uint_as_float(r[i + u]);
+      float gscale = 1.f;
+      if constexpr (SCORE == 1) s += xb + yb[i + u];
+      if constexpr (SCORE == 2) {
+        const float d2 = fmaxf(fmaf(-2.f, s, xb + yb[i + u]), 1e-12f);
+        gscale = rsqrtf(d2);
+        s = fmaf(-d2, gscale, margin);
+      }
       float label = base;
       if constexpr (MASK) label = ((mword >> (i + u)) & 1u) ? label_pos : base;
       float sig;
@@ -154,7 +174,9 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
         sig = fmaf(fast_tanh(0.5f * s), 0.5f, 0.5f);
       }
       float d = sig - label;
+      if constexpr (SCORE == 2) d *= gscale;
       if (!FULL && i + u >= y_valid) d = 0.f;
+      if constexpr (SCORE != 0) dsum += d;
       ds2[u] = d;
     }
     __nv_bfloat162 v = __floats2bfloat162_rn(ds2[0], ds2[1]);  // .x (low 16 bits) = even K element
@@ -162,7 +184,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
   }
 }
 
-template <int D, bool LOSS, bool MASK>
+template <int D, bool LOSS, bool MASK, int SCORE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
                     const KvsAllParams p) {
@@ -377,6 +399,11 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int x_global = x * BLOCK_X + row;
       const bool valid_x = x_global < p.x_rows;
       float seg_loss = 0.f;
+      float seg_dsum = 0.f;
+      float xb = 0.f;
+      if constexpr (SCORE != 0) {
+        if (valid_x && p.x_bias != nullptr) xb = p.x_bias[x_global];
+      }
 
       // label words are fetched one tile ahead: the strided global load would otherwise sit on the critical path
       const uint32_t* mrow = nullptr;
@@ -393,6 +420,22 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if constexpr (MASK) {
           if (valid_x && t + 1 < n) mnext = mrow[(t + 1) * 4];
         }
+        // the 32 per-column scalars of this chunk: the same addresses in every lane (a broadcast from L1), fetched
+        // before the wait for S
+        float yb[SCORE != 0 ? 32 : 1];
+        if constexpr (SCORE != 0) {
+          if (p.y_bias != nullptr) {
+            const float4* src = reinterpret_cast<const float4*>(p.y_bias + static_cast<size_t>(y0 + t) * BLOCK_Y + cg * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 v = __ldg(src + i);
+              yb[4 * i] = v.x; yb[4 * i + 1] = v.y; yb[4 * i + 2] = v.z; yb[4 * i + 3] = v.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) yb[i] = 0.f;
+          }
+        }
         if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1, s_abort)) { ok = false; break; }
         if (warp == 2 && lane == 0) stamp(g, 3);
         tc_fence_after();
@@ -403,9 +446,11 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tc_wait_ld();
         uint32_t packed[16];
         if (y_valid >= 32) {
-          epilogue_chunk<LOSS, MASK, true>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+          epilogue_chunk<LOSS, MASK, true, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_loss, xb, yb,
+                                                  p.margin, seg_dsum);
         } else {
-          epilogue_chunk<LOSS, MASK, false>(r, mword, p.base, label_pos, y_valid, packed, seg_loss);
+          epilogue_chunk<LOSS, MASK, false, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_loss, xb, yb,
+                                                   p.margin, seg_dsum);
         }
         tmem_st16(s_addr, packed);
         tc_wait_st();
@@ -416,6 +461,9 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       }
       if (!ok) break;
       if (valid_x) loss_acc += seg_loss;
+      if constexpr (SCORE != 0) {
+        if (valid_x && p.x_dsum != nullptr) atomicAdd(p.x_dsum + x_global, seg_dsum * p.scale);
+      }
 
       // drain the accumulated out tile of this segment: this warp owns D / 4 of its columns
       if (!mbar_wait_bounded(dx_full, seg & 1, s_abort)) { ok = false; break; }
@@ -479,10 +527,10 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int D, bool LOSS, bool MASK>
+template <int D, bool LOSS, bool MASK, int SCORE>
 static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllParams& p, int num_ctas,
                   cudaStream_t stream) {
-  auto kern = kvsall_fused_kernel<D, LOSS, MASK>;
+  auto kern = kvsall_fused_kernel<D, LOSS, MASK, SCORE>;
   static bool configured[64] = {false};   // the attribute is per device: one flag per device ordinal
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
@@ -503,10 +551,17 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 // launch; device-side failures are reported through *status.  trace (optional, device int64 [64][8]): CTA 0 writes
 // clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
 // 4 epilogue wrote dS, 5 out tile drained) for pipeline diagnostics.
+// score_mode 0: logit = x.y.  1: logit = x.y + x_bias[x] + y_bias[y].  2: logit = margin - sqrt(x_bias[x] + y_bias[y]
+// - 2 x.y) with the squared row norms as x_bias / y_bias; out then holds sum_y w y with w = dS / distance and the
+// caller subtracts x_dsum[x] * x.  Modes 1 and 2 need a label mask; x_bias / y_bias (either may be null = zeros) must
+// be readable up to the next multiple of 128 rows; x_dsum (optional, [x_rows], caller-zeroed) receives scale * the row
+// sums of the values fed to the second GEMM (mode 1: the gradient of x_bias).
 extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out,
                                  double* loss, float base, float scale, int with_loss, int* status, int num_ctas,
                                  float* const* out_table, int out_block_rows, const unsigned int* mask,
-                                 int mask_stride, float pos_delta, long long* trace, void* stream) {
+                                 int mask_stride, float pos_delta, long long* trace, int score_mode,
+                                 const float* x_bias, const float* y_bias, float* x_dsum, float margin,
+                                 void* stream) {
   using namespace dice;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
@@ -534,6 +589,12 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.mask_stride = mask_stride;
   p.pos_delta = pos_delta;
   p.trace = trace;
+  p.x_bias = x_bias;
+  p.y_bias = y_bias;
+  p.x_dsum = x_dsum;
+  p.margin = margin;
+  if (score_mode < 0 || score_mode > 2 || (score_mode != 0 && mask == nullptr)) return -6;
+  if (reinterpret_cast<uintptr_t>(y_bias) & 15) return -5;
   if (mask != nullptr && ((mask_stride & 3) || (reinterpret_cast<uintptr_t>(mask) & 7))) return -5;
   if (num_ctas <= 0) {
     int dev = 0, sms = 148;
@@ -548,8 +609,12 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   const bool mk = mask != nullptr;
 #define DICE_DISPATCH(DD)                                                                        \
   case DD:                                                                                       \
-    if (wl) return mk ? launch<DD, true, true>(tx, ty, p, num_ctas, s) : launch<DD, true, false>(tx, ty, p, num_ctas, s); \
-    return mk ? launch<DD, false, true>(tx, ty, p, num_ctas, s) : launch<DD, false, false>(tx, ty, p, num_ctas, s);
+    if (score_mode == 1)                                                                         \
+      return wl ? launch<DD, true, true, 1>(tx, ty, p, num_ctas, s) : launch<DD, false, true, 1>(tx, ty, p, num_ctas, s); \
+    if (score_mode == 2)                                                                         \
+      return wl ? launch<DD, true, true, 2>(tx, ty, p, num_ctas, s) : launch<DD, false, true, 2>(tx, ty, p, num_ctas, s); \
+    if (wl) return mk ? launch<DD, true, true, 0>(tx, ty, p, num_ctas, s) : launch<DD, true, false, 0>(tx, ty, p, num_ctas, s); \
+    return mk ? launch<DD, false, true, 0>(tx, ty, p, num_ctas, s) : launch<DD, false, false, 0>(tx, ty, p, num_ctas, s);
   switch (D) {
     DICE_DISPATCH(256)
     DICE_DISPATCH(128)

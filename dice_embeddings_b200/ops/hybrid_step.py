@@ -1,4 +1,4 @@
-"""Tensor-core scoring for every model with the bilinear contract ``score(h, r, t) = compose(h, r) · t``.
+"""Tensor-core scoring for every model whose score is ``compose(h, r) · t`` (+ a per-query scalar), or a distance.
 
 :mod:`fused_step` covers the models whose composition is one of the algebra products the lookup kernel knows.  The
 rest of the bilinear zoo produces its query vector with ordinary PyTorch modules: the convolutional gates of ConEx /
@@ -15,6 +15,14 @@ or a normaliser sits between the embedding and the product.  For those the step 
   the dense ``dE`` the kernel produced, and the table is updated by the fused optimiser kernel (bf16 shadow refreshed
   in the same sweep).  All other parameters are stepped by the model's own optimiser.
 
+Two epilogue variants of the scoring kernel widen the contract.  Models whose score adds a scalar that depends on the
+query only — the general Clifford models Keci / CKeci (p, q) and DeCaL (p, q, r), whose σ_pp / σ_qq / σ_pq / … terms
+are summed into one number per (h, r) (``dicee/models/clifford.py:258-305``, ``:601-790``) — pass it as a per-query bias
+(a column bias in the launch that keeps the table stationary, a row bias in the other, which also returns its
+gradient).  TransE (``dicee/models/real.py:52-76``) uses the distance epilogue: ``margin − sqrt(‖q‖² + ‖e‖² − 2 q·e)``
+from the same dot products, with the squared norms as per-row scalars; the kernel's second GEMM then yields
+``Σ w e`` with ``w = dS / distance`` together with ``Σ w``, and the gradient is ``Σ w e − (Σ w) q``.
+
 The reference runs these models as ``conv2d`` / ``Linear`` / four to eight ``torch.mm`` against the table plus
 ``BCEWithLogitsLoss`` on dense labels (``dicee/models/complex.py:33-62``, ``dicee/models/quaternion.py:242-319``,
 ``dicee/models/octonion.py:206-313``, ``dicee/models/dualE.py:102-127``, ``dicee/models/base_model.py:25-46``).
@@ -30,25 +38,24 @@ from .fused_step import SUPPORTED_DIMS, SUPPORTED_SCORING, _EngineOptimizer, fus
 
 
 def hybrid_supported(model) -> bool:
-    """Bilinear contract without a per-query bias, a width the scoring kernel takes, ordinary index inputs."""
-    if not getattr(model, "bilinear", False) or getattr(model, "byte_pair_encoding", False):
+    """Bilinear contract (with or without a per-query bias) or TransE's distance, a width the scoring kernel takes,
+    ordinary index inputs."""
+    if getattr(model, "byte_pair_encoding", False):
         return False
     if model.embedding_dim not in SUPPORTED_DIMS or model.optimizer_name not in K.OPT_CODE:
         return False
-    name = type(model).__name__
-    if name == "TransE":                       # distance score: not a dot product against the table
-        return False
-    if name in ("Keci", "CKeci", "DeCaL") and not (getattr(model, "p", 0) == 0 and getattr(model, "q", 0) == 1
-                                                   and getattr(model, "r", 0) == 0):
-        return False                           # per-query scalar terms next to the dot product
-    return hasattr(model, "compose")
+    if type(model).__name__ == "TransE":
+        return True
+    return bool(getattr(model, "bilinear", False)) and hasattr(model, "compose")
 
 
 class FusedScoring(torch.autograd.Function):
-    """``loss = mean BCE-with-logits(Q Eᵀ, labels)`` with the gradient w.r.t. ``Q`` computed in the same call."""
+    """``loss = mean BCE-with-logits(logits(Q, E), labels)`` with the gradient w.r.t. ``Q`` (and the per-query bias)
+    computed in the same call.  ``mode`` 0: ``Q Eᵀ``; 1: ``Q Eᵀ + bias[:, None]``; 2: ``margin − cdist(Q, E)``."""
 
     @staticmethod
-    def forward(ctx, q: torch.Tensor, engine: "ExternalQueryEngine", dp: torch.Tensor):
+    def forward(ctx, q: torch.Tensor, bias: Optional[torch.Tensor], engine: "ExternalQueryEngine", dp: torch.Tensor,
+                mode: int):
         n = q.shape[0]
         b = engine._buffers(n)
         scale = 1.0 / (float(n) * float(engine.NE))
@@ -59,16 +66,36 @@ class FusedScoring(torch.autograd.Function):
         b.mask_e.zero_()
         K.build_label_masks(dp, engine.offsets, engine.values, n, 1, 0, b.mask_q, b.mask_e,
                             num_data_points=engine.num_data_points, num_local_rows=engine.NE, status=engine.status)
+        common = dict(pos_delta=engine.pos_weight, score_mode=mode, margin=engine.margin)
+        if mode == 0:
+            e_kw, q_kw = {}, {}
+        elif mode == 1:
+            b.q_scalar[:n].copy_(bias.detach())
+            b.q_sum.zero_()
+            e_kw = dict(y_bias=b.q_scalar)
+            q_kw = dict(x_bias=b.q_scalar, x_dsum=b.q_sum)
+        else:
+            # squared norms of the operands as the tensor cores see them (bf16-rounded)
+            torch.sum(b.Q.float() ** 2, dim=1, out=b.q_scalar[:n])
+            torch.sum(engine.E_bf16.float() ** 2, dim=1, out=engine.e_scalar[:engine.NE])
+            b.q_sum.zero_()
+            engine.e_sum.zero_()
+            e_kw = dict(x_bias=engine.e_scalar, y_bias=b.q_scalar, x_dsum=engine.e_sum)
+            q_kw = dict(x_bias=b.q_scalar, y_bias=engine.e_scalar, x_dsum=b.q_sum)
         K.kvsall_fused(engine.E_bf16, b.Q, engine.gE, engine.loss_acc, engine.status, engine.base, scale, True,
-                       mask=b.mask_e, pos_delta=engine.pos_weight)
+                       mask=b.mask_e, **common, **e_kw)
         K.kvsall_fused(b.Q, engine.E_bf16, b.dQ, None, engine.status, engine.base, scale, False,
-                       mask=b.mask_q, pos_delta=engine.pos_weight)
-        ctx.dq = b.dQ
+                       mask=b.mask_q, **common, **q_kw)
+        if mode == 2:
+            # d logit / d x = (y − x) / distance: the kernels returned Σ w y and Σ w
+            engine.gE.addcmul_(engine.e_sum[:, None], engine.E, value=-1.0)
+            b.dQ.addcmul_(b.q_sum[:, None], q.detach(), value=-1.0)
+        ctx.dq, ctx.dbias = b.dQ, (b.q_sum if mode == 1 else None)
         return (engine.loss_acc * scale).to(torch.float32).reshape(())
 
     @staticmethod
     def backward(ctx, grad_out):
-        return grad_out * ctx.dq, None, None
+        return grad_out * ctx.dq, (None if ctx.dbias is None else grad_out * ctx.dbias), None, None, None
 
 
 class ExternalQueryEngine:
@@ -108,6 +135,11 @@ class ExternalQueryEngine:
             self.values = pairs[:, 2].contiguous()
             pos, base = 1.0, 0.0
         self.pos_weight, self.base = float(pos - base), float(base)
+        self.distance = type(model).__name__ == "TransE"
+        self.margin = float(getattr(model, "margin", 0.0)) if self.distance else 0.0
+        if self.distance:
+            self.e_scalar = torch.zeros(K.padded_rows(self.NE), device=dev)
+            self.e_sum = torch.zeros(self.NE, device=dev)
         self.num_data_points = int(self.offsets.numel() - 1)
         self.label_mode = "mask"
         self._bufs = {}
@@ -121,6 +153,8 @@ class ExternalQueryEngine:
             b.dQ = torch.zeros(n, self.D, dtype=torch.float32, device=dev)
             b.mask_q = torch.zeros(n, K.mask_stride(self.NE), dtype=torch.int32, device=dev)
             b.mask_e = torch.zeros(self.NE, K.mask_stride(n), dtype=torch.int32, device=dev)
+            b.q_scalar = torch.zeros(K.padded_rows(n), device=dev)     # per-query bias or squared norm
+            b.q_sum = torch.zeros(n, device=dev)
             self._bufs[n] = b
         return self._bufs[n]
 
@@ -134,9 +168,14 @@ class ExternalQueryEngine:
         head_rows = self.E[h_idx].requires_grad_(True)          # leaf: the table itself stays outside autograd
         h = m.normalize_head_entity_embeddings(m.input_dp_ent_real(head_rows))
         r = m.normalize_relation_embeddings(m.input_dp_rel_real(m.relation_embeddings(x[:, 1])))
-        q, bias = m.compose(h, r)
-        assert bias is None, "models with a per-query bias are outside this engine"
-        loss = FusedScoring.apply(q.float().contiguous(), self, dp.contiguous())
+        if self.distance:
+            q, bias, mode = h + r + m._eps, None, 2
+        else:
+            q, bias = m.compose(h, r)
+            mode = 0 if bias is None else 1
+            if bias is not None:
+                bias = bias.float().reshape(-1).contiguous()
+        loss = FusedScoring.apply(q.float().contiguous(), bias, self, dp.contiguous(), mode)
         loss.backward()
         self.gE.index_add_(0, h_idx, head_rows.grad)           # row gradients of the lookups join the dense dE
         if self.rest_optimizer is not None:

@@ -72,15 +72,33 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
                  status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0,
                  out_table: Optional[torch.Tensor] = None, out_block_rows: int = 0,
                  mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0,
-                 trace: Optional[torch.Tensor] = None, loss_share: int = -1) -> None:
+                 trace: Optional[torch.Tensor] = None, loss_share: int = -1, score_mode: int = 0,
+                 x_bias: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None,
+                 x_dsum: Optional[torch.Tensor] = None, margin: float = 0.0) -> None:
     """``out[x_rows, D] += scale · (sigmoid(X Yᵀ) − base) · Y`` and optionally
     ``loss_acc += Σ softplus(X Yᵀ) − base · X Yᵀ`` on the tcgen05 path.  ``x``/``y`` bf16, ``out`` fp32.
+
+    ``score_mode`` 1 adds one scalar per row of ``x`` and of ``y`` to the logit (``x_bias``, ``y_bias``; fp32, padded
+    with readable zeros to a multiple of 128 rows, see :func:`padded_rows`); ``x_dsum [x_rows]`` then receives
+    ``scale · Σ_y dS``, the gradient of ``x_bias``.  ``score_mode`` 2 makes the logit
+    ``margin − sqrt(x_bias + y_bias − 2 x·y)`` with the squared row norms as biases; ``out`` then holds
+    ``scale · Σ_y w y`` with ``w = dS / distance`` and ``x_dsum`` the row sums of ``scale · w``: the gradient with
+    respect to ``x`` is ``out − x_dsum[:, None] · x``.  Both modes need a label mask.
 
     ``loss_share`` splits the loss arithmetic between the two launches of a training step (the same pairs with the
     roles of ``x`` and ``y`` swapped): launch 0 and launch 1 each add the loss of one half of the ``(x, y)`` plane
     (256 x 256 blocks of alternating parity); ``-1`` keeps all of it in this launch.  The one-CTA kernel does not
     split: there share 0 takes everything and share 1 nothing."""
-    pair = x.shape[1] == 256 and out_table is None and pair_kernel_enabled()
+    pair = x.shape[1] == 256 and out_table is None and score_mode == 0 and pair_kernel_enabled()
+    if score_mode != 0:
+        assert mask is not None and score_mode in (1, 2)
+        for t, rows, nm in ((x_bias, x.shape[0], "x_bias"), (y_bias, y.shape[0], "y_bias")):
+            if t is not None:
+                _req(t, torch.float32, nm)
+                assert t.numel() >= padded_rows(rows), f"{nm} must be padded to a multiple of 128 rows"
+        if x_dsum is not None:
+            _req(x_dsum, torch.float32, "x_dsum")
+            assert x_dsum.numel() >= x.shape[0]
     if with_loss and loss_share >= 0 and not pair:
         if loss_share == 1:
             with_loss, loss_acc = False, None
@@ -104,7 +122,13 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     _call("dice_kvsall_fused", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
           float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas), _ptr(out_table),
           int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
-          others=(y, out, loss_acc, status, mask, trace))
+          int(score_mode), _ptr(x_bias), _ptr(y_bias), _ptr(x_dsum), float(margin),
+          others=(y, out, loss_acc, status, mask, trace, x_bias, y_bias, x_dsum))
+
+
+def padded_rows(n: int) -> int:
+    """Length the per-row scalar vectors of :func:`kvsall_fused` need for ``n`` rows (whole 128-row tiles)."""
+    return (int(n) + 127) // 128 * 128
 
 
 def lookup_compose(model: int, normalize: bool, idx_h, idx_r, ent_table: torch.Tensor, W: int, num_entities: int,

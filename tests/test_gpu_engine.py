@@ -63,11 +63,13 @@ def test_one_sgd_step_matches_autograd(name, label_mode, D):
 
 @pytest.mark.parametrize("name,extra", [("ConEx", {}), ("AConEx", {}), ("ConvQ", {}), ("AConvO", {}), ("DualE", {}),
                                         ("ComplEx", {"normalization": "LayerNorm"}),
-                                        ("QMult", {"normalization": "BatchNorm1d"})])
+                                        ("QMult", {"normalization": "BatchNorm1d"}),
+                                        ("Keci", {"p": 1, "q": 2}), ("DeCaL", {"p": 3, "q": 3, "r": 1}),
+                                        ("TransE", {})])
 @pytest.mark.parametrize("D", [64, 256])
 def test_external_query_engine_matches_autograd(name, extra, D):
-    """Models whose query vector comes out of PyTorch modules (convolutional gates, normalisers, dual quaternions):
-    one SGD step through the tensor-core scoring function against the same step in plain autograd on dense labels."""
+    """Models whose query vector comes out of PyTorch modules (convolutional gates, normalisers, dual quaternions),
+    models with a per-query scalar next to the dot product (general Clifford algebras) and the distance model: one SGD step through the tensor-core scoring function against the same step in plain autograd on dense labels."""
     from dice_embeddings_b200.ops.hybrid_step import ExternalQueryEngine, build_hybrid_engine, hybrid_supported
     lr = 50.0
     NE, NR = 700, 15
@@ -84,6 +86,9 @@ def test_external_query_engine_matches_autograd(name, extra, D):
         with torch.no_grad():
             m.entity_embeddings.weight.mul_(0.3)
             m.relation_embeddings.weight.mul_(0.3)
+            for n, p in m.named_parameters():
+                if "coefficients" in n:
+                    p.fill_(0.7)           # the interaction terms (and with them the per-query bias) are switched on
         m.train()
     assert hybrid_supported(hyb)
     B = 384

@@ -120,6 +120,74 @@ def test_pair_kernel_loss_split_between_the_two_roles_adds_up(monkeypatch):
     assert (ox - ox2).abs().max() <= 2e-2 * ox.abs().max()
 
 
+def _pad128(v):
+    out = torch.zeros(K.padded_rows(v.numel()), device=v.device)
+    out[: v.numel()] = v
+    return out
+
+
+@pytest.mark.parametrize("nx,ny,D,ctas", [(300, 200, 64, 0), (257, 515, 128, 0), (1000, 777, 256, 0), (1500, 900, 256, 3)])
+@pytest.mark.parametrize("with_loss", [True, False])
+def test_kvsall_fused_with_row_and_column_bias(nx, ny, D, ctas, with_loss):
+    """score_mode 1: logit = x·y + bx[x] + by[y]; loss, out and the gradient of bx against fp32 autograd."""
+    torch.manual_seed(nx + ny + D)
+    x = (torch.randn(nx, D, device=DEV) * 0.3).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.3).to(torch.bfloat16)
+    bx = torch.randn(nx, device=DEV) * 0.5
+    by = torch.randn(ny, device=DEV) * 0.5
+    bits = torch.rand(nx, ny, device=DEV) < 0.05
+    base, pos, scale = 0.01, 0.92, 1.0 / 64
+    xf = x.float().requires_grad_(True)
+    bxf = bx.clone().requires_grad_(True)
+    s = xf @ y.float().t() + bxf[:, None] + by[None, :]
+    labels = torch.where(bits, torch.full_like(s, pos), torch.full_like(s, base))
+    ref_loss = (torch.nn.functional.softplus(s) - labels * s).double().sum()
+    (ref_loss * scale).backward()
+    out = torch.zeros(nx, D, device=DEV)
+    dsum = torch.zeros(nx, device=DEV)
+    loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.kvsall_fused(x, y, out, loss if with_loss else None, status, base, scale, with_loss, num_ctas=ctas,
+                   mask=_pack_mask(bits), pos_delta=pos - base, score_mode=1, x_bias=_pad128(bx), y_bias=_pad128(by),
+                   x_dsum=dsum)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    assert (out - xf.grad).abs().max() / xf.grad.abs().max() < 2e-2
+    assert (dsum - bxf.grad).abs().max() / bxf.grad.abs().max() < 1e-2
+    if with_loss:
+        assert abs(loss.item() - ref_loss.item()) / abs(ref_loss.item()) < 2e-3
+
+
+@pytest.mark.parametrize("nx,ny,D,ctas", [(300, 200, 64, 0), (257, 515, 128, 0), (1000, 777, 256, 0), (1500, 900, 256, 3)])
+@pytest.mark.parametrize("with_loss", [True, False])
+def test_kvsall_fused_distance_score(nx, ny, D, ctas, with_loss):
+    """score_mode 2: logit = margin − ‖x − y‖; gradient with respect to x = out − dsum · x against fp32 autograd."""
+    torch.manual_seed(nx * 3 + ny + D)
+    x = (torch.randn(nx, D, device=DEV) * 0.3).to(torch.bfloat16)
+    y = (torch.randn(ny, D, device=DEV) * 0.3).to(torch.bfloat16)
+    bits = torch.rand(nx, ny, device=DEV) < 0.05
+    base, pos, scale, margin = 0.01, 0.92, 1.0 / 64, 4.0
+    xf = x.float().requires_grad_(True)
+    s = margin - torch.cdist(xf, y.float())
+    labels = torch.where(bits, torch.full_like(s, pos), torch.full_like(s, base))
+    ref_loss = (torch.nn.functional.softplus(s) - labels * s).double().sum()
+    (ref_loss * scale).backward()
+    out = torch.zeros(nx, D, device=DEV)
+    dsum = torch.zeros(nx, device=DEV)
+    loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.kvsall_fused(x, y, out, loss if with_loss else None, status, base, scale, with_loss, num_ctas=ctas,
+                   mask=_pack_mask(bits), pos_delta=pos - base, score_mode=2,
+                   x_bias=_pad128((x.float() ** 2).sum(1)), y_bias=_pad128((y.float() ** 2).sum(1)), x_dsum=dsum,
+                   margin=margin)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    grad = out - dsum[:, None] * x.float()
+    assert (grad - xf.grad).abs().max() / xf.grad.abs().max() < 2e-2
+    if with_loss:
+        assert abs(loss.item() - ref_loss.item()) / abs(ref_loss.item()) < 2e-3
+
+
 def test_kvsall_fused_accumulates_and_splits_work():
     """Two launches add up; any CTA count gives the same sums (work ranges are arbitrary cuts of the tile grid)."""
     torch.manual_seed(0)
