@@ -27,13 +27,14 @@ extern "C" {
 // ---------------------------------------------------------------------------------------- tensor-core scoring
 // out[x_rows, D] += scale * (sigmoid(X Yᵀ) - label) * Y and, with_loss, *loss += sum softplus(s) - label * s; x, y bf16
 // row-major, D in {64, 128, 256}.  Labels: `base` everywhere, base + pos_delta where the bit mask (row stride
-// mask_stride words, a multiple of 4) is set.  out_table (optional) scatters result rows to per-block owners; trace
-// (optional) receives int64[64][8] pipeline stamps of CTA 0.
+// mask_stride words, a multiple of 4) is set.  trace (optional) receives int64[64][8] pipeline stamps of CTA 0.
+// score_mode 0: logit = x.y; 1: x.y + x_bias[x] + y_bias[y]; 2: margin - sqrt(x_bias[x] + y_bias[y] - 2 x.y) (squared
+// norms as biases; out then holds sum_y w y with w = dS / distance).  x_bias / y_bias: fp32, readable up to the next
+// multiple of 128 rows, null = zeros; x_dsum (optional, [x_rows]) += scale * row sums of the second GEMM's A operand.
 int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss,
-                      float base, float scale, int with_loss, int* status, int num_ctas, float* const* out_table,
-                      int out_block_rows, const unsigned int* mask, int mask_stride, float pos_delta,
-                      long long* trace, int score_mode, const float* x_bias, const float* y_bias, float* x_dsum,
-                      float margin, void* stream);
+                      float base, float scale, int with_loss, int* status, int num_ctas, const unsigned int* mask,
+                      int mask_stride, float pos_delta, long long* trace, int score_mode, const float* x_bias,
+                      const float* y_bias, float* x_dsum, float margin, void* stream);
 // CTA-pair variant (tcgen05.mma.cta_group::2), D = 256.  loss_share -1 / 0 / 1: all / even / odd 256 x 256 blocks add
 // their loss terms in this launch.  trace: optional int64[64][8] pipeline stamps.
 int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss, float base,

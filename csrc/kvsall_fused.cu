@@ -41,8 +41,6 @@ constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 
 struct KvsAllParams {
   float* out;           // [x_rows, D] fp32, accumulated with red.add
-  float* const* out_table;  // optional: row x goes to out_table[x / out_block_rows] + (x % out_block_rows) * D, so
-  int out_block_rows;       // that blocks of rows can live on different GPUs (peer pointers): GEMM -> reduce-scatter
   double* loss;         // scalar accumulator (may be null when LOSS == false)
   int* status;          // 0 = ok, otherwise first failure code
   int x_rows, y_rows;   // valid row counts
@@ -469,11 +467,7 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       if (!mbar_wait_bounded(dx_full, seg & 1, s_abort)) { ok = false; break; }
       tc_fence_after();
       float* out_row = p.out;
-      if (valid_x) {
-        out_row = (p.out_table != nullptr)
-                      ? p.out_table[x_global / p.out_block_rows] + static_cast<size_t>(x_global % p.out_block_rows) * D
-                      : p.out + static_cast<size_t>(x_global) * D;
-      }
+      if (valid_x) out_row = p.out + static_cast<size_t>(x_global) * D;
       constexpr int DC = D / 4;
       if constexpr (DC >= 32) {
 #pragma unroll
@@ -546,8 +540,7 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 }  // namespace dice
 
 // x, y: bf16 row-major with 16-byte aligned base; D in {64, 128, 256}.  out must be zero-initialised (or hold a
-// running sum) by the caller; *loss likewise.  With out_table != null (a device array of base pointers, one per
-// block of out_block_rows rows, possibly in peer memory) the result rows are scattered to their owners instead.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
+// running sum) by the caller; *loss likewise.  num_ctas <= 0 selects one CTA per SM.  Returns 0 on a successful
 // launch; device-side failures are reported through *status.  trace (optional, device int64 [64][8]): CTA 0 writes
 // clock64 stamps per tile into it (0 Y-load issued, 1 S GEMM issued, 2 second GEMM issued, 3 epilogue sees S,
 // 4 epilogue wrote dS, 5 out tile drained) for pipeline diagnostics.
@@ -558,14 +551,13 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 // sums of the values fed to the second GEMM (mode 1: the gradient of x_bias).
 extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out,
                                  double* loss, float base, float scale, int with_loss, int* status, int num_ctas,
-                                 float* const* out_table, int out_block_rows, const unsigned int* mask,
-                                 int mask_stride, float pos_delta, long long* trace, int score_mode,
+                                 const unsigned int* mask, int mask_stride, float pos_delta, long long* trace, int score_mode,
                                  const float* x_bias, const float* y_bias, float* x_dsum, float margin,
                                  void* stream) {
   using namespace dice;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
-      (out_table == nullptr && (reinterpret_cast<uintptr_t>(out) & 15)))
+      (reinterpret_cast<uintptr_t>(out) & 15))
     return -5;
   CUtensorMap tx, ty;
   int rc = make_tmap_bf16(&tx, x, x_rows, D);
@@ -574,8 +566,6 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   if (rc) return rc;
   KvsAllParams p;
   p.out = out;
-  p.out_table = out_table;
-  p.out_block_rows = out_block_rows > 0 ? out_block_rows : 1;
   p.loss = loss;
   p.status = status;
   p.x_rows = x_rows;

@@ -70,7 +70,6 @@ def pair_kernel_enabled() -> bool:
 
 def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: Optional[torch.Tensor],
                  status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0,
-                 out_table: Optional[torch.Tensor] = None, out_block_rows: int = 0,
                  mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0,
                  trace: Optional[torch.Tensor] = None, loss_share: int = -1, score_mode: int = 0,
                  x_bias: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None,
@@ -89,7 +88,7 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     roles of ``x`` and ``y`` swapped): launch 0 and launch 1 each add the loss of one half of the ``(x, y)`` plane
     (256 x 256 blocks of alternating parity); ``-1`` keeps all of it in this launch.  The one-CTA kernel does not
     split: there share 0 takes everything and share 1 nothing."""
-    pair = x.shape[1] == 256 and out_table is None and score_mode == 0 and pair_kernel_enabled()
+    pair = x.shape[1] == 256 and score_mode == 0 and pair_kernel_enabled()
     if score_mode != 0:
         assert mask is not None and score_mode in (1, 2)
         for t, rows, nm in ((x_bias, x.shape[0], "x_bias"), (y_bias, y.shape[0], "y_bias")):
@@ -106,9 +105,8 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     _req(x, torch.bfloat16, "x")
     _req(y, torch.bfloat16, "y")
     D = x.shape[1]
-    if out_table is None:
-        _req(out, torch.float32, "out")
-        assert out.shape[0] >= x.shape[0] and out.shape[1] == D
+    _req(out, torch.float32, "out")
+    assert out.shape[0] >= x.shape[0] and out.shape[1] == D
     assert y.shape[1] == D
     if with_loss:
         _req(loss_acc, torch.float64, "loss_acc")
@@ -120,8 +118,8 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
               others=(y, out, loss_acc, status, mask, trace))
         return
     _call("dice_kvsall_fused", x, _ptr(x), x.shape[0], _ptr(y), y.shape[0], D, _ptr(out), _ptr(loss_acc),
-          float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas), _ptr(out_table),
-          int(out_block_rows), _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
+          float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas),
+          _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
           int(score_mode), _ptr(x_bias), _ptr(y_bias), _ptr(x_dsum), float(margin),
           others=(y, out, loss_acc, status, mask, trace, x_bias, y_bias, x_dsum))
 
