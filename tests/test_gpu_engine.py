@@ -162,6 +162,23 @@ def test_trainer_uses_fused_engine(tmp_path):
     assert len(k.predict_topk(h=[next(iter(k.entity_to_idx))], r=[next(iter(k.relation_to_idx))], topk=3)[0]) == 3
 
 
+@pytest.mark.parametrize("model,extra", [("TransE", {}), ("Keci", {"p": 1, "q": 2}), ("ConEx", {"num_of_output_channels": 2})])
+def test_trainer_uses_external_query_engine(tmp_path, model, extra):
+    """The distance model, a Clifford model with per-query scalar terms and a convolutional model train through
+    ``Execute`` on the tensor-core scoring function and learn the planted graph."""
+    from dice_embeddings_b200 import Execute, Namespace
+    from dice_embeddings_b200.data.synthetic import make_planted_kg
+    from dice_embeddings_b200.ops.hybrid_step import ExternalQueryEngine
+    kg = make_planted_kg(str(tmp_path / "kg"), num_entities=300, num_relations=10, seed=1)
+    a = Namespace(dataset_dir=kg, model=model, scoring_technique="KvsAll", embedding_dim=64, num_epochs=150,
+                  batch_size=256, lr=0.05, optim="Adam", path_to_store_single_run=str(tmp_path / "run"), gpus=0,
+                  kernel_backend="cuda", trainer="torchCPUTrainer", **extra)
+    ex = Execute(a)
+    rep = ex.start()
+    assert isinstance(ex.trainer.trainer.engine, ExternalQueryEngine)
+    assert rep["Train"]["MRR"] > 0.5, rep["Train"]
+
+
 def test_pipelined_host_steps_return_the_same_losses():
     ds, m1, m2 = _make("ComplEx", 64, "Adam", 0.05)
     B = 256
