@@ -24,6 +24,21 @@ typedef unsigned short dice_bf16;   /* raw bits of a bfloat16 */
 extern "C" {
 #endif
 
+// Optimiser step fused into dice_kvsall_fused: the launch that produces the last partial gradient of a 128-row tile of
+// X applies Adam (kind 0), AdamW (1), SGD (2) or ADOPT (3) to that tile.  param / m / v: fp32 [x_rows, D]; shadow: the
+// bf16 rows (the x operand itself); count: [ceil(x_rows / 128)] zero-initialised words (zero again afterwards);
+// step: device counter of completed steps (read, not advanced).
+typedef struct DiceFusedOptimizer {
+  float* param;
+  float* m;
+  float* v;
+  void* shadow;
+  unsigned int* count;
+  const long long* step;
+  float lr, beta1, beta2, eps, weight_decay;
+  int kind;
+} DiceFusedOptimizer;
+
 // ---------------------------------------------------------------------------------------- tensor-core scoring
 // out[x_rows, D] += scale * (sigmoid(X Yᵀ) - label) * Y and, with_loss, *loss += sum softplus(s) - label * s; x, y bf16
 // row-major, D in {64, 128, 256}.  Labels: `base` everywhere, base + pos_delta where the bit mask (row stride
@@ -34,7 +49,7 @@ extern "C" {
 int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss,
                       float base, float scale, int with_loss, int* status, int num_ctas, const unsigned int* mask,
                       int mask_stride, float pos_delta, long long* trace, int score_mode, const float* x_bias,
-                      const float* y_bias, float* x_dsum, float margin, void* stream);
+                      const float* y_bias, float* x_dsum, float margin, const DiceFusedOptimizer* opt, void* stream);
 // CTA-pair variant (tcgen05.mma.cta_group::2), D = 256.  loss_share -1 / 0 / 1: all / even / odd 256 x 256 blocks add
 // their loss terms in this launch.  trace: optional int64[64][8] pipeline stamps.
 int dice_kvsall_pair(const void* x, int x_rows, const void* y, int y_rows, int D, float* out, double* loss, float base,

@@ -8,6 +8,7 @@
 // arrays of per-rank base pointers, so with W == 1 they act on one table and with W > 1 they read / write peer
 // memory directly (plain ld/st/red over NVLink; no multicast loads).
 #include "algebra.cuh"
+#include "optim.cuh"
 #include "ptx_sm100.cuh"
 
 namespace dice {
@@ -534,36 +535,6 @@ __device__ __forceinline__ float opt_multimem_sum1(const float* mc_addr) {
   float r;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(r) : "l"(mc_addr) : "memory");
   return r;
-}
-
-// One parameter element: returns the updated weight; m / v are updated in place (registers).
-__device__ __forceinline__ float opt_update(int kind, float w, float g, float& m, float& v, float lr, float beta1,
-                                            float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2,
-                                            float clip, bool first_step) {
-  if (kind == 0) {
-    g = fmaf(wd, w, g);
-    m = fmaf(beta1, m, (1.f - beta1) * g);
-    v = fmaf(beta2, v, (1.f - beta2) * g * g);
-    return w - lr * inv_bc1 * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
-  } else if (kind == 1) {
-    w *= 1.f - lr * wd;
-    m = fmaf(beta1, m, (1.f - beta1) * g);
-    v = fmaf(beta2, v, (1.f - beta2) * g * g);
-    return w - lr * inv_bc1 * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
-  } else if (kind == 2) {
-    g = fmaf(wd, w, g);
-    return w - lr * g;
-  }
-  g = fmaf(wd, w, g);  // ADOPT
-  if (first_step) {
-    v = g * g;
-    return w;
-  }
-  float ng = g / fmaxf(sqrtf(v), eps);
-  ng = fminf(fmaxf(ng, -clip), clip);
-  m = m + (1.f - beta1) * (ng - m);
-  v = fmaf(beta2, v, (1.f - beta2) * g * g);
-  return w - lr * m;
 }
 
 __global__ void __launch_bounds__(256) optimizer_kernel(const OptParams p) {

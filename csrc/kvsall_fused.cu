@@ -25,6 +25,7 @@
 // Every mbarrier wait is bounded; on a time-out the kernel records a status code, drains its TMA copies, frees
 // TMEM and returns.
 #include "dice_b200.h"
+#include "optim.cuh"
 #include "ptx_sm100.cuh"
 #include "tile_map.cuh"
 #include "tma_host.cuh"
@@ -57,6 +58,10 @@ struct KvsAllParams {
   const float* y_bias;  // [ny_tiles * 128] or null (= 0), padded to whole tiles: the same for the rows of Y
   float* x_dsum;        // optional [x_rows]: += scale * sum over y of the value fed to the second GEMM
   float margin;         // SCORE 2: logit = margin - sqrt(|x|^2 + |y|^2 - 2 x.y)
+  // Optimiser fused into the drain (opt.param != null): out is then the gradient buffer of the rows of X, and the CTA
+  // whose partial sums complete an x tile (tile counters) updates those 128 rows at once: master weights, moments,
+  // the bf16 rows that X itself is (no CTA reads a completed tile again) and clears the gradient.
+  DiceFusedOptimizer opt;
 };
 
 template <int D>
@@ -202,6 +207,9 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   uint64_t* y_full = bars + 12;      // [NSTAGE][4]: one per 64-column slab, so the S GEMM starts on the first slab
   uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 28);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 29);
+  volatile int* s_last = reinterpret_cast<volatile int*>(bars + 30);   // this CTA completed the x tile (fused optimiser)
+  uint64_t* opt_issued = bars + 31;   // all epilogue warps have issued the reductions of a segment
+  uint64_t* opt_decided = bars + 32;  // s_last of the segment is valid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -224,6 +232,8 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(y_empty + i, 1);
       for (int sl = 0; sl < C::NSLAB; ++sl) mbar_init(y_full + i * 4 + sl, 1);
     }
+    mbar_init(opt_issued, NUM_EPI_WARPS);
+    mbar_init(opt_decided, 1);
     *reinterpret_cast<volatile uint64_t*>(bars + 29) = 0;  // abort flag and an always-zero word next to it
     fence_barrier_init();
   }
@@ -499,6 +509,55 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       __syncwarp();
       if (warp == 2 && lane == 0) stamp(g - 1, 5);
       if (lane == 0) mbar_arrive(dx_empty);
+      if (p.opt.param != nullptr) {
+        // the y tiles of this segment are counted once all sixteen warps' reductions are on their way to L2; whoever
+        // brings the count of the x tile to ny_tiles holds the last partial sum and applies the update.  The hand-shake
+        // between the warps uses mbarriers with bounded waits, like every other wait of this kernel.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(opt_issued);
+        if (warp == 2) {
+          if (!mbar_wait_bounded(opt_issued, seg & 1, s_abort)) { ok = false; break; }
+          if (lane == 0) {
+            __threadfence();
+            *s_last = (atomicAdd(p.opt.count + x, static_cast<unsigned>(n)) + n == static_cast<unsigned>(p.ny_tiles)) ? 1 : 0;
+            mbar_arrive(opt_decided);
+          }
+        }
+        if (!mbar_wait_bounded(opt_decided, seg & 1, s_abort)) { ok = false; break; }
+        const bool is_last = *s_last != 0;
+        if (is_last) {
+          __threadfence();
+          const int rows = min(BLOCK_X, p.x_rows - x * BLOCK_X);
+          const size_t base4 = static_cast<size_t>(x) * BLOCK_X * (D / 4);
+          float4* __restrict__ pw = reinterpret_cast<float4*>(p.opt.param) + base4;
+          float4* __restrict__ pg = reinterpret_cast<float4*>(p.out) + base4;
+          float4* __restrict__ pm = reinterpret_cast<float4*>(p.opt.m) + base4;
+          float4* __restrict__ pv = reinterpret_cast<float4*>(p.opt.v) + base4;
+          uint2* __restrict__ ps = reinterpret_cast<uint2*>(p.opt.shadow) + base4;
+          const int kind = p.opt.kind;
+          const OptStepConsts c = opt_step_consts(kind, *p.opt.step + 1, p.opt.beta1, p.opt.beta2);
+          for (int i = threadIdx.x - 64; i < rows * (D / 4); i += 32 * NUM_EPI_WARPS) {
+            float4 wv = pw[i];
+            const float4 gv = __ldcg(pg + i);   // the sums were formed in L2 by other SMs' reductions
+            float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+            if (kind != 2) { m = pm[i]; v = pv[i]; }
+            wv.x = opt_update(kind, wv.x, gv.x, m.x, v.x, p.opt.lr, p.opt.beta1, p.opt.beta2, p.opt.eps, p.opt.weight_decay, c.inv_bc1, c.inv_sqrt_bc2, c.clip, c.first_step);
+            wv.y = opt_update(kind, wv.y, gv.y, m.y, v.y, p.opt.lr, p.opt.beta1, p.opt.beta2, p.opt.eps, p.opt.weight_decay, c.inv_bc1, c.inv_sqrt_bc2, c.clip, c.first_step);
+            wv.z = opt_update(kind, wv.z, gv.z, m.z, v.z, p.opt.lr, p.opt.beta1, p.opt.beta2, p.opt.eps, p.opt.weight_decay, c.inv_bc1, c.inv_sqrt_bc2, c.clip, c.first_step);
+            wv.w = opt_update(kind, wv.w, gv.w, m.w, v.w, p.opt.lr, p.opt.beta1, p.opt.beta2, p.opt.eps, p.opt.weight_decay, c.inv_bc1, c.inv_sqrt_bc2, c.clip, c.first_step);
+            pw[i] = wv;
+            pg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (kind != 2) { pm[i] = m; pv[i] = v; }
+            __nv_bfloat162 lo = __floats2bfloat162_rn(wv.x, wv.y), hi = __floats2bfloat162_rn(wv.z, wv.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            ps[i] = pk;
+          }
+          if (threadIdx.x == 64) p.opt.count[x] = 0u;   // ready for the next launch
+        }
+      }
       w += n;
       ++seg;
     }
@@ -549,11 +608,13 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
 // caller subtracts x_dsum[x] * x.  Modes 1 and 2 need a label mask; x_bias / y_bias (either may be null = zeros) must
 // be readable up to the next multiple of 128 rows; x_dsum (optional, [x_rows], caller-zeroed) receives scale * the row
 // sums of the values fed to the second GEMM (mode 1: the gradient of x_bias).
+// opt (optional): the optimiser step of the rows of X fused into this launch, see DiceFusedOptimizer; `out` must then
+// already hold every other contribution to the gradient of those rows, and opt->shadow must be x itself.
 extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y_rows, int D, float* out,
                                  double* loss, float base, float scale, int with_loss, int* status, int num_ctas,
                                  const unsigned int* mask, int mask_stride, float pos_delta, long long* trace, int score_mode,
                                  const float* x_bias, const float* y_bias, float* x_dsum, float margin,
-                                 void* stream) {
+                                 const DiceFusedOptimizer* opt, void* stream) {
   using namespace dice;
   if (x_rows <= 0 || y_rows <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) ||
@@ -583,6 +644,16 @@ extern "C" int dice_kvsall_fused(const void* x, int x_rows, const void* y, int y
   p.y_bias = y_bias;
   p.x_dsum = x_dsum;
   p.margin = margin;
+  if (opt != nullptr && opt->param != nullptr) {
+    // the update is written over the rows of X: masters, moments and gradient must line up with them, 16-byte aligned
+    if (opt->m == nullptr || opt->v == nullptr || opt->shadow != x || opt->count == nullptr || opt->step == nullptr ||
+        ((reinterpret_cast<uintptr_t>(opt->param) | reinterpret_cast<uintptr_t>(opt->m) |
+          reinterpret_cast<uintptr_t>(opt->v)) & 15) || opt->kind < 0 || opt->kind > 3)
+      return -5;
+    p.opt = *opt;
+  } else {
+    p.opt = DiceFusedOptimizer{};
+  }
   if (score_mode < 0 || score_mode > 2 || (score_mode != 0 && mask == nullptr)) return -6;
   if (reinterpret_cast<uintptr_t>(y_bias) & 15) return -5;
   if (mask != nullptr && ((mask_stride & 3) || (reinterpret_cast<uintptr_t>(mask) & 7))) return -5;

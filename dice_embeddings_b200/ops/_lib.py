@@ -103,7 +103,7 @@ _d = ctypes.c_double
 
 
 class _Sigs:
-    dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _f, _p]
+    dice_kvsall_fused = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _f, _p, _p]
     dice_kvsall_pair = [_p, _i, _p, _i, _i, _p, _p, _f, _f, _i, _p, _i, _p, _i, _f, _i, _p, _p]
     dice_build_label_masks = [_p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _p]
     dice_build_label_masks_flat = [_p, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _l, _l, _p, _p]

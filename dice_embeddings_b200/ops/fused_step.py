@@ -143,6 +143,17 @@ class FusedKvsAllEngine:
             segs.append(dict(param=self.coeff, grad=self.gC, m=self.mC, v=self.vC))
         self._tail = K.StepTail(self.opt_kind, segs, self.step_count, self.status, finish=True, acc=self.loss_acc,
                                 loss_out=self.loss_out)
+        # DICE_B200_FUSED_UPDATE=1: the launch order becomes query role -> backward -> entity role, and the entity update
+        # rides inside the entity-role launch (the CTA that completes a 128-row tile of dE applies the optimiser to it).
+        # Measured slower (112 us against 84 + 19 us: every tile completes at the very end of some CTA's range, where
+        # one SM's memory bandwidth then bounds its update), so it is opt-in.  Running the backward of the composition on
+        # a parallel branch beside the entity-role launch was measured too: the launch slows down by what the overlap
+        # saves (96 us against 84 + 14 us), so the step stays serial.
+        self.fuse_entity_update = self.label_mode == "mask" and os.environ.get("DICE_B200_FUSED_UPDATE", "0") == "1"
+        if self.fuse_entity_update:
+            self._tile_count = torch.zeros((self.NE + 127) // 128, dtype=torch.int32, device=dev)
+            self._tail_rest_finish = K.StepTail(self.opt_kind, segs[1:], self.step_count, self.status, finish=True,
+                                                acc=self.loss_acc, loss_out=self.loss_out)
 
     # ------------------------------------------------------------------ buffers per batch size
     def _buffers(self, n: int):
@@ -192,6 +203,30 @@ class FusedKvsAllEngine:
         K.lookup_compose_vec(self.code, self.normalize, b.h, b.r, None, b.ent_tab, 1, self.NE, self.NR, self.R,
                              self.coeff, b.q_tab, 1, 0, 0, None, None, 0, n, self.D, self.status, idx_stride=2)
         self._mark("lookup")
+        b1, b2 = self.betas
+        if self.label_mode == "mask" and self.fuse_entity_update:
+            main.wait_stream(self._side)
+            self._mark("masks_join")
+            K.kvsall_fused(b.Q, self.E_bf16, b.dQ, self.loss_acc, self.status, self.base, scale, True,
+                           mask=b.mask_q, pos_delta=self.pos_weight, loss_share=1)
+            self._mark("fused_Q")
+            K.compose_backward_owner(self.code, self.normalize, b.h, b.r, self.E, 1, 0, self.NE, self.NR, self.R,
+                                     self.coeff, b.dQ, None, 0, 0, self.gE, self.gR,
+                                     self.gC if self.coeff_trainable else None, n, self.D, self.status, idx_stride=2)
+            self._mark("backward")
+            # relation table, coefficient and dQ clear on a parallel branch: they need nothing of the launch below
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                b.dQ.zero_()
+            opt = K.fused_optimizer_args(self.opt_kind, self.E, self.mE, self.vE, self.E_bf16, self._tile_count,
+                                         self.step_count, self.lr, b1, b2, self.eps, self.weight_decay)
+            K.kvsall_fused(self.E_bf16, b.Q, self.gE, self.loss_acc, self.status, self.base, scale, True,
+                           mask=b.mask_e, pos_delta=self.pos_weight, loss_share=0, opt=opt)
+            self._mark("fused_E+update")
+            self._tail_rest_finish.launch(self.lr, b1, b2, self.eps, self.weight_decay, scale)
+            main.wait_stream(self._side)
+            self._mark("tail")
+            return
         if self.label_mode == "mask":
             main.wait_stream(self._side)
             self._mark("masks_join")
@@ -218,7 +253,6 @@ class FusedKvsAllEngine:
                                  self.coeff, b.dQ, None, 0, 0, self.gE, self.gR,
                                  self.gC if self.coeff_trainable else None, n, self.D, self.status, idx_stride=2)
         self._mark("backward")
-        b1, b2 = self.betas
         self._side.wait_stream(main)
         with torch.cuda.stream(self._side):
             b.dQ.zero_()

@@ -8,6 +8,7 @@ the call fails.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional, Sequence
 
@@ -68,12 +69,38 @@ def pair_kernel_enabled() -> bool:
     return os.environ.get("DICE_B200_PAIR", "0") == "1"
 
 
+class FusedOptimizerArgs(ctypes.Structure):
+    """``DiceFusedOptimizer`` of ``csrc/dice_b200.h``: the optimiser step of the rows of ``x`` applied inside
+    :func:`kvsall_fused` by whichever CTA completes a 128-row tile of the gradient."""
+    _fields_ = [("param", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("shadow", ctypes.c_void_p),
+                ("count", ctypes.c_void_p), ("step", ctypes.c_void_p), ("lr", ctypes.c_float), ("beta1", ctypes.c_float),
+                ("beta2", ctypes.c_float), ("eps", ctypes.c_float), ("weight_decay", ctypes.c_float),
+                ("kind", ctypes.c_int)]
+
+
+def fused_optimizer_args(kind: int, param: torch.Tensor, m: torch.Tensor, v: torch.Tensor, shadow: torch.Tensor,
+                         count: torch.Tensor, step: torch.Tensor, lr: float, beta1: float, beta2: float, eps: float,
+                         weight_decay: float) -> FusedOptimizerArgs:
+    _req(param, torch.float32, "param")
+    _req(m, torch.float32, "m")
+    _req(v, torch.float32, "v")
+    _req(shadow, torch.bfloat16, "shadow")
+    _req(count, torch.int32, "count")
+    _req(step, torch.int64, "step")
+    assert count.numel() >= (param.shape[0] + 127) // 128
+    a = FusedOptimizerArgs(_ptr(param), _ptr(m), _ptr(v), _ptr(shadow), _ptr(count), _ptr(step), float(lr), float(beta1),
+                           float(beta2), float(eps), float(weight_decay), int(kind))
+    a._keep = (param, m, v, shadow, count, step)
+    return a
+
+
 def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: Optional[torch.Tensor],
                  status: torch.Tensor, base: float, scale: float, with_loss: bool, num_ctas: int = 0,
                  mask: Optional[torch.Tensor] = None, pos_delta: float = 0.0,
                  trace: Optional[torch.Tensor] = None, loss_share: int = -1, score_mode: int = 0,
                  x_bias: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None,
-                 x_dsum: Optional[torch.Tensor] = None, margin: float = 0.0) -> None:
+                 x_dsum: Optional[torch.Tensor] = None, margin: float = 0.0,
+                 opt: Optional[FusedOptimizerArgs] = None) -> None:
     """``out[x_rows, D] += scale · (sigmoid(X Yᵀ) − base) · Y`` and optionally
     ``loss_acc += Σ softplus(X Yᵀ) − base · X Yᵀ`` on the tcgen05 path.  ``x``/``y`` bf16, ``out`` fp32.
 
@@ -84,11 +111,14 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
     ``scale · Σ_y w y`` with ``w = dS / distance`` and ``x_dsum`` the row sums of ``scale · w``: the gradient with
     respect to ``x`` is ``out − x_dsum[:, None] · x``.  Both modes need a label mask.
 
+    ``opt`` (:func:`fused_optimizer_args`) fuses the optimiser step of the rows of ``x`` into the launch: ``out`` is
+    then their gradient buffer, already holding every other contribution, and comes back cleared.
+
     ``loss_share`` splits the loss arithmetic between the two launches of a training step (the same pairs with the
     roles of ``x`` and ``y`` swapped): launch 0 and launch 1 each add the loss of one half of the ``(x, y)`` plane
     (256 x 256 blocks of alternating parity); ``-1`` keeps all of it in this launch.  The one-CTA kernel does not
     split: there share 0 takes everything and share 1 nothing."""
-    pair = x.shape[1] == 256 and score_mode == 0 and pair_kernel_enabled()
+    pair = x.shape[1] == 256 and score_mode == 0 and opt is None and pair_kernel_enabled()
     if score_mode != 0:
         assert mask is not None and score_mode in (1, 2)
         for t, rows, nm in ((x_bias, x.shape[0], "x_bias"), (y_bias, y.shape[0], "y_bias")):
@@ -121,6 +151,7 @@ def kvsall_fused(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, loss_acc: 
           float(base), float(scale), int(with_loss), _ptr(status), int(num_ctas),
           _ptr(mask), 0 if mask is None else mask.shape[1], float(pos_delta), _ptr(trace),
           int(score_mode), _ptr(x_bias), _ptr(y_bias), _ptr(x_dsum), float(margin),
+          ctypes.addressof(opt) if opt is not None else None,
           others=(y, out, loss_acc, status, mask, trace, x_bias, y_bias, x_dsum))
 
 

@@ -188,6 +188,45 @@ def test_kvsall_fused_distance_score(nx, ny, D, ctas, with_loss):
         assert abs(loss.item() - ref_loss.item()) / abs(ref_loss.item()) < 2e-3
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("nx,ny,D,ctas", [(300, 200, 64, 0), (1000, 777, 256, 0), (1500, 2100, 256, 5), (700, 900, 128, 148)])
+def test_fused_entity_update_equals_scoring_then_optimizer(kind, nx, ny, D, ctas):
+    """The optimiser applied inside the scoring launch (by the CTA that completes a 128-row tile of the gradient)
+    against the same launch followed by the optimiser sweep: two steps, each starting from the same state in both
+    paths (the gradient sums come from atomics, and over several steps that rounding noise grows through the bf16
+    rounding of the operand), with a gradient buffer that already holds other contributions."""
+    torch.manual_seed(kind * 100 + nx)
+    y = (torch.randn(ny, D, device=DEV) * 0.3).to(torch.bfloat16)
+    mask = _pack_mask(torch.rand(nx, ny, device=DEV) < 0.05)
+    lr, b1, b2, eps, wd = 0.05, 0.9, 0.999, 1e-3, 0.01
+    P = torch.randn(nx, D, device=DEV) * 0.3
+    m, v = torch.zeros_like(P), torch.zeros_like(P)
+    step = torch.zeros(1, dtype=torch.int64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    count = torch.zeros((nx + 127) // 128, dtype=torch.int32, device=DEV)
+    for it in range(2):
+        g0 = torch.randn_like(P) * 1e-3                      # e.g. the row gradients of the lookups
+        res = []
+        for fused in (False, True):
+            Pi, mi, vi, gi = P.clone(), m.clone(), v.clone(), g0.clone()
+            Xi = Pi.to(torch.bfloat16)
+            loss = torch.zeros(1, dtype=torch.float64, device=DEV)
+            opt = K.fused_optimizer_args(kind, Pi, mi, vi, Xi, count, step, lr, b1, b2, eps, wd) if fused else None
+            K.kvsall_fused(Xi, y, gi, loss, status, 0.01, 1.0 / 64, True, num_ctas=ctas, mask=mask, pos_delta=0.9,
+                           opt=opt)
+            if not fused:
+                K.optimizer_step(kind, Pi, gi, mi, vi, Xi, step, lr, b1, b2, eps, wd)
+            torch.cuda.synchronize()
+            K.check_status(status)
+            assert float(gi.abs().max()) == 0.0 and int(count.abs().max()) == 0
+            assert torch.equal(Xi, Pi.to(torch.bfloat16))
+            res.append((Pi, mi, vi, loss))
+        for a, b in zip(*res):
+            assert (a - b).abs().max() <= 2e-5 * a.abs().max().clamp_min(1e-6) + 1e-7
+        P, m, v = res[0][:3]
+        step += 1
+
+
 def test_kvsall_fused_accumulates_and_splits_work():
     """Two launches add up; any CTA count gives the same sums (work ranges are arbitrary cuts of the tile grid)."""
     torch.manual_seed(0)
