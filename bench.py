@@ -385,6 +385,114 @@ def run_torch(args) -> dict:
             "repeats": len(blocks), "clocks": clocks, "last_loss": loss_host[-1], "gpu_launches": 0}
 
 
+def run_replicated(args) -> dict:
+    """Config 7: one data-parallel training step of a model that is replicated on every GPU (ConEx, d = 256, 32 output
+    channels, KvsAll over the config-2 graph, 1024 queries per GPU, Adam).  ``--impl ours``: parameters and gradients in
+    the symmetric heap, buckets reduced + updated + broadcast by one kernel each, queued from autograd hooks
+    (``parallel/peer_allreduce_optimizer.py``).  ``--impl torch``: ``DistributedDataParallel`` (bucketed NCCL all-reduce
+    from hooks) + fused ``torch.optim.Adam``, which is what the reference's ``torchDDP`` trainer runs
+    (``dicee/trainer/torch_trainer_ddp.py:87-122``).  Forward and backward are the same PyTorch modules in both arms."""
+    import torch
+    import torch.distributed as dist
+    from dice_embeddings_b200.data.datasets import KvsAll
+    from dice_embeddings_b200.data.synthetic import zipf_kg
+    from dice_embeddings_b200.models import MODEL_REGISTRY
+    rank, local, world = _dist_env()
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    c = KVSALL_CONFIGS[2]
+    NE, NR, NT, D, B = c["entities"], c["relations"], c["triples"], c["dim"], 1024
+    triples = zipf_kg(NE, NR, NT, c["zipf_e"], c["zipf_r"], seed=0)
+    ds = KvsAll(triples, NE, NR, "EntityPrediction", label_smoothing_rate=c["smoothing"]).to(dev)
+    num_pairs = len(ds)
+    torch.manual_seed(0)
+    margs = dict(model="ConEx", embedding_dim=D, num_entities=NE, num_relations=NR, optim="Adam", learning_rate=0.001,
+                 scoring_technique="KvsAll", num_of_output_channels=32, kernel_size=3)
+    with torch.device(dev):
+        model = MODEL_REGISTRY["ConEx"][0](margs)
+    with torch.no_grad():     # the default N(0, 1) embeddings saturate this model within three steps
+        model.entity_embeddings.weight.mul_(0.1)
+        model.relation_embeddings.weight.mul_(0.1)
+    model.train()
+    n_params = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    if args.impl == "torch":
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+        opt = torch.optim.Adam(model.parameters(), lr=0.001, fused=True)
+        check = None
+    else:
+        if world == 1:
+            raise SystemExit("--config 7 --impl ours needs --gpus >= 2 (the optimiser is a collective)")
+        from dice_embeddings_b200.parallel.peer_allreduce_optimizer import PeerAllReduceOptimizer
+        net = model
+        opt = PeerAllReduceOptimizer(model, lr=0.001, device=dev)
+        check = opt.check
+    g = torch.Generator().manual_seed(1234)
+    total_steps = args.warmup + args.steps
+    perm = torch.cat([torch.randperm(num_pairs, generator=g) for _ in range(-(-total_steps * B * world // num_pairs))])
+    idx_dev = perm[: total_steps * B * world].view(total_steps, world, B)[:, rank].contiguous().to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step(i):
+        x, y = ds.make_batch(idx_dev[i])
+        loss = torch.nn.functional.binary_cross_entropy_with_logits(net(x), y)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize(dev)
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    blocks, total = [], 0.0
+    while True:
+        evs = []
+        barrier()
+        for i in range(args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            loss = step(args.warmup + i)
+            e1.record()
+            evs.append((e0, e1))
+        barrier()
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        blocks.append(float(t))
+        total += blocks[-1]
+        if total >= 1000.0 or len(blocks) >= 100:
+            break
+    clocks = sampler.stop() if sampler is not None else None
+    if check is not None:
+        check()
+    last = float(loss.detach())
+    ms = statistics.median(blocks)
+    tps = B * world * NT / num_pairs
+    res = {"metric": "train triples/sec (device-timed, max over ranks)", "value": tps * args.steps / (ms / 1e3),
+           "unit": "triples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "fp32 (replicated PyTorch modules)", "data": "synthetic", "impl": args.impl,
+           "config": {"model": "ConEx KvsAll d=256, 32 output channels", "global_batch": B * world, "seq_len": None,
+                      "parallelism": f"dp{world}: " + ("symmetric-heap buckets, reduce + Adam + broadcast in one kernel "
+                                                        "per bucket, queued from autograd hooks" if args.impl == "ours"
+                                                        else "DistributedDataParallel + fused torch.optim.Adam"),
+                      "entities": NE, "relations": NR, "parameters": n_params, "optimizer": "Adam lr=0.001",
+                      "l2": "256 MiB buffer written between timed steps"},
+           "repeats": len(blocks), "clocks": clocks, "last_loss": last,
+           "gpu_launches": 0 if args.impl == "torch" else args.steps * (2 * len(opt.buckets) + 1)}
+    if world > 1:
+        dist.destroy_process_group()
+    return res if rank == 0 else None
+
+
 def run_ours_cpu(args) -> dict:
     """Config 1: Keci KvsAll on the CPU through ``Execute(...).start()`` with the generic PyTorch trainer; K steps
     are timed on the host between optimiser steps, exactly as the reference arm is timed."""
@@ -755,13 +863,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--ref_num_core", type=int, default=0,
                     help="reference arm: DataLoader workers (its --num_core flag; 0 is the reference's default)")
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6, 7])
     ap.add_argument("--model", default=None, help="override the model of the chosen config (ours arm)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.config == 6:
         res = run_eval_small(args)
+    elif args.config == 7:
+        res = run_replicated(args)
     elif args.impl == "reference":
         res = run_reference(args)
     elif args.impl == "torch":
