@@ -72,19 +72,9 @@ struct Cfg {
   static constexpr int SMEM_BYTES = TILE_BYTES * (1 + NSTAGE) + 1024 /*align*/ + 512 /*barriers*/;
 };
 
-__device__ __forceinline__ float fast_ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ float fast_lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float fast_rcp(float x) {
-  float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float fast_tanh(float x) {
@@ -123,20 +113,8 @@ struct TileCursor {
   }
 };
 
-// log1p(e) / e on [0, 1] (degree-5 minimax fit, absolute error of log1p below 7e-6): keeps the logarithm of the
-// loss off the special-function unit, which the exponential and the reciprocal already occupy.
-__device__ __forceinline__ float log1p_over_e(float e) {
-  float q = -0.02397957257926464f;
-  q = fmaf(q, e, 0.10150004923343658f);
-  q = fmaf(q, e, -0.2102936953306198f);
-  q = fmaf(q, e, 0.3252951502799988f);
-  q = fmaf(q, e, -0.49937260150909424f);
-  q = fmaf(q, e, 0.9999918341636658f);
-  return q;
-}
-
 // One thread's 32 logits of a tile: dS = sigmoid(s) - label packed as bf16 pairs (low half = even column) and, with
-// LOSS, the BCE-with-logits terms added to loss.  FULL: all 32 columns are valid entries of Y.
+// LOSS, the BCE-with-logits terms added to lacc.  FULL: all 32 columns are valid entries of Y.
 // SCORE selects how the logit follows from the dot product a = x.y of the tensor cores:
 //   0  s = a
 //   1  s = a + xb + yb[col]                     (per-query scalar terms of the Clifford models)
@@ -144,11 +122,20 @@ __device__ __forceinline__ float log1p_over_e(float e) {
 //      to the second GEMM is then dS / distance, and the caller subtracts (sum of those values) * x from the result:
 //      d s / d x = (y - x) / distance.
 // dsum accumulates the values handed to the second GEMM (SCORE != 0 only).
+//
+// The epilogue is bound by instruction issue (sixteen warps share four schedulers), so everything is derived from one
+// hyperbolic tangent of the non-positive half argument, t = tanh(-|s| / 2) in (-1, 0]:
+//   sigmoid(|s|) = u = 0.5 - 0.5 t  in [0.5, 1)        (no cancellation)
+//   tanh(s / 2)  = t with its sign flipped where s >= 0 (one logic op on the sign bits)
+//   dS = sigmoid(s) - label = 0.5 tanh(s / 2) + c      with c = 0.5 - label (one of two constants, picked by the mask)
+//   BCE(s, label) = softplus(s) - label s = c s + 0.5 |s| - ln 2 * lg2(u)
+// and the three sums  sum c s,  sum |s|,  sum lg2(u)  are kept apart (lacc[0..2]) and combined once per segment.
+// Two special-function operations (tanh, lg2) and about ten other instructions per logit.
 template <bool LOSS, bool MASK, bool FULL, int SCORE>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t mword, float base, float label_pos,
-                                               int y_valid, uint32_t (&packed)[16], float& loss, float xb,
+                                               int y_valid, uint32_t (&packed)[16], float (&lacc)[3], float xb,
                                                const float* __restrict__ yb, float margin, float& dsum) {
-  constexpr float LOG2E = 1.4426950408889634f;
+  const float c_base = 0.5f - base, c_pos = 0.5f - label_pos;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float ds2[2];
@@ -162,23 +149,25 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
         gscale = rsqrtf(d2);
         s = fmaf(-d2, gscale, margin);
       }
-      float label = base;
-      if constexpr (MASK) label = ((mword >> (i + u)) & 1u) ? label_pos : base;
-      float sig;
+      float c = c_base;
+      if constexpr (MASK) c = ((mword >> (i + u)) & 1u) ? c_pos : c_base;
+      const bool valid = FULL || (i + u < y_valid);
+      float th;  // tanh(s / 2)
       if constexpr (LOSS) {
-        const float e = fast_ex2(-fabsf(s) * LOG2E);       // exp(-|s|)
-        const float inv = fast_rcp(1.f + e);               // sigmoid(|s|)
-        sig = s >= 0.f ? inv : e * inv;
-        float l = fmaf(log1p_over_e(e), e, fmaxf(s, 0.f)); // softplus(s)
-        l = fmaf(-label, s, l);
-        if (!FULL && i + u >= y_valid) l = 0.f;
-        loss += l;
+        const float tn = fast_tanh(-0.5f * fabsf(s));
+        th = __uint_as_float(__float_as_uint(tn) ^ (~__float_as_uint(s) & 0x80000000u));
+        const float lg = fast_lg2(fmaf(-0.5f, tn, 0.5f));
+        if (valid) {
+          lacc[0] = fmaf(c, s, lacc[0]);
+          lacc[1] += fabsf(s);
+          lacc[2] += lg;
+        }
       } else {
-        sig = fmaf(fast_tanh(0.5f * s), 0.5f, 0.5f);
+        th = fast_tanh(0.5f * s);
       }
-      float d = sig - label;
+      float d = fmaf(0.5f, th, c);
       if constexpr (SCORE == 2) d *= gscale;
-      if (!FULL && i + u >= y_valid) d = 0.f;
+      if (!valid) d = 0.f;
       if constexpr (SCORE != 0) dsum += d;
       ds2[u] = d;
     }
@@ -406,7 +395,7 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       const int n = static_cast<int>(min(static_cast<long long>(run), w_end - w));
       const int x_global = x * BLOCK_X + row;
       const bool valid_x = x_global < p.x_rows;
-      float seg_loss = 0.f;
+      float seg_l[3] = {0.f, 0.f, 0.f};   // sum c s, sum |s|, sum lg2(sigmoid(|s|)) of this thread's logits
       float seg_dsum = 0.f;
       float xb = 0.f;
       if constexpr (SCORE != 0) {
@@ -454,10 +443,10 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tc_wait_ld();
         uint32_t packed[16];
         if (y_valid >= 32) {
-          epilogue_chunk<LOSS, MASK, true, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_loss, xb, yb,
+          epilogue_chunk<LOSS, MASK, true, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_l, xb, yb,
                                                   p.margin, seg_dsum);
         } else {
-          epilogue_chunk<LOSS, MASK, false, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_loss, xb, yb,
+          epilogue_chunk<LOSS, MASK, false, SCORE>(r, mword, p.base, label_pos, y_valid, packed, seg_l, xb, yb,
                                                    p.margin, seg_dsum);
         }
         tmem_st16(s_addr, packed);
@@ -468,7 +457,7 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (lane == 0) mbar_arrive(ds_full + b);
       }
       if (!ok) break;
-      if (valid_x) loss_acc += seg_loss;
+      if (valid_x) loss_acc += fmaf(0.5f, seg_l[1], seg_l[0]) - 0.6931471805599453f * seg_l[2];
       if constexpr (SCORE != 0) {
         if (valid_x && p.x_dsum != nullptr) atomicAdd(p.x_dsum + x_global, seg_dsum * p.scale);
       }
