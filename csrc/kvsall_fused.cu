@@ -129,13 +129,17 @@ struct TileCursor {
 //   tanh(s / 2)  = t with its sign flipped where s >= 0 (one logic op on the sign bits)
 //   dS = sigmoid(s) - label = 0.5 tanh(s / 2) + c      with c = 0.5 - label (one of two constants, picked by the mask)
 //   BCE(s, label) = softplus(s) - label s = c s + 0.5 |s| - ln 2 * lg2(u)
-// and the three sums  sum c s,  sum |s|,  sum lg2(u)  are kept apart (lacc[0..2]) and combined once per segment.
-// Two special-function operations (tanh, lg2) and about ten other instructions per logit.
+// and the three sums  sum c s,  sum |s|,  sum lg2(u)  are kept apart (lacc[0..2]) and combined once per segment.  The
+// last one is the logarithm of a product: the 32 factors u of a chunk (each in [0.5, 1), so the product stays above
+// 2^-32) are multiplied up and ONE logarithm is taken per chunk.  That leaves one special-function operation (the
+// tanh) and about ten other instructions per logit; the special-function unit (16 results per clock and SM) would
+// otherwise need as many cycles per tile as the two GEMMs do.
 template <bool LOSS, bool MASK, bool FULL, int SCORE>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t mword, float base, float label_pos,
                                                int y_valid, uint32_t (&packed)[16], float (&lacc)[3], float xb,
                                                const float* __restrict__ yb, float margin, float& dsum) {
   const float c_base = 0.5f - base, c_pos = 0.5f - label_pos;
+  float uprod = 1.f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float ds2[2];
@@ -156,11 +160,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
       if constexpr (LOSS) {
         const float tn = fast_tanh(-0.5f * fabsf(s));
         th = __uint_as_float(__float_as_uint(tn) ^ (~__float_as_uint(s) & 0x80000000u));
-        const float lg = fast_lg2(fmaf(-0.5f, tn, 0.5f));
+        const float us = fmaf(-0.5f, tn, 0.5f);   // sigmoid(|s|)
         if (valid) {
           lacc[0] = fmaf(c, s, lacc[0]);
           lacc[1] += fabsf(s);
-          lacc[2] += lg;
+          uprod *= us;
         }
       } else {
         th = fast_tanh(0.5f * s);
@@ -174,6 +178,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
     __nv_bfloat162 v = __floats2bfloat162_rn(ds2[0], ds2[1]);  // .x (low 16 bits) = even K element
     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
   }
+  if constexpr (LOSS) lacc[2] += fast_lg2(uprod);
 }
 
 template <int D, bool LOSS, bool MASK, int SCORE>
