@@ -23,13 +23,13 @@ static inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// [rows, D] bf16 row-major, box = 64 columns x 128 rows, 128-byte swizzle, out-of-range rows read as zero.
-static inline int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, int D) {
+// [rows, D] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range rows read as zero.
+static inline int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, int D, int box_rows = 128) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return -1;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 2};
-  cuuint32_t box[2] = {64, 128};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
