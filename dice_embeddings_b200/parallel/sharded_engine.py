@@ -203,6 +203,8 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._side = torch.cuda.Stream(device=dev)
+        # DICE_B200_OVERLAP_BACKWARD=0 keeps the serial order entity role -> query role -> S2 -> backward
+        self.overlap_backward = os.environ.get("DICE_B200_OVERLAP_BACKWARD", "1") != "0"
         if comm == "p2p":
             segs = [dict(param=self.R, grad=self.gR, m=self.mR, v=self.vR, grad_table=self.tab.gR, grad_mc=self.mc.gR)]
             if self.coeff_trainable:
@@ -283,6 +285,43 @@ class ShardedKvsAllEngine:
                 K.positive_scan(self.dp_all, self.offsets_loc, n, self.first)
                 K.positive_correction(self.dp_all, self.offsets_loc, self.values_loc, self.first, self.Q, self.E_bf16,
                                       self.dQ, self.gE, self.loss_acc[:1], self.pos_weight, scale, n, D, 1, 0)
+        if masks and self.overlap_backward:
+            # query role first; then the barrier S2, the pull of the partial dQ rows over NVLink and the backward of the
+            # composition run on a parallel branch BESIDE the entity-role launch, which needs none of them: the wait
+            # for the slowest rank and the link latency of the pull hide behind tensor-core work
+            K.kvsall_fused(self.Q, e_loc, self.dQ, self.loss_acc[:1], self.status, self.base, scale, True,
+                           mask=self.mask_q, pos_delta=self.pos_weight, loss_share=1)
+            self._mark("fused_Q")
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                self._barrier()                           # S2: every rank's partial dQ is complete
+                K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
+                                         self.NE, self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ,
+                                         self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
+                                         self.status)
+            K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
+                           mask=self.mask_e, pos_delta=self.pos_weight, loss_share=0)
+            self._mark("fused_E")
+            main.wait_stream(self._side)
+            self._mark("S2+backward (joined)")
+        else:
+            self._score_then_backward(masks, main, e_loc, scale, W, n, D)
+        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
+                         status=self.status)
+        self._mark("optim_E")
+        self._barrier()                                   # S3: shards updated, partial sums complete, dQ pulls done
+        self._mark("S3")
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            self.dQ.zero_()
+        # one launch: the replicated tables are updated from the sum of all ranks' gradient buffers (multimem.ld_reduce
+        # or peer loads: the all-reduce folded into the update) and the last block sums the loss partials
+        self._tail.launch(*a, scale)
+        main.wait_stream(self._side)
+        self._mark("optim_R")
+
+    def _score_then_backward(self, masks, main, e_loc, scale, W, n, D) -> None:
+        """Serial order: entity role, query role, S2, owner-side backward."""
         # both launches add half of the loss terms each (the epilogue with loss costs several times the one without)
         K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
                        mask=self.mask_e, pos_delta=self.pos_weight, loss_share=0)
@@ -299,19 +338,6 @@ class ShardedKvsAllEngine:
                                  self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ, self.gE, self.gR,
                                  self.gC if self.coeff_trainable else None, n, D, self.status)
         self._mark("backward+reduce_scatter")
-        K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
-                         status=self.status)
-        self._mark("optim_E")
-        self._barrier()                                   # S3: shards updated, partial sums complete, dQ pulls done
-        self._mark("S3")
-        self._side.wait_stream(main)
-        with torch.cuda.stream(self._side):
-            self.dQ.zero_()
-        # one launch: the replicated tables are updated from the sum of all ranks' gradient buffers (multimem.ld_reduce
-        # or peer loads: the all-reduce folded into the update) and the last block sums the loss partials
-        self._tail.launch(*a, scale)
-        main.wait_stream(self._side)
-        self._mark("optim_R")
 
     def launches_per_step(self) -> int:
         if self.comm != "p2p":
