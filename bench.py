@@ -265,7 +265,8 @@ def run_ours(args) -> dict:
         "gpu_launches": engine.launches_per_step() * args.steps,
     }
     if world > 1:
-        out["comm"] = {"multimem": bool(getattr(engine, "multimem", False)), "barriers_per_step": 3}
+        out["comm"] = {"multimem": bool(getattr(engine, "multimem", False)), "barriers_per_step": 4 if getattr(engine, "overlap_backward", False) else 3,
+                       "barriers_on_critical_path": 3}
     if equal is not None:
         out.update(equal)
     if world > 1:

@@ -140,17 +140,20 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
     """Replay the sharded step.  ``h, r, labels`` hold the *global* batch (rank ``k`` owns its rows
     ``[k·b, (k+1)·b)``); entity ``e`` lives on rank ``e % world`` at row ``e // world``.
 
-    Three barriers per step:
+    Four barriers per step, three of them on the critical path of the device code (``S2`` and ``S2b`` run on a
+    branch beside the entity-role scoring launch, which needs nothing from the other ranks):
 
     * ``S1`` after the lookup (peer reads of head rows) and the broadcast of query rows and batch indices,
-    * ``S2`` after the two scoring passes over the local shard (every rank's partial ``dQ`` is complete),
-    * ``S3`` after the *owner-side* backward (the owner of a head row sums that query's ``dQ`` partials from all
+    * ``S2`` after the query-role scoring pass over the local shard (every rank's partial ``dQ`` is complete),
+    * ``S2b`` after the *owner-side* backward (the owner of a head row sums that query's ``dQ`` partials from all
       ranks, applies the chain rule and adds the row gradient to its own shard, so no row gradient crosses the
-      fabric) and the update of the local entity shard; behind it the replicated relation table is updated from
-      all ranks' gradient buffers and the loss partials are summed.  ``S3`` also orders the next step's peer reads
-      of the updated entity rows, so no barrier opens a step.
+      fabric); behind it the replicated relation table is updated from all ranks' gradient buffers and ``dQ`` is
+      cleared,
+    * ``S3`` after the entity-role scoring pass (loss, dense gradient of the shard) and the update of the local
+      entity shard; behind it the loss partials are summed.  ``S3`` also orders the next step's peer reads of the
+      updated entity rows, so no barrier opens a step.
 
-    Fault injection: ``skip_barrier`` ∈ {"S1","S2","S3"} removes that barrier on every rank (the phases it
+    Fault injection: ``skip_barrier`` ∈ {"S1","S2","S2b","S3"} removes that barrier on every rank (the phases it
     separated then count as one, which is what the hazard check looks at); ``absent_rank`` never starts;
     ``drop(sender, peer, count)`` suppresses single barrier signals.  ``steps`` repeats the step on the same batch.
     Returns ``(E_new, R_new, loss)`` assembled from the shards, or raises the first rank failure."""
@@ -202,10 +205,8 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 s = Q @ Eloc.T                                 # [B, local rows]
                 y = labels[:, own]
                 sig = 1.0 / (1.0 + np.exp(-s))
-                heap.add("loss", rank, rank, 0, np.sum(np.maximum(s, 0) - s * y + np.log1p(np.exp(-np.abs(s)))))
                 ds = (sig - y) / (B * NE)
-                gE[rank][:n_own] += ds.T @ Q
-                heap.add("dQ", rank, rank, np.arange(B), ds @ Eloc)   # partial over this shard, kept locally
+                heap.add("dQ", rank, rank, np.arange(B), ds @ Eloc)   # query role: partial over this shard, kept locally
                 barrier(rank, "S2")                            # every rank's partial of dQ is complete
                 # owner-side backward: queries whose head row lives here; their dQ is the sum of all ranks' partials
                 h_all, r_all = heap.read("h", rank, rank), heap.read("r", rank, rank)
@@ -214,14 +215,18 @@ def run_sharded_step(world: int, E, R, h, r, labels, lr, skip_barrier: Optional[
                 hv_own = heap.read("E", rank, rank)[h_all[mine] // W]
                 np.add.at(gE[rank], h_all[mine] // W, dq * Rrep[rank][r_all[mine]])
                 heap.add("gR", rank, rank, r_all[mine], dq * hv_own)
+                barrier(rank, "S2b")                           # every rank's backward is through
+                gR = sum(heap.read("gR", p, rank) for p in range(W))     # replicated all-reduce by peer reads
+                Rrep[rank] = Rrep[rank] - lr * gR
+                heap.write("dQ", rank, rank, slice(None), 0.0)
+                # entity role (on the device it runs beside S2, the backward and S2b): loss and dense gradient
+                heap.add("loss", rank, rank, 0, np.sum(np.maximum(s, 0) - s * y + np.log1p(np.exp(-np.abs(s)))))
+                gE[rank][:n_own] += ds.T @ Q
                 g_own = gE[rank].copy()                        # the update follows this rank's own reads in stream order
                 heap.write("E", rank, rank, slice(None), heap.bufs["E"][rank] - lr * g_own)
                 gE[rank][:] = 0.0
-                barrier(rank, "S3")                            # shards updated, all partial sums complete, dQ pulls done
-                gR = sum(heap.read("gR", p, rank) for p in range(W))     # replicated all-reduce by peer reads
+                barrier(rank, "S3")                            # shards updated, loss partials complete
                 loss = sum(float(heap.read("loss", p, rank)[0]) for p in range(W)) / (B * NE)
-                Rrep[rank] = Rrep[rank] - lr * gR
-                heap.write("dQ", rank, rank, slice(None), 0.0)
                 losses[rank] = loss
         except BaseException as exc:  # noqa: BLE001 - reported to the caller
             errors[rank] = exc

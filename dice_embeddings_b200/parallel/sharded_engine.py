@@ -211,6 +211,7 @@ class ShardedKvsAllEngine:
                 segs.append(dict(param=self.coeff, grad=self.gC[:1], m=self.mC, v=self.vC, grad_table=self.tab.gC))
             self._tail = K.StepTail(self.opt_kind, segs, self.step_count, self.status, finish=True,
                                     loss_out=self.loss_out, acc_table=self.tab.loss, n_acc=W, n_grad=W)
+            self._tail_rest = K.StepTail(self.opt_kind, segs, self.step_count, self.status, finish=False, n_grad=W)
         self._phase_events = [] if os.environ.get("DICE_B200_PHASE_TIMING") == "1" else None
         self._phase_names = []
         self._phase_slots = torch.zeros(32, dtype=torch.int64, device=dev)
@@ -299,13 +300,26 @@ class ShardedKvsAllEngine:
                                          self.NE, self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ,
                                          self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
                                          self.status)
+                # still beside the entity-role launch: once every rank's backward is through (barrier S2b) the
+                # replicated tables are updated from the sum of all ranks' gradient buffers, and dQ is cleared
+                self._barrier()
+                self._tail_rest.launch(*a, scale)
+                self.dQ.zero_()
             K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
                            mask=self.mask_e, pos_delta=self.pos_weight, loss_share=0)
             self._mark("fused_E")
             main.wait_stream(self._side)
-            self._mark("S2+backward (joined)")
-        else:
-            self._score_then_backward(masks, main, e_loc, scale, W, n, D)
+            self._mark("side branch joined")
+            K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
+                             status=self.status)
+            self._mark("optim_E")
+            self._barrier()                               # S3: shards updated, loss partials complete everywhere
+            self._mark("S3")
+            K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=W,
+                          status=self.status)
+            self._mark("finish")
+            return
+        self._score_then_backward(masks, main, e_loc, scale, W, n, D)
         K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
                          status=self.status)
         self._mark("optim_E")
@@ -342,6 +356,8 @@ class ShardedKvsAllEngine:
     def launches_per_step(self) -> int:
         if self.comm != "p2p":
             return 9
+        if self.label_mode == "mask" and self.overlap_backward:
+            return 4 + 10          # four barriers (one of them beside the entity-role launch) + ten other kernels
         return 3 + (9 if self.label_mode == "mask" else 8)
 
     # ------------------------------------------------------------------ the step, collective flavour

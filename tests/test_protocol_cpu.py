@@ -33,7 +33,7 @@ def test_two_steps_match_and_the_closing_barrier_orders_the_next_lookup():
         ps.run_sharded_step(3, E, R, h, r, y, lr=0.3, steps=2, skip_barrier="S3")
 
 
-@pytest.mark.parametrize("name", ["S1", "S2", "S3"])
+@pytest.mark.parametrize("name", ["S1", "S2", "S2b", "S3"])
 def test_removed_barrier_is_reported_as_hazard(name):
     E, R, h, r, y = _problem(seed=2)
     with pytest.raises(ps.ProtocolHazard):
