@@ -144,10 +144,13 @@ class ShardedKvsAllEngine:
         self.loss_out = torch.zeros(1, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier_count = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier_count_side = torch.zeros(1, dtype=torch.int32, device=dev)
 
         self.tab = SimpleNamespace(E=heap.table("E"), gR=heap.table("gR"), gC=heap.table("gC"),
                                    Q=heap.table("Q"), dQ=heap.table("dQ"), ids=heap.table("ids"),
                                    loss=heap.table("loss"), sig=heap.table("sig"))
+        assert W <= 32, "the signal region holds two sets of 32 slots"
+        self.sig_side = self.tab.sig + 128        # second half of every rank's 64-word signal region
         mm = self.multimem
         # Measured on B200s (owner-side backward of 4096 owned queries, d = 256): multimem.ld_reduce 30 us against 17 us
         # with peer loads at two ranks, 52 us against 25 us at four.  The 16-byte in-switch reductions of scattered
@@ -218,8 +221,13 @@ class ShardedKvsAllEngine:
         heap.host_barrier()
 
     # ------------------------------------------------------------------ the step, peer-memory flavour
-    def _barrier(self) -> None:
-        K.p2p_barrier(self.tab.sig, self.rank, self.W, self.barrier_count, self.status)
+    def _barrier(self, side: bool = False) -> None:
+        """Bounded device barrier.  The barriers of the parallel branch (``side``) use their own signal slots and
+        counter: they may be in flight at the same time as a barrier of the main branch."""
+        if side:
+            K.p2p_barrier(self.sig_side, self.rank, self.W, self.barrier_count_side, self.status)
+        else:
+            K.p2p_barrier(self.tab.sig, self.rank, self.W, self.barrier_count, self.status)
 
     def _optimizers_and_finish(self, scale: float) -> None:
         """Collective flavour: replicated gradients and the loss were already summed by library collectives."""
@@ -295,26 +303,30 @@ class ShardedKvsAllEngine:
             self._mark("fused_Q")
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
-                self._barrier()                           # S2: every rank's partial dQ is complete
+                self._barrier(side=True)                  # S2: every rank's partial dQ is complete
                 K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
                                          self.NE, self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ,
                                          self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
                                          self.status)
-                # still beside the entity-role launch: once every rank's backward is through (barrier S2b) the
-                # replicated tables are updated from the sum of all ranks' gradient buffers, and dQ is cleared
-                self._barrier()
+                backward_done = torch.cuda.Event()
+                backward_done.record(self._side)
+                # the branch goes on beside the entity update and S3: once every rank's backward is through (barrier
+                # S2b) the replicated tables are updated from the sum of all ranks' gradient buffers, and dQ is cleared
+                self._barrier(side=True)
                 self._tail_rest.launch(*a, scale)
                 self.dQ.zero_()
             K.kvsall_fused(e_loc, self.Q, self.gE, self.loss_acc[:1], self.status, self.base, scale, True,
                            mask=self.mask_e, pos_delta=self.pos_weight, loss_share=0)
             self._mark("fused_E")
-            main.wait_stream(self._side)
-            self._mark("side branch joined")
+            main.wait_event(backward_done)                # the row gradients of the lookups are in gE
+            self._mark("backward joined")
             K.optimizer_step(self.opt_kind, self.E, self.gE, self.mE, self.vE, self.E_bf16, self.step_count, *a,
                              status=self.status)
             self._mark("optim_E")
             self._barrier()                               # S3: shards updated, loss partials complete everywhere
             self._mark("S3")
+            main.wait_stream(self._side)
+            self._mark("side branch joined")
             K.finish_step(self.loss_acc, self.loss_out, scale, self.step_count, acc_table=self.tab.loss, n_acc=W,
                           status=self.status)
             self._mark("finish")
