@@ -511,6 +511,54 @@ extern "C" int dice_compose_backward_owner(int model, int normalize, const long 
   }
 }
 
+// Reduce-scatter of the partial query gradients on its own: for every batch row whose head entity this rank owns, the
+// W partial rows (one per rank, in dq_table) are summed by peer loads and the sum replaces this rank's own partial row
+// in dq_local.  Nobody else reads those rows (a peer pulls only the rows IT owns), so the update is in place.  One
+// thread moves 16 bytes and holds W independent loads in flight; with about 30 registers per thread its blocks fit
+// beside the one scoring CTA per SM, so the NVLink transfer runs under the entity-role launch, and the backward of the
+// composition afterwards reads local memory only.
+extern "C" int dice_dq_pull_owner(const long long* idx_h, int idx_stride, const float* const* dq_table, int n_dq,
+                                  float* dq_local, int n, int D, int W, int rank, long long num_entities, int* status,
+                                  void* stream);
+
+namespace dice {
+__global__ void __launch_bounds__(256) dq_pull_owner_kernel(const long long* __restrict__ idx_h, int idx_stride,
+                                                            const float* const* __restrict__ dq_table, int n_dq,
+                                                            float* __restrict__ dq_local, int n, int D, int W, int rank,
+                                                            long long num_entities, int* status) {
+  if (*status != 0) return;
+  const int per_row = D >> 2;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (tid >= static_cast<long long>(n) * per_row) return;
+  const int i = static_cast<int>(tid / per_row);
+  const int c = static_cast<int>(tid % per_row);
+  const long long h = idx_h[static_cast<long long>(i) * idx_stride];
+  if (h < 0 || h >= num_entities) {
+    atomicCAS(status, 0, ST_BAD_INDEX);
+    return;
+  }
+  if (h % W != rank) return;   // another rank owns this head row and pulls it
+  const size_t off = (static_cast<size_t>(i) * D >> 2) + c;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < n_dq; ++k) {
+    const float4 v = reinterpret_cast<const float4*>(dq_table[k])[off];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  reinterpret_cast<float4*>(dq_local)[off] = acc;
+}
+}  // namespace dice
+
+extern "C" int dice_dq_pull_owner(const long long* idx_h, int idx_stride, const float* const* dq_table, int n_dq,
+                                  float* dq_local, int n, int D, int W, int rank, long long num_entities, int* status,
+                                  void* stream) {
+  if (n <= 0 || W <= 1) return 0;
+  if (status == nullptr || dq_table == nullptr || (D & 3) || (reinterpret_cast<uintptr_t>(dq_local) & 15)) return -5;
+  const long long threads = static_cast<long long>(n) * (D >> 2);
+  dice::dq_pull_owner_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      idx_h, idx_stride > 0 ? idx_stride : 1, dq_table, n_dq, dq_local, n, D, W, rank, num_entities, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 // Two-shot all-reduce of one slice [lo, hi) of a flat gradient vector fused with the optimiser update of that slice
 // and the broadcast of the updated parameters (see bucket_reduce_update_kernel).  lo, hi and every buffer must be
 // 16-byte aligned.  g_mc / p_mc != null select the NVSwitch multicast path, otherwise g_src / p_dst (device arrays of

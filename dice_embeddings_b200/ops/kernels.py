@@ -219,6 +219,16 @@ def compose_backward_owner(model: int, normalize: bool, idx_h, idx_r, ent_local:
           others=(idx_h, idx_r, ent_local, dq, g_ent_local, g_rel, status))
 
 
+def dq_pull_owner(idx_h, dq_table: torch.Tensor, n_dq: int, dq_local: torch.Tensor, n: int, D: int, W: int, rank: int,
+                  num_entities: int, status: torch.Tensor, idx_stride: int = 1) -> None:
+    """Reduce-scatter of the partial query gradients on its own: for the batch rows whose head this rank owns,
+    ``dq_local[i] = Σ_k dq_table[k][i]`` (peer loads), in place.  Light enough (16 bytes per thread, ~30 registers)
+    to run beside a scoring launch, so the NVLink transfer hides under tensor-core work."""
+    _req(dq_local, torch.float32, "dq_local")
+    _call("dice_dq_pull_owner", dq_local, _ptr(idx_h), int(idx_stride), _ptr(dq_table), int(n_dq), _ptr(dq_local),
+          int(n), int(D), int(W), int(rank), int(num_entities), _ptr(status), others=(idx_h, dq_table, status))
+
+
 def mask_stride(n_bits: int) -> int:
     """Words per mask row: one bit per column, padded to a multiple of 4 words (and of the 128-column tile)."""
     return ((n_bits + 127) // 128) * 4

@@ -206,6 +206,7 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._side = torch.cuda.Stream(device=dev)
+        self._capture_stream = torch.cuda.Stream(device=dev, priority=-1)
         # DICE_B200_OVERLAP_BACKWARD=0 keeps the serial order entity role -> query role -> S2 -> backward
         self.overlap_backward = os.environ.get("DICE_B200_OVERLAP_BACKWARD", "1") != "0"
         if comm == "p2p":
@@ -304,8 +305,11 @@ class ShardedKvsAllEngine:
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
                 self._barrier(side=True)                  # S2: every rank's partial dQ is complete
+                # the reduce-scatter of dQ alone (light blocks that fit beside the scoring CTA of every SM: the NVLink
+                # transfer runs under the entity-role launch), then the backward of the composition on local memory
+                K.dq_pull_owner(self.h_all, self.tab.dQ, W, self.dQ, n, D, W, self.rank, self.NE, self.status)
                 K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
-                                         self.NE, self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ,
+                                         self.NE, self.NR, self.R, self.coeff, self.dQ, None, 0, 0,
                                          self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
                                          self.status)
                 backward_done = torch.cuda.Event()
@@ -440,7 +444,9 @@ class ShardedKvsAllEngine:
                 self._graph_lr = -1.0
                 return
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # captured on a high-priority stream: kernel nodes inherit it, so where the main branch and the side branch
+            # are both ready the scoring launch gets its CTAs resident first and the side branch fills what is left
+            with torch.cuda.graph(g, stream=self._capture_stream):
                 launch()
             self._graph, self._graph_lr = g, self.lr
         self._graph.replay()
