@@ -89,10 +89,13 @@ int dice_compose_backward_owner(int model, int normalize, const long long* idx_h
                                 int num_relations, const float* rel, const float* coeff, const float* dq,
                                 const float* const* dq_table, int n_dq, const void* dq_mc, float* g_ent_local,
                                 float* g_rel, float* g_coeff, int n, int D, int* status, void* stream);
-// Reduce-scatter of the partial query gradients alone: for the rows whose head this rank owns, dq_local[i] = sum over
-// the n_dq buffers of dq_table (peer loads), in place.  Light enough to run beside a scoring launch.
-int dice_dq_pull_owner(const long long* idx_h, int idx_stride, const float* const* dq_table, int n_dq, float* dq_local,
-                       int n, int D, int W, int rank, long long num_entities, int* status, void* stream);
+// Reduce-scatter of the partial query gradients alone.  dice_owned_rows compacts the batch rows whose head this rank
+// owns into list[0 .. *count) (count zeroed by the caller); dice_dq_pull_owner then sets dq_local[i] = sum over the n_dq
+// buffers of dq_table (peer loads) for the listed rows, in place.  Light enough to run beside a scoring launch.
+int dice_owned_rows(const long long* idx_h, int idx_stride, int n, int W, int rank, long long num_entities, int* list,
+                    int* count, int* status, void* stream);
+int dice_dq_pull_owner(const int* list, const int* count, const float* const* dq_table, int n_dq, float* dq_local, int D,
+                       int* status, void* stream);
 // Scalar-per-thread variants (any D; used by the sampled engines and the collective-library comparison pipeline).
 int dice_lookup_compose(int model, int normalize, const long long* idx_h, const long long* idx_r,
                         const float* const* ent, int W, long long num_entities, const float* rel, const float* coeff,

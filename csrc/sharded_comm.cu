@@ -511,51 +511,77 @@ extern "C" int dice_compose_backward_owner(int model, int normalize, const long 
   }
 }
 
-// Reduce-scatter of the partial query gradients on its own: for every batch row whose head entity this rank owns, the
-// W partial rows (one per rank, in dq_table) are summed by peer loads and the sum replaces this rank's own partial row
-// in dq_local.  Nobody else reads those rows (a peer pulls only the rows IT owns), so the update is in place.  One
-// thread moves 16 bytes and holds W independent loads in flight; with about 30 registers per thread its blocks fit
-// beside the one scoring CTA per SM, so the NVLink transfer runs under the entity-role launch, and the backward of the
-// composition afterwards reads local memory only.
-extern "C" int dice_dq_pull_owner(const long long* idx_h, int idx_stride, const float* const* dq_table, int n_dq,
-                                  float* dq_local, int n, int D, int W, int rank, long long num_entities, int* status,
-                                  void* stream);
-
+// Reduce-scatter of the partial query gradients on its own, in two launches.
+//   dice_owned_rows    compacts the batch rows whose head entity this rank owns into a list (order irrelevant);
+//   dice_dq_pull_owner sums, for every listed row, the W partial rows (one per rank, in dq_table) by peer loads and puts
+//                      the sum in place of this rank's own partial row in dq_local.  Nobody else reads those rows (a
+//                      peer pulls only the rows IT owns), so the update is in place.
+// The pull is a persistent grid of light blocks (16 bytes per work item, W independent loads in flight per thread,
+// about 30 registers): its blocks fit beside the one scoring CTA per SM, and because the list holds owned rows only,
+// every thread has loads in flight, which is what keeps NVLink busy at one resident block per SM.  The backward of
+// the composition afterwards reads local memory only.
 namespace dice {
-__global__ void __launch_bounds__(256) dq_pull_owner_kernel(const long long* __restrict__ idx_h, int idx_stride,
-                                                            const float* const* __restrict__ dq_table, int n_dq,
-                                                            float* __restrict__ dq_local, int n, int D, int W, int rank,
-                                                            long long num_entities, int* status) {
+__global__ void __launch_bounds__(256) owned_rows_kernel(const long long* __restrict__ idx_h, int idx_stride, int n, int W,
+                                                         int rank, long long num_entities, int* __restrict__ list,
+                                                         int* __restrict__ count, int* status) {
+  if (*status != 0) return;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool owned = false;
+  if (i < n) {
+    const long long h = idx_h[static_cast<long long>(i) * idx_stride];
+    if (h < 0 || h >= num_entities) atomicCAS(status, 0, ST_BAD_INDEX);
+    else owned = (h % W == rank);
+  }
+  const unsigned ballot = __ballot_sync(0xffffffffu, owned);
+  const int lane = threadIdx.x & 31;
+  int base = 0;
+  if (lane == 0 && ballot != 0u) base = atomicAdd(count, __popc(ballot));
+  base = __shfl_sync(0xffffffffu, base, 0);
+  if (owned) list[base + __popc(ballot & ((1u << lane) - 1u))] = i;
+}
+
+__global__ void __launch_bounds__(256) dq_pull_list_kernel(const int* __restrict__ list, const int* __restrict__ count,
+                                                           const float* const* __restrict__ dq_table, int n_dq,
+                                                           float* __restrict__ dq_local, int D, const int* status) {
   if (*status != 0) return;
   const int per_row = D >> 2;
-  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (tid >= static_cast<long long>(n) * per_row) return;
-  const int i = static_cast<int>(tid / per_row);
-  const int c = static_cast<int>(tid % per_row);
-  const long long h = idx_h[static_cast<long long>(i) * idx_stride];
-  if (h < 0 || h >= num_entities) {
-    atomicCAS(status, 0, ST_BAD_INDEX);
-    return;
+  const long long total = static_cast<long long>(*count) * per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += stride) {
+    const int i = list[t / per_row];
+    const size_t off = (static_cast<size_t>(i) * D >> 2) + static_cast<size_t>(t % per_row);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int k = 0; k < n_dq; ++k) {
+      const float4 v = reinterpret_cast<const float4*>(dq_table[k])[off];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(dq_local)[off] = acc;
   }
-  if (h % W != rank) return;   // another rank owns this head row and pulls it
-  const size_t off = (static_cast<size_t>(i) * D >> 2) + c;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k = 0; k < n_dq; ++k) {
-    const float4 v = reinterpret_cast<const float4*>(dq_table[k])[off];
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-  }
-  reinterpret_cast<float4*>(dq_local)[off] = acc;
 }
 }  // namespace dice
 
-extern "C" int dice_dq_pull_owner(const long long* idx_h, int idx_stride, const float* const* dq_table, int n_dq,
-                                  float* dq_local, int n, int D, int W, int rank, long long num_entities, int* status,
-                                  void* stream) {
-  if (n <= 0 || W <= 1) return 0;
-  if (status == nullptr || dq_table == nullptr || (D & 3) || (reinterpret_cast<uintptr_t>(dq_local) & 15)) return -5;
-  const long long threads = static_cast<long long>(n) * (D >> 2);
-  dice::dq_pull_owner_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      idx_h, idx_stride > 0 ? idx_stride : 1, dq_table, n_dq, dq_local, n, D, W, rank, num_entities, status);
+// list: int[n]; count: int[1], zeroed by the caller before the launch.
+extern "C" int dice_owned_rows(const long long* idx_h, int idx_stride, int n, int W, int rank, long long num_entities,
+                               int* list, int* count, int* status, void* stream) {
+  if (n <= 0) return 0;
+  if (status == nullptr || list == nullptr || count == nullptr || W < 1) return -5;
+  dice::owned_rows_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      idx_h, idx_stride > 0 ? idx_stride : 1, n, W, rank, num_entities, list, count, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int dice_dq_pull_owner(const int* list, const int* count, const float* const* dq_table, int n_dq,
+                                  float* dq_local, int D, int* status, void* stream) {
+  if (n_dq <= 1) return 0;
+  if (status == nullptr || dq_table == nullptr || list == nullptr || count == nullptr || (D & 3) ||
+      (reinterpret_cast<uintptr_t>(dq_local) & 15))
+    return -5;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  dice::dq_pull_list_kernel<<<2 * sms, 256, 0, static_cast<cudaStream_t>(stream)>>>(list, count, dq_table, n_dq, dq_local,
+                                                                                   D, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -110,7 +110,8 @@ class _Sigs:
     dice_lookup_vec_supported = [_i, _i]
     dice_lookup_compose_vec = [_i, _i, _p, _p, _i, _p, _p, _i, _l, _i, _p, _p, _p, _i, _p, _l, _p, _p, _l, _i, _i, _p, _p]
     dice_compose_backward_owner = [_i, _i, _p, _p, _i, _p, _i, _i, _l, _i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p, _p]
-    dice_dq_pull_owner = [_p, _i, _p, _i, _p, _i, _i, _i, _i, _l, _p, _p]
+    dice_owned_rows = [_p, _i, _i, _i, _i, _l, _p, _p, _p, _p]
+    dice_dq_pull_owner = [_p, _p, _p, _i, _p, _i, _p, _p]
     dice_bucket_reduce_update = [_i, _p, _p, _p, _p, _p, _p, _p, _p, _l, _l, _i, _f, _f, _f, _f, _f, _f, _p, _p]
     dice_step_tail = [_i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _f, _f, _f, _f, _f, _p, _p, _d, _p, _i, _p, _p, _p]
     dice_positive_correction_noalloc = [_p, _p, _p, _p, _p, _p, _p, _p, _f, _f, _i, _i, _i, _i, _p]

@@ -219,14 +219,24 @@ def compose_backward_owner(model: int, normalize: bool, idx_h, idx_r, ent_local:
           others=(idx_h, idx_r, ent_local, dq, g_ent_local, g_rel, status))
 
 
-def dq_pull_owner(idx_h, dq_table: torch.Tensor, n_dq: int, dq_local: torch.Tensor, n: int, D: int, W: int, rank: int,
-                  num_entities: int, status: torch.Tensor, idx_stride: int = 1) -> None:
-    """Reduce-scatter of the partial query gradients on its own: for the batch rows whose head this rank owns,
-    ``dq_local[i] = Σ_k dq_table[k][i]`` (peer loads), in place.  Light enough (16 bytes per thread, ~30 registers)
-    to run beside a scoring launch, so the NVLink transfer hides under tensor-core work."""
+def owned_rows(idx_h, n: int, W: int, rank: int, num_entities: int, rows: torch.Tensor, count: torch.Tensor,
+               status: torch.Tensor, idx_stride: int = 1) -> None:
+    """Compact the batch rows whose head entity this rank owns (``h % W == rank``) into ``rows[0 .. count)``;
+    ``count`` (int32 scalar) must be zero on entry."""
+    _req(rows, torch.int32, "rows")
+    _req(count, torch.int32, "count")
+    _call("dice_owned_rows", rows, _ptr(idx_h), int(idx_stride), int(n), int(W), int(rank), int(num_entities),
+          _ptr(rows), _ptr(count), _ptr(status), others=(idx_h, count, status))
+
+
+def dq_pull_owner(rows: torch.Tensor, count: torch.Tensor, dq_table: torch.Tensor, n_dq: int, dq_local: torch.Tensor,
+                  D: int, status: torch.Tensor) -> None:
+    """Reduce-scatter of the partial query gradients on its own: for the listed batch rows (see :func:`owned_rows`),
+    ``dq_local[i] = Σ_k dq_table[k][i]`` (peer loads), in place.  A persistent grid of light blocks (16 bytes per work
+    item, ~30 registers) that fits beside a scoring launch, so the NVLink transfer hides under tensor-core work."""
     _req(dq_local, torch.float32, "dq_local")
-    _call("dice_dq_pull_owner", dq_local, _ptr(idx_h), int(idx_stride), _ptr(dq_table), int(n_dq), _ptr(dq_local),
-          int(n), int(D), int(W), int(rank), int(num_entities), _ptr(status), others=(idx_h, dq_table, status))
+    _call("dice_dq_pull_owner", dq_local, _ptr(rows), _ptr(count), _ptr(dq_table), int(n_dq), _ptr(dq_local), int(D),
+          _ptr(status), others=(rows, count, dq_table, status))
 
 
 def mask_stride(n_bits: int) -> int:

@@ -145,6 +145,8 @@ class ShardedKvsAllEngine:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier_count = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier_count_side = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.owned_list = torch.zeros(W * batch_size, dtype=torch.int32, device=dev)   # batch rows whose head lives here
+        self.owned_count = torch.zeros(1, dtype=torch.int32, device=dev)
 
         self.tab = SimpleNamespace(E=heap.table("E"), gR=heap.table("gR"), gC=heap.table("gC"),
                                    Q=heap.table("Q"), dQ=heap.table("dQ"), ids=heap.table("ids"),
@@ -304,10 +306,12 @@ class ShardedKvsAllEngine:
             self._mark("fused_Q")
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
+                self.owned_count.zero_()
+                K.owned_rows(self.h_all, n, W, self.rank, self.NE, self.owned_list, self.owned_count, self.status)
                 self._barrier(side=True)                  # S2: every rank's partial dQ is complete
                 # the reduce-scatter of dQ alone (light blocks that fit beside the scoring CTA of every SM: the NVLink
                 # transfer runs under the entity-role launch), then the backward of the composition on local memory
-                K.dq_pull_owner(self.h_all, self.tab.dQ, W, self.dQ, n, D, W, self.rank, self.NE, self.status)
+                K.dq_pull_owner(self.owned_list, self.owned_count, self.tab.dQ, W, self.dQ, D, self.status)
                 K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
                                          self.NE, self.NR, self.R, self.coeff, self.dQ, None, 0, 0,
                                          self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
