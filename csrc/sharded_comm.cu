@@ -516,12 +516,21 @@ extern "C" int dice_compose_backward_owner(int model, int normalize, const long 
 //   dice_dq_pull_owner sums, for every listed row, the W partial rows (one per rank, in dq_table) by peer loads and puts
 //                      the sum in place of this rank's own partial row in dq_local.  Nobody else reads those rows (a
 //                      peer pulls only the rows IT owns), so the update is in place.
-// The pull is a persistent grid of light blocks (16 bytes per work item, W independent loads in flight per thread,
-// about 30 registers): its blocks fit beside the one scoring CTA per SM, and because the list holds owned rows only,
-// every thread has loads in flight, which is what keeps NVLink busy at one resident block per SM.  The backward of
-// the composition afterwards reads local memory only.
+// Both run on a graph branch beside the entity-role scoring launch, whose one CTA per SM (18 warps of 96 registers)
+// leaves room for ONE more warp of at most 32 registers in each of the SM's four register partitions (measured: blocks
+// of 256 threads do not start until the scoring CTA has left, a one-warp kernel does).  Hence blocks of 128 threads
+// capped at 32 registers.  The pull is a persistent grid (16 bytes per work item, W independent loads in flight per
+// thread); because the list holds owned rows only, every thread has loads in flight, which is what keeps NVLink busy
+// at one resident block per SM.  The backward of the composition afterwards reads local memory only.
 namespace dice {
-__global__ void __launch_bounds__(256) owned_rows_kernel(const long long* __restrict__ idx_h, int idx_stride, int n, int W,
+// Kernels meant to run beside a scoring launch ask for the same shared-memory carveout as that launch (the maximum):
+// an SM is not shared between kernels that want different carveouts.
+template <typename Kern>
+static void prefer_max_shared(Kern kern) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
+__global__ void __launch_bounds__(128, 16) owned_rows_kernel(const long long* __restrict__ idx_h, int idx_stride, int n, int W,
                                                          int rank, long long num_entities, int* __restrict__ list,
                                                          int* __restrict__ count, int* status) {
   if (*status != 0) return;
@@ -540,7 +549,7 @@ __global__ void __launch_bounds__(256) owned_rows_kernel(const long long* __rest
   if (owned) list[base + __popc(ballot & ((1u << lane) - 1u))] = i;
 }
 
-__global__ void __launch_bounds__(256) dq_pull_list_kernel(const int* __restrict__ list, const int* __restrict__ count,
+__global__ void __launch_bounds__(128, 16) dq_pull_list_kernel(const int* __restrict__ list, const int* __restrict__ count,
                                                            const float* const* __restrict__ dq_table, int n_dq,
                                                            float* __restrict__ dq_local, int D, const int* status) {
   if (*status != 0) return;
@@ -566,7 +575,8 @@ extern "C" int dice_owned_rows(const long long* idx_h, int idx_stride, int n, in
                                int* list, int* count, int* status, void* stream) {
   if (n <= 0) return 0;
   if (status == nullptr || list == nullptr || count == nullptr || W < 1) return -5;
-  dice::owned_rows_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  dice::prefer_max_shared(dice::owned_rows_kernel);
+  dice::owned_rows_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       idx_h, idx_stride > 0 ? idx_stride : 1, n, W, rank, num_entities, list, count, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -580,7 +590,8 @@ extern "C" int dice_dq_pull_owner(const int* list, const int* count, const float
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  dice::dq_pull_list_kernel<<<2 * sms, 256, 0, static_cast<cudaStream_t>(stream)>>>(list, count, dq_table, n_dq, dq_local,
+  dice::prefer_max_shared(dice::dq_pull_list_kernel);
+  dice::dq_pull_list_kernel<<<2 * sms, 128, 0, static_cast<cudaStream_t>(stream)>>>(list, count, dq_table, n_dq, dq_local,
                                                                                    D, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -282,6 +282,7 @@ class ShardedKvsAllEngine:
         self.gR.zero_()                                   # every peer has read last step's partial sums by now
         self.gC.zero_()
         self.loss_acc.zero_()
+        self.owned_count.zero_()                          # (here: a fill kernel would not fit beside the scoring launch)
         if masks:
             main.wait_stream(self._side)
             K.build_label_masks(self.dp_all, self.offsets_loc, self.values_loc, n, 1, 0, self.mask_q, self.mask_e,
@@ -306,7 +307,6 @@ class ShardedKvsAllEngine:
             self._mark("fused_Q")
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
-                self.owned_count.zero_()
                 K.owned_rows(self.h_all, n, W, self.rank, self.NE, self.owned_list, self.owned_count, self.status)
                 self._barrier(side=True)                  # S2: every rank's partial dQ is complete
                 # the reduce-scatter of dQ alone (light blocks that fit beside the scoring CTA of every SM: the NVLink
