@@ -208,7 +208,15 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._side = torch.cuda.Stream(device=dev)
-        self._capture_stream = torch.cuda.Stream(device=dev, priority=-1)
+        # Reduce-scatter of dQ as a light kernel of its own (DICE_B200_DQ_PULL=1) or inside the backward kernel (=0).
+        # Measured, ms per step at N = 2 / 8: 0.236 / 0.349 with the light kernel (it fits beside the scoring CTA, but
+        # its 32-register budget keeps only a few of the W peer loads of a thread in flight, which costs more than the
+        # overlap gains once W is large), 0.246 / 0.318 inside the backward kernel.  Default: the light kernel at W = 2.
+        pull = os.environ.get("DICE_B200_DQ_PULL", "auto")
+        self.dq_pull = (W <= 2) if pull == "auto" else pull == "1"
+        # with the light kernel the graph is captured on a high-priority stream: kernel nodes inherit it, so where both
+        # branches are ready the scoring launch gets its CTAs resident first and the side branch fills what is left
+        self._capture_stream = torch.cuda.Stream(device=dev, priority=-1) if self.dq_pull else None
         # DICE_B200_OVERLAP_BACKWARD=0 keeps the serial order entity role -> query role -> S2 -> backward
         self.overlap_backward = os.environ.get("DICE_B200_OVERLAP_BACKWARD", "1") != "0"
         if comm == "p2p":
@@ -307,15 +315,23 @@ class ShardedKvsAllEngine:
             self._mark("fused_Q")
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
-                K.owned_rows(self.h_all, n, W, self.rank, self.NE, self.owned_list, self.owned_count, self.status)
+                if self.dq_pull:
+                    K.owned_rows(self.h_all, n, W, self.rank, self.NE, self.owned_list, self.owned_count, self.status)
                 self._barrier(side=True)                  # S2: every rank's partial dQ is complete
-                # the reduce-scatter of dQ alone (light blocks that fit beside the scoring CTA of every SM: the NVLink
-                # transfer runs under the entity-role launch), then the backward of the composition on local memory
-                K.dq_pull_owner(self.owned_list, self.owned_count, self.tab.dQ, W, self.dQ, D, self.status)
-                K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
-                                         self.NE, self.NR, self.R, self.coeff, self.dQ, None, 0, 0,
-                                         self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
-                                         self.status)
+                if self.dq_pull:
+                    # the reduce-scatter of dQ alone (light blocks that fit beside the scoring CTA of every SM: the
+                    # NVLink transfer runs under the entity-role launch), then the backward on local memory
+                    K.dq_pull_owner(self.owned_list, self.owned_count, self.tab.dQ, W, self.dQ, D, self.status)
+                    K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
+                                             self.NE, self.NR, self.R, self.coeff, self.dQ, None, 0, 0,
+                                             self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
+                                             self.status)
+                else:
+                    # owner-side backward with the reduce-scatter inside it (peer loads or multimem.ld_reduce)
+                    K.compose_backward_owner(self.code, self.normalize, self.h_all, self.r_all, self.E, W, self.rank,
+                                             self.NE, self.NR, self.R, self.coeff, None, self.tab.dQ, W, self.mc.dQ,
+                                             self.gE, self.gR, self.gC if self.coeff_trainable else None, n, D,
+                                             self.status)
                 backward_done = torch.cuda.Event()
                 backward_done.record(self._side)
                 # the branch goes on beside the entity update and S3: once every rank's backward is through (barrier
@@ -448,9 +464,8 @@ class ShardedKvsAllEngine:
                 self._graph_lr = -1.0
                 return
             g = torch.cuda.CUDAGraph()
-            # captured on a high-priority stream: kernel nodes inherit it, so where the main branch and the side branch
-            # are both ready the scoring launch gets its CTAs resident first and the side branch fills what is left
-            with torch.cuda.graph(g, stream=self._capture_stream):
+            with (torch.cuda.graph(g, stream=self._capture_stream) if self._capture_stream is not None
+                  else torch.cuda.graph(g)):
                 launch()
             self._graph, self._graph_lr = g, self.lr
         self._graph.replay()
