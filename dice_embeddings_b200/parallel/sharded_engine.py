@@ -11,23 +11,29 @@ step  kernel                                                 traffic over NVLink
       compose, publish the bf16 query row and the batch        of query row reaches every rank (the all-gather of
       indices on every rank                                    Q); without multicast, one store per rank
 S1    ``p2p_barrier``
-2     ``build_label_masks`` + ``kvsall_fused`` (entity-        none (local shard × all queries; the label CSR is
-      stationary): loss and dense ``dE`` of the local shard    partitioned by owner when the engine is built)
-3     ``kvsall_fused`` (query-stationary): partial ``dQ``      none (the partials of the whole batch stay local)
-      of the local shard for all queries
-S2    ``p2p_barrier``
-4     ``compose_backward_owner``: the *owner of the head       peer loads of the query-gradient rows of all ranks
-      row* sums that query's partial ``dQ`` over all ranks,     (the reduce-scatter of dQ, done by its consumer);
-      applies the chain rule and adds the row gradient to       ``multimem.ld_reduce.add`` on request (slower for
-      its own gradient shard                                    scattered rows).  No row gradient crosses the fabric.
-5     ``optimizer_step`` over the local entity shard           none
+2     ``build_label_masks`` + ``kvsall_fused`` (query-         none (local shard × all queries; the label CSR is
+      stationary): partial ``dQ`` of the local shard for       partitioned by owner when the engine is built; the
+      all queries                                              partials of the whole batch stay local)
+3m    main branch: ``kvsall_fused`` (entity-stationary):       none
+      loss and dense ``dE`` of the local shard
+3s    side branch, beside 3m.  ``S2``, then the *owner of      peer loads of the query-gradient rows of all ranks
+      the head row* sums that query's partial ``dQ`` over      (the reduce-scatter of dQ, done by its consumer:
+      all ranks, applies the chain rule and adds the row       inside ``compose_backward_owner``, or as the light
+      gradient to its own gradient shard; ``S2b``; the         kernel ``dq_pull_owner`` in front of it);
+      replicated tables are updated from the sum of all        peer loads of every rank's gradient buffer: the
+      ranks' gradient buffers (``step_tail``); dQ cleared      all-reduce folded into the update.  No row gradient
+                                                               crosses the fabric.
+4     main joins the backward; ``optimizer_step`` over the     none
+      local entity shard
 S3    ``p2p_barrier``
-6     ``step_tail``: the replicated tables are updated from    peer loads (or ``multimem.ld_reduce``) of every
-      the sum of all ranks' gradient buffers and the last       rank's buffer: the all-reduce folded into the update
-      block sums the loss partials
+5     main joins the side branch; ``finish_step`` sums the     peer loads of the loss partials
+      loss partials
 ====  =====================================================  ==================================================
 
-``S3`` also orders the next step's peer reads of the updated entity rows, so a step needs three barriers.  Buffers
+``S3`` also orders the next step's peer reads of the updated entity rows, so no barrier opens a step: three barriers
+lie on the critical path, ``S2`` and ``S2b`` (on signal slots and a counter of their own, since they can be in flight
+together with ``S3``) beside the entity-role launch.  ``DICE_B200_OVERLAP_BACKWARD=0`` and the sparse-label flavour keep
+the serial order entity role → query role → ``S2`` → backward → update → ``S3`` → ``step_tail``.  Buffers
 that peers read after a barrier (``gR``, loss partials) are cleared behind the *next* barrier, when every peer is
 known to have read them.  Once a barrier times out the status word is set and every later kernel that would touch
 peer memory returns at once; :meth:`check` reports it.
