@@ -142,3 +142,33 @@ def test_semantic_constraint_zeroes_impossible_triples(tmp_path):
         pytest.approx(float(plain.triple_score(inv_e[h_in], inv_r[r], inv_e[t_in])))
     assert float(strict.triple_score(inv_e[h_in], inv_r[r], inv_e[t_out])) == 0.0
     assert float(plain.triple_score(inv_e[h_in], inv_r[r], inv_e[t_out])) > 0.0
+
+
+def test_dict_vocabularies_vectorised_and_written_by_the_helper_process(tmp_path):
+    """The dict-of-lists filter vocabularies: the sort-based construction equals the per-triple loop (input order kept
+    per key, absent keys give an empty list), and the helper process writes the three pickles of a run folder."""
+    import pickle
+    import subprocess
+    import sys
+    from collections import defaultdict
+
+    import numpy as np
+
+    from dice_embeddings_b200.data import vocab_writer
+    from dice_embeddings_b200.data.vocab import get_ee_vocab, get_er_vocab, get_re_vocab
+    rng = np.random.default_rng(0)
+    d = np.stack([rng.integers(0, 60, 3000), rng.integers(0, 7, 3000), rng.integers(0, 60, 3000)], 1)
+    for fn, (i, j, k) in ((get_er_vocab, (0, 1, 2)), (get_re_vocab, (1, 2, 0)), (get_ee_vocab, (0, 2, 1))):
+        ref = defaultdict(list)
+        for row in d.tolist():
+            ref[(row[i], row[j])].append(row[k])
+        got = fn(d)
+        assert dict(got) == dict(ref)
+        assert got[(10 ** 6, 0)] == []
+    assert dict(get_er_vocab(np.zeros((0, 3), dtype=np.int64))) == {}
+    src = tmp_path / "triples.npy"
+    np.save(src, d)
+    subprocess.run([sys.executable, vocab_writer.__file__, str(src), str(tmp_path)], check=True)
+    assert not src.exists()
+    with open(tmp_path / "re_vocab.p", "rb") as f:
+        assert dict(pickle.load(f)) == dict(get_re_vocab(d))
