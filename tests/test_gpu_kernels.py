@@ -485,3 +485,35 @@ def test_positive_scan_equals_cumsum(n):
     K.positive_scan(dp, offsets, n, first)
     want = torch.cat((torch.zeros(1, dtype=torch.int64, device=DEV), counts[dp].cumsum(0)))
     assert torch.equal(first.long(), want)
+
+
+@pytest.mark.parametrize("W,rank,n,D", [(2, 1, 1000, 64), (4, 2, 4096, 256), (8, 5, 3001, 128)])
+def test_owned_row_list_and_dq_pull(W, rank, n, D):
+    """Reduce-scatter of the partial query gradients as a kernel of its own, with the W ranks' buffers emulated by W
+    local tensors: the rows whose head this rank owns are listed exactly once, their partial rows are summed in place
+    in this rank's buffer, and every other row of that buffer stays as it was."""
+    torch.manual_seed(W * 100 + rank)
+    NE = 5000
+    h = torch.randint(0, NE, (n,), device=DEV)
+    parts = [torch.randn(n, D, device=DEV) for _ in range(W)]
+    table = K.pointer_table(parts, DEV)
+    rows = torch.zeros(n, dtype=torch.int32, device=DEV)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    expect = parts[rank].clone()
+    owned = (h % W) == rank
+    expect[owned] = sum(p[owned] for p in parts)
+    K.owned_rows(h, n, W, rank, NE, rows, count, status)
+    K.dq_pull_owner(rows, count, table, W, parts[rank], D, status)
+    torch.cuda.synchronize()
+    K.check_status(status)
+    c = int(count)
+    assert c == int(owned.sum())
+    assert torch.equal(torch.sort(rows[:c].long()).values, owned.nonzero().flatten())
+    assert (parts[rank] - expect).abs().max() < 1e-5
+    bad = h.clone()
+    bad[7] = NE + 3                                      # an id outside the table is reported, not followed
+    count.zero_()
+    K.owned_rows(bad, n, W, rank, NE, rows, count, status)
+    torch.cuda.synchronize()
+    assert int(status) != 0
