@@ -65,8 +65,9 @@ def _read_table(path: str, read_only_few=None, sample_triples_ratio=None, backen
             df = polars.read_csv(path, has_header=False, n_rows=read_only_few, columns=[0, 1, 2],
                                  new_columns=["subject", "relation", "object"], separator=sep,
                                  infer_schema_length=0).to_pandas()
-        except (ImportError, AttributeError, RuntimeError):
+        except (ImportError, AttributeError, RuntimeError) as exc:
             # polars is optional (absent, or a stub that refuses to read); pandas reads the same files
+            print(f"--backend polars is not usable here ({type(exc).__name__}); reading {path} with pandas instead")
             df = pd.read_csv(path, sep=separator, header=None, nrows=read_only_few, usecols=[0, 1, 2],
                              names=["subject", "relation", "object"], dtype=str)
     elif ext in ("nt", "ttl", "txt", "csv", "zst", "tsv"):
