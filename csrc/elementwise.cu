@@ -10,6 +10,7 @@
 #include "algebra.cuh"
 #include "optim.cuh"
 #include "ptx_sm100.cuh"
+#include "launch_pdl.cuh"
 
 namespace dice {
 
@@ -723,6 +724,7 @@ __device__ __forceinline__ void optimizer_segment(const OptParams& p, long long 
 }
 
 __global__ void __launch_bounds__(256) step_tail_kernel(const StepTailParams p) {
+  griddep_wait();
   if (p.status != nullptr && *p.status != 0) return;
   const long long t = *p.step_rw + 1;
   for (int s = 0; s < p.n_seg; ++s) optimizer_segment(p.seg[s], t);
@@ -961,7 +963,9 @@ extern "C" int dice_step_tail(int kind, int n_seg, float* const* param, float* c
   long long blocks = (total / 4 + threads - 1) / threads;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  step_tail_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (launch_pdl(step_tail_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0,
+                 static_cast<cudaStream_t>(stream), p) != cudaSuccess)
+    return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -30,6 +30,7 @@
 #include "tile_map.cuh"
 #include "tma_host.cuh"
 #include "kvsall_common.cuh"
+#include "launch_pdl.cuh"
 
 #include <stdio.h>
 
@@ -111,6 +112,9 @@ kvsall_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_smem;
+  // everything above (barriers, tensor-memory allocation, descriptor prefetch) may overlap the previous kernel's tail
+  griddep_wait();
+  griddep_launch();
   const uint32_t tmem_out = tmem_base;              // D columns
   const uint32_t tmem_s0 = tmem_base + 256;         // two S buffers of 128 columns
 
@@ -454,8 +458,7 @@ static int launch(const CUtensorMap& tx, const CUtensorMap& ty, const KvsAllPara
       return -3;
     configured[dev] = true;
   }
-  kern<<<num_ctas, NUM_THREADS, Cfg<D>::SMEM_BYTES, stream>>>(tx, ty, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, dim3(num_ctas), dim3(NUM_THREADS), Cfg<D>::SMEM_BYTES, stream, tx, ty, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace dice

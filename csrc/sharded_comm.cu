@@ -18,6 +18,7 @@
 #include "dice_b200.h"
 #include "algebra.cuh"
 #include "ptx_sm100.cuh"
+#include "launch_pdl.cuh"
 
 namespace dice {
 
@@ -190,6 +191,8 @@ struct BwdOwnerParams {
 
 template <int K>
 __global__ void __launch_bounds__(256) compose_backward_owner_kernel(const BwdOwnerParams p) {
+  griddep_wait();
+  griddep_launch();
   if (*p.status != 0) return;
   const int w = p.D / K;
   const int per_row = w >> 3;
@@ -418,8 +421,10 @@ static int launch_lookup_vec(const LookupVecParams& p, cudaStream_t s) {
 template <int K>
 static int launch_bwd_owner(const BwdOwnerParams& p, cudaStream_t s) {
   const long long n = static_cast<long long>(p.n) * (p.D / K / 8);
-  compose_backward_owner_kernel<K><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(compose_backward_owner_kernel<K>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, p) ==
+                 cudaSuccess
+             ? 0
+             : -4;
 }
 
 static int algebra_blocks(int model) {

@@ -214,6 +214,9 @@ class ShardedKvsAllEngine:
         self._graph = None
         self._graph_lr = None
         self._side = torch.cuda.Stream(device=dev)
+        # Programmatic dependent launch (csrc/launch_pdl.cuh) is measured and tested on the single-GPU step only (1 %
+        # there); the sharded step keeps ordinary stream-ordered launches unless DICE_B200_PDL=1 is set.
+        os.environ.setdefault("DICE_B200_PDL", "0")
         # Reduce-scatter of dQ as a light kernel of its own (DICE_B200_DQ_PULL=1) or inside the backward kernel (=0).
         # Measured, ms per step at N = 2 / 8: 0.236 / 0.349 with the light kernel (it fits beside the scoring CTA, but
         # its 32-register budget keeps only a few of the W peer loads of a thread in flight, which costs more than the
