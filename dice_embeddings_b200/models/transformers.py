@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 from torch.nn import functional as F
 
-from .base import BaseKGE
+from .base import BaseKGE, IdentityClass
 
 
 class LayerNorm(nn.Module):
@@ -110,7 +110,16 @@ class CoKEConfig:
 
 
 class CoKE(BaseKGE):
-    """Contextualised KG embedding: the hidden state of the MASK position scores all entities."""
+    """Contextualised KG embedding: the hidden state of the MASK position scores all entities.  That hidden state is
+    the query vector of the bilinear contract (``compose``), so the tensor-core scoring function and the ranking kernel
+    apply whenever the tail normaliser is the identity (its default)."""
+
+    @property
+    def bilinear(self) -> bool:
+        return isinstance(self.normalize_tail_entity_embeddings, IdentityClass)
+
+    def compose(self, h: torch.Tensor, r: torch.Tensor):
+        return self._encode(h, r), None
 
     def __init__(self, args, config: CoKEConfig = None):
         super().__init__(args)
