@@ -402,7 +402,9 @@ class ShardedKvsAllEngine:
         if self.comm != "p2p":
             return 9
         if self.label_mode == "mask" and self.overlap_backward:
-            return 4 + 10          # four barriers (one of them beside the entity-role launch) + ten other kernels
+            # four barriers + lookup, masks, two scoring launches, backward, replicated-table update, entity update,
+            # loss sum (+ owned-row list and dQ pull)
+            return 4 + 8 + (2 if self.dq_pull else 0)
         return 3 + (9 if self.label_mode == "mask" else 8)
 
     # ------------------------------------------------------------------ the step, collective flavour
