@@ -299,7 +299,8 @@ class ShardedKvsAllEngine:
         self.gR.zero_()                                   # every peer has read last step's partial sums by now
         self.gC.zero_()
         self.loss_acc.zero_()
-        self.owned_count.zero_()                          # (here: a fill kernel would not fit beside the scoring launch)
+        if self.dq_pull:
+            self.owned_count.zero_()                      # (here: a fill kernel would not fit beside the scoring launch)
         if masks:
             main.wait_stream(self._side)
             K.build_label_masks(self.dp_all, self.offsets_loc, self.values_loc, n, 1, 0, self.mask_q, self.mask_e,
