@@ -17,7 +17,7 @@ def _ref_fused(x, y, base, scale):
     s = x.float() @ y.float().t()
     loss = (torch.nn.functional.softplus(s) - base * s).double().sum()
     ds = torch.sigmoid(s) - base
-    out = scale * (ds.to(torch.bfloat16).float() @ y.float())
+    out = scale * (ds @ y.float())          # plain fp32: the kernel's bf16 rounding of dS is part of what is tested
     return loss, out
 
 
